@@ -1,0 +1,170 @@
+/*
+ * vqattn.h - C ABI of the B200 (sm_100a) fused vector-quantised attention library.
+ *
+ * Every entry point is plain C: pointers, sizes and small structs; no C++ or framework
+ * types cross the boundary.  The caller owns every buffer (inputs, outputs, workspaces);
+ * the library allocates no device memory.  All calls are asynchronous on the CUDA stream
+ * passed as `stream` (a cudaStream_t cast to void*; NULL = the legacy default stream) and
+ * return 0 or a negative VqStatus.  All tensors must live on the same CUDA device, which
+ * must be the calling thread's current device.
+ *
+ * Each function names the reference (LouChao98/vqtree) interface it replaces, by file:line.
+ */
+#ifndef VQATTN_H
+#define VQATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VQATTN_VERSION 100
+#define VQATTN_BLOCK 128   /* key/query block size; ops/attn_vq.py:23 BLOCK_SIZE ("MUST MATCH KERNEL") */
+#define VQATTN_MAX_DIMS 5
+
+typedef enum VqDtype {
+    VQ_F32 = 0,
+    VQ_BF16 = 1,
+    VQ_U8 = 2,
+    VQ_U16 = 3,
+    VQ_I32 = 4,
+    VQ_I64 = 5
+} VqDtype;
+
+typedef enum VqStatus {
+    VQ_OK = 0,
+    VQ_EINVAL_SHAPE = -1,   /* a shape disagrees with the others or breaks a documented constraint */
+    VQ_EINVAL_DTYPE = -2,   /* unsupported dtype or dtype combination */
+    VQ_EINVAL_STRIDE = -3,  /* innermost stride != 1, or a layout the kernels cannot address */
+    VQ_EDEVICE = -4,        /* tensors on different devices, or not on the current device */
+    VQ_ELAUNCH = -5,        /* the CUDA runtime rejected a launch or attribute call */
+    VQ_ETIMEOUT = -6,       /* a bounded device-side wait expired (reported through a status word) */
+    VQ_EINVAL_ARG = -7,     /* null pointer or bad scalar argument */
+    VQ_EUNSUPPORTED = -8,   /* valid request outside what the kernels cover (head dim, codebook size) */
+    VQ_EWORKSPACE = -9      /* workspace missing or too small */
+} VqStatus;
+
+/* Dense tensor view.  `stride` is in elements.  `device` is the CUDA ordinal. */
+typedef struct VqTensorDesc {
+    void *ptr;
+    int32_t dtype; /* VqDtype */
+    int32_t ndim;
+    int64_t shape[VQATTN_MAX_DIMS];
+    int64_t stride[VQATTN_MAX_DIMS];
+    int32_t device;
+} VqTensorDesc;
+
+/* Which prefill kernel to run; AUTO picks the tensor-core kernel for bf16 and the fp32 kernel for f32. */
+typedef enum VqPrefillImpl { VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2 } VqPrefillImpl;
+
+int vqattn_version(void);
+const char *vqattn_status_string(int status);
+
+/*
+ * Key -> code assignment.  Replaces ops/mini_vq.py:4-18 multi_head_single_quantize (scores by
+ * raw inner product, first arg-max) and generalises it to M codebooks by greedy residual
+ * assignment: r0 = k; c_m = argmax_c(r_m.C_m[c] + bias_m[c]); r_{m+1} = r_m - C_m[c_m].
+ * Arithmetic is fp32 with a fixed order (one fused-multiply-add chain over d = 0..D-1), so the
+ * codes are reproducible bit for bit.
+ *   k         [B,Hkv,L,D]  f32 | bf16      (D in {64,128})
+ *   codebooks [Hkv,M,K,D]  f32             (K % 64 == 0, K <= 65536)
+ *   bias      NULL or [Hkv,M,K] f32
+ *   codes     [B,Hkv,L,M]  u8 (K <= 256) | u16 | i32 | i64
+ */
+int vqattn_assign_codes(const VqTensorDesc *k, const VqTensorDesc *codebooks, const VqTensorDesc *bias_or_null,
+                        VqTensorDesc *codes, void *stream);
+
+/*
+ * Per-block aggregates.  Replaces the host preparation at ops/attn_vq.py:352-384,411-417 (one-hot
+ * cumsum, argsort, gather, prefix sums): block n of the outputs describes the keys [0,128(n+1)):
+ *   cnt  [B,Hkv,NB,M*K]    f32  number of those keys whose code in codebook m is c  (row m*K+c)
+ *   vsum [B,Hkv,NB,M*K,D]  f32 | bf16  sum of their value rows, accumulated in fp32 in position order
+ * from
+ *   codes [B,Hkv,L,M] u8|u16|i32|i64,  v [B,Hkv,L,D] f32|bf16,   NB <= L/128.
+ */
+int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
+                            VqTensorDesc *vsum, void *stream);
+
+/*
+ * Converts the reference's own aggregate format to the dense one above, for callers that already
+ * hold it (the arguments of ops/triton_fused_vq_attn.py:190 vq_attn_forward):
+ *   v_vq [B,H,L+1,D] f32|bf16 (sorted within-code prefix sums, ops/attn_vq.py:364-383)
+ *   vi   [B,H,NBin,C] i32|i64 (row of v_vq per block and code, ops/attn_vq.py:384,412-413)
+ *   ->   vsum [B,H,NB,C,D] (same dtype as v_vq), NB <= NBin
+ */
+int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensorDesc *vi, VqTensorDesc *vsum, void *stream);
+
+/*
+ * Fused prefill attention.  Replaces ops/triton_fused_vq_attn.py:190-251 vq_attn_forward, i.e. the
+ * far kernel (:88-187), the local ReRoPE window kernel (ops/triton_fused_local_attn_rerope.py:121-226)
+ * and the log-sum-exp merge (:246-250), as one kernel with a single online softmax.
+ * For query row i, with boundary = max(0, ((i - window)/128)*128):
+ *   keys j in [max(0,i-window), i]       scored q1_i.k1_j
+ *   keys j in [boundary, max(0,i-window)) scored q2_i.k3_j
+ *   keys j <  boundary                   through the aggregates of block boundary/128 - 1:
+ *       score q2_i.codebook[r] for every row r with cnt[r] > 0, numerator weight vsum[r],
+ *       denominator weight cnt[r]                         (ops/triton_fused_vq_attn.py:38-68)
+ * All of q1,q2,k1,k3,v,codebook,vsum,out share one dtype (f32 or bf16); math is fp32.
+ *   q1,q2,out [B,Hq,L,D]; k1,k3,v [B,Hkv,L,D]; codebook [Hkv,MK,D]; cnt [B,Hkv,NB,MK] f32;
+ *   vsum [B,Hkv,NB,MK,D]; lse2 NULL or [B,Hq,L] f32 (base-2 log-sum-exp of the scaled scores).
+ * Constraints: D in {64,128}; window % 128 == 0; MK % 128 == 0; Hq % Hkv == 0;
+ * NB >= L/128 - window/128 - 1 when that is positive (cnt/vsum may be NULL otherwise).
+ * codebook.ptr == NULL computes the local part only (the far keys are ignored), which is what
+ * ops/triton_fused_local_attn_rerope.py:287-294 flash_attn_func returns.
+ * q2 may alias q1 and k3 may alias k1 (plain-RoPE mode).
+ */
+typedef struct VqPrefillArgs {
+    VqTensorDesc q1, q2, k1, k3, v;
+    VqTensorDesc codebook, cnt, vsum;
+    VqTensorDesc out;
+    VqTensorDesc lse2;     /* ptr may be NULL */
+    int64_t window;
+    float scale;           /* <= 0: 1/sqrt(D) */
+    int32_t impl;          /* VqPrefillImpl */
+    int32_t *status_word;  /* device int32 or NULL: set non-zero by a kernel whose bounded wait expired */
+} VqPrefillArgs;
+
+int vqattn_prefill(const VqPrefillArgs *args, void *stream);
+
+/*
+ * Single-query decode over a cache (seqlen_q == 1).  The reference promises this kernel
+ * (README.md:8) but its cache update is unfinished (ops/attn_vq.py:128-165); the semantics are
+ * those of prefill row n-1 for a context of n tokens.  The cache holds the newest keys in
+ * k1_win/k3_win/v_win (entries [0,n_valid)); the first n_bd entries are scored q2.k3, the rest
+ * q1.k1; older keys are in cnt/vsum (skipped when use_far == 0).
+ *   q1,q2,out [B,Hq,D]; k1_win,k3_win,v_win [B,Hkv,Nwin,D]; codebook [Hkv,MK,D] (f32 or the
+ *   activation dtype); cnt [B,Hkv,MK] f32; vsum [B,Hkv,MK,D] (activation dtype).
+ * `workspace` must hold vqattn_decode_workspace_bytes(...) bytes and be zero-filled before its
+ * first use; the kernel leaves it ready for the next call on the same stream.
+ */
+typedef struct VqDecodeArgs {
+    VqTensorDesc q1, q2, k1_win, k3_win, v_win;
+    VqTensorDesc codebook, cnt, vsum;
+    VqTensorDesc out;
+    int64_t n_valid, n_bd;
+    int32_t use_far;
+    float scale;
+    void *workspace;
+    size_t workspace_bytes;
+} VqDecodeArgs;
+
+size_t vqattn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D);
+int vqattn_decode(const VqDecodeArgs *args, void *stream);
+
+/*
+ * Cache advance: folds `n_new` (a multiple of 128 is not required) keys that cross the boundary
+ * into the running aggregates of a decode cache.  Stands in for the unfinished
+ * ops/attn_vq.py:128-165 VectorQuantizedReRoPECache.update.
+ *   codes [B,Hkv,n_new,M] ; v_new [B,Hkv,n_new,D] ;
+ *   cnt [B,Hkv,MK] f32 (in/out) ; vsum_f32 [B,Hkv,MK,D] f32 master (in/out) ;
+ *   vsum_act NULL or [B,Hkv,MK,D] bf16 shadow refreshed for the touched rows.
+ */
+int vqattn_cache_advance(const VqTensorDesc *codes, const VqTensorDesc *v_new, int32_t K, VqTensorDesc *cnt,
+                         VqTensorDesc *vsum_f32, VqTensorDesc *vsum_act_or_null, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VQATTN_H */

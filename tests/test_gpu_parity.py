@@ -1,0 +1,252 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle and the golden vectors.
+
+Tolerances (stated by the task): codes bit-exact; outputs max-abs <= 2e-2 in bf16 and <= 1e-4 in
+fp32 against the naive oracle evaluated on the same (rounded) inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import vq_oracle as vo
+from tests.vq_cases import make_case, oracle_prefill
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
+
+
+@pytest.fixture(scope="module")
+def api():
+    assert torch.cuda.is_available(), "the gpu-marked tests need a CUDA device"
+    from vqtree_b200 import api as _api
+    return _api
+
+
+def dev(t):
+    return t.cuda() if t is not None else None
+
+
+# ----------------------------------------------------------------------------- assignment
+
+@pytest.mark.parametrize("B,Hkv,L,D,M,K,dtype,code_dtype", [
+    (1, 8, 1024, 64, 2, 256, torch.float32, torch.uint8),      # config 1 shape
+    (1, 8, 1024, 64, 1, 256, torch.float32, torch.int64),      # the reference's single-codebook case
+    (2, 3, 640, 128, 4, 256, torch.bfloat16, torch.uint8),
+    (1, 2, 333, 128, 4, 512, torch.bfloat16, torch.uint16),    # ragged length, 9-bit codes
+    (1, 2, 64, 64, 3, 64, torch.float32, torch.int32),
+])
+def test_assign_codes_bit_exact(api, B, Hkv, L, D, M, K, dtype, code_dtype):
+    g = torch.Generator().manual_seed(11 + L + K)
+    k = torch.randn(B, Hkv, L, D, generator=g).to(dtype)
+    cb = torch.randn(Hkv, M, K, D, generator=g) * D ** -0.25
+    want = vo.assign_codes(k.float().numpy(), cb.numpy())
+    got = api.assign_codes(dev(k), dev(cb), out_dtype=code_dtype)
+    assert got.dtype == code_dtype
+    np.testing.assert_array_equal(got.cpu().to(torch.int64).numpy(), want)
+
+
+def test_assign_codes_with_bias_and_strided_keys(api):
+    g = torch.Generator().manual_seed(5)
+    B, Hkv, L, D, M, K = 2, 2, 256, 64, 2, 128
+    kfull = torch.randn(B, L, Hkv, D, generator=g)           # [B,L,H,D] storage, viewed as [B,H,L,D]
+    k = kfull.transpose(1, 2)
+    cb = torch.randn(Hkv, M, K, D, generator=g) * 0.4
+    bias = -0.5 * (cb ** 2).sum(-1)                            # the L2 assignment rule
+    want = vo.assign_codes(k.contiguous().numpy(), cb.numpy(), bias.numpy())
+    got = api.assign_codes(dev(kfull).transpose(1, 2), dev(cb), dev(bias))
+    np.testing.assert_array_equal(got.cpu().to(torch.int64).numpy(), want)
+
+
+def test_assign_matches_reference_golden(api, golden_dir):
+    for name in ("assign_a.npz", "assign_b.npz"):
+        gd = np.load(golden_dir / name)
+        k, cb, ids = torch.from_numpy(gd["k"]), torch.from_numpy(gd["codebook"]), gd["ids"]
+        got = api.assign_codes(dev(k), dev(cb[:, None].contiguous())).cpu().to(torch.int64).numpy()[..., 0]
+        mism = got != ids
+        if mism.any():
+            margin, mx = vo.assign_margin(gd["k"], gd["codebook"][:, None], ids[..., None])
+            assert (np.abs(margin[..., 0])[mism] <= 2.0 ** -18 * mx[..., 0][mism]).all()
+        assert mism.mean() < 1e-3
+
+
+# ----------------------------------------------------------------------------- aggregates
+
+@pytest.mark.parametrize("D,M,K,dtype", [(64, 2, 256, torch.float32), (128, 4, 256, torch.bfloat16),
+                                         (128, 2, 512, torch.bfloat16), (64, 1, 128, torch.float32)])
+def test_build_aggregates(api, D, M, K, dtype):
+    B, Hkv, L = 2, 2, 768
+    g = torch.Generator().manual_seed(3 + K)
+    codes = torch.randint(0, K, (B, Hkv, L, M), generator=g)
+    v = torch.randn(B, Hkv, L, D, generator=g).to(dtype)
+    cnt_w, vsum_w = vo.build_aggregates(codes.numpy(), v.float().numpy(), K, NB=5)
+    cdt = torch.uint8 if K <= 256 else torch.uint16
+    cnt, vsum = api.build_aggregates(dev(codes.to(cdt)), dev(v), K, nb=5)
+    np.testing.assert_array_equal(cnt.cpu().numpy().reshape(cnt_w.shape), cnt_w.astype(np.float32))
+    want = vsum_w.reshape(B, Hkv, 5, M * K, D)
+    if dtype == torch.bfloat16:
+        want = vo.round_bf16(want)
+    np.testing.assert_array_equal(vsum.float().cpu().numpy(), want)  # same fp32 order -> bit-exact
+    # fp32 master copy from bf16 values
+    if dtype == torch.bfloat16:
+        _, vs32 = api.build_aggregates(dev(codes.to(cdt)), dev(v), K, nb=5, out_dtype=torch.float32)
+        np.testing.assert_array_equal(vs32.cpu().numpy(), vsum_w.reshape(B, Hkv, 5, M * K, D))
+
+
+def test_gather_aggregates_from_reference_format(api, golden_dir):
+    f = np.load(golden_dir / "fast_w128.npz")
+    v_vq, vi = torch.from_numpy(f["v_vq"]), torch.from_numpy(f["vi"]).to(torch.int64)
+    nb = vi.shape[2]
+    got = api.gather_aggregates(dev(v_vq), dev(vi), nb).cpu().numpy()
+    B, H = vi.shape[:2]
+    for b in range(B):
+        for h in range(H):
+            np.testing.assert_array_equal(got[b, h], f["v_vq"][b, h][f["vi"][b, h]])
+
+
+# ----------------------------------------------------------------------------- prefill
+
+def _run_prefill(api, case, impl):
+    d = {k: dev(t) if isinstance(t, torch.Tensor) else t for k, t in case.items()}
+    q2 = d["q1"] if case["q2"] is case["q1"] else d["q2"]
+    k3 = d["k1"] if case["k3"] is case["k1"] else d["k3"]
+    out, st = api.vq_attention_prefill(d["q1"], q2, d["k1"], k3, d["v"], d["cb"], case["W"], impl=impl, return_state=True)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy(), st
+
+
+PREFILL_CASES = [
+    # B, Hq, Hkv, L,   D,  M, K,   W,  seed, rerope, dtype
+    (1, 8, 8, 1024, 64, 2, 256, 128, 0, False, torch.float32),    # config 1
+    (1, 8, 8, 1024, 64, 1, 256, 128, 0, True, torch.float32),     # config 1 shape, reference-pinned M = 1, ReRoPE
+    (1, 4, 2, 896, 128, 2, 128, 256, 7, True, torch.float32),     # GQA, D = 128
+    (1, 2, 2, 700, 64, 1, 128, 128, 8, True, torch.float32),      # ragged tail (L % 128 != 0)
+    (1, 2, 2, 200, 64, 1, 128, 128, 9, True, torch.float32),      # shorter than window + 128: no far part
+    (1, 4, 4, 1024, 128, 4, 256, 256, 1, False, torch.bfloat16),  # config 2 shape, scaled down
+    (2, 4, 2, 1024, 128, 4, 512, 128, 3, True, torch.bfloat16),   # config 4 shape, scaled down, GQA
+    (1, 2, 2, 717, 64, 2, 128, 128, 4, True, torch.bfloat16),     # ragged, D = 64
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,L,D,M,K,W,seed,rerope,dtype", PREFILL_CASES)
+@pytest.mark.parametrize("impl", ["simt", "tensor"])
+def test_prefill_matches_naive_oracle(api, impl, B, Hq, Hkv, L, D, M, K, W, seed, rerope, dtype):
+    if impl == "tensor" and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core kernel computes in bf16")
+    case = make_case(B, Hq, Hkv, L, D, M, K, W, seed, rerope, dtype)
+    want, codes = oracle_prefill(case)
+    got, st = _run_prefill(api, case, impl)
+    if st["codes"] is not None:
+        np.testing.assert_array_equal(st["codes"].cpu().to(torch.int64).numpy(), codes)
+    err = np.abs(got - want).max()
+    assert np.isfinite(got).all()
+    assert err <= TOL[dtype], f"max-abs error {err}"
+
+
+def test_prefill_matches_reference_golden_output(api, golden_dir):
+    """The reference's own naive loop and fast path (fp32, M = 1) on its inputs."""
+    gd = np.load(golden_dir / "naive_w128.npz")
+    W = int(gd["window"])
+    q, k, v, cb = (torch.from_numpy(gd[n]) for n in ("q", "k", "v", "codebook"))
+    L, D = q.shape[2], q.shape[3]
+    cos, sin = vo.rope_tables(max(L, W + 2), D)
+    pos = np.arange(L)
+    q1 = torch.from_numpy(vo.apply_rope(q.numpy(), cos, sin, pos))
+    k1 = torch.from_numpy(vo.apply_rope(k.numpy(), cos, sin, pos))
+    q2 = torch.from_numpy(vo.apply_rope(q.numpy(), cos, sin, np.full(L, W + 1)))
+    out = api.vq_attention_prefill(dev(q1), dev(q2), dev(k1), dev(k), dev(v), dev(cb[:, None].contiguous()), W)
+    np.testing.assert_allclose(out.cpu().numpy(), gd["out"], atol=1e-4, rtol=0)
+    fast = np.load(golden_dir / "fast_w128.npz")
+    np.testing.assert_allclose(out.cpu().numpy(), fast["out"], atol=1e-4, rtol=0)
+
+
+def test_prefill_lse_and_local_only(api, golden_dir):
+    f = np.load(golden_dir / "fast_w128.npz")
+    gd = np.load(golden_dir / "naive_w128.npz")
+    W = int(gd["window"])
+    q1, q2, k1 = (dev(torch.from_numpy(f[n])) for n in ("q1", "q2", "k1"))
+    k3, v = dev(torch.from_numpy(gd["k"])), dev(torch.from_numpy(gd["v"]))
+    out, lse = api.prefill_from_aggregates(q1, q2, k1, k3, v, None, None, None, W, return_lse=True)
+    np.testing.assert_allclose(out.cpu().numpy(), f["o_local"], atol=1e-4, rtol=0)
+    np.testing.assert_allclose(lse.cpu().numpy(), f["lse_local"], atol=1e-3, rtol=0)
+
+
+# ----------------------------------------------------------------------------- decode
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,M,K,W,dtype,cb_f32", [
+    (2, 4, 4, 128, 2, 128, 256, torch.bfloat16, True),
+    (2, 8, 2, 128, 2, 128, 128, torch.bfloat16, False),   # GQA group of 4
+    (1, 6, 2, 64, 1, 128, 128, torch.float32, True),      # group of 3 -> one head per CTA
+    (3, 2, 1, 64, 2, 256, 128, torch.bfloat16, True),
+])
+def test_decode_matches_oracle_and_prefill_row(api, B, Hq, Hkv, D, M, K, W, dtype, cb_f32):
+    L = 1024
+    case = make_case(B, Hq, Hkv, L, D, M, K, W, 21, True, dtype)
+    f = lambda t: t.float().numpy()
+    cb = case["cb"].numpy()
+    codes = vo.assign_codes(f(case["k3"]), cb)
+    cnt, vsum = vo.build_aggregates(codes, f(case["v"]), K)
+    cb_o = cb if (cb_f32 or dtype == torch.float32) else vo.round_bf16(cb)
+    full = vo.attn_naive(f(case["q1"]), f(case["q2"]), f(case["k1"]), f(case["k3"]), f(case["v"]), cb_o, codes, W)
+    ws = api.decode_workspace(B, Hq, Hkv, D, "cuda")
+    for n in (W // 2, W + 130, 777, L):
+        i = n - 1
+        bd = max(0, (i - W) // 128 * 128)
+        lb = max(0, i - W)
+        far = bd > 0
+        blk = bd // 128 - 1 if far else 0
+        cnt_n = torch.from_numpy(cnt[:, :, blk].reshape(B, Hkv, M * K).astype(np.float32))
+        vs_n = torch.from_numpy(vsum[:, :, blk].reshape(B, Hkv, M * K, D))
+        vs_n = vs_n.to(dtype)
+        cbk = torch.from_numpy(cb.reshape(Hkv, M * K, D))
+        cbk = cbk if (cb_f32 or dtype == torch.float32) else cbk.to(dtype)
+        # window buffers with slack rows beyond n_valid
+        Nwin = W + 128 + 8
+        def win(t):
+            w = torch.zeros(B, Hkv, Nwin, D, dtype=dtype)
+            w[:, :, : n - bd] = t[:, :, bd:n]
+            return dev(w)
+        got = api.vq_attention_decode(dev(case["q1"][:, :, i].contiguous()), dev(case["q2"][:, :, i].contiguous()),
+                                      win(case["k1"]), win(case["k3"]), win(case["v"]),
+                                      dev(cbk) if far else None, dev(cnt_n) if far else None, dev(vs_n) if far else None,
+                                      n_valid=n - bd, n_bd=lb - bd, workspace=ws)
+        want = vo.decode(f(case["q1"][:, :, i]), f(case["q2"][:, :, i]), f(case["k1"][:, :, bd:n]), f(case["k3"][:, :, bd:n]),
+                         f(case["v"][:, :, bd:n]), cb_o, cnt[:, :, blk], f(vs_n).reshape(B, Hkv, M, K, D),
+                         n - bd, lb - bd, use_far=far)
+        tol = TOL[dtype]
+        np.testing.assert_allclose(got.float().cpu().numpy(), want, atol=tol, rtol=0)
+        np.testing.assert_allclose(got.float().cpu().numpy(), full[:, :, i], atol=tol, rtol=0)
+
+
+def test_cache_advance(api):
+    B, Hkv, D, M, K, n_new = 2, 2, 128, 2, 128, 128
+    g = torch.Generator().manual_seed(31)
+    codes0 = torch.randint(0, K, (B, Hkv, 256, M), generator=g)
+    v0 = torch.randn(B, Hkv, 256, D, generator=g).bfloat16()
+    cnt_w, vsum_w = vo.build_aggregates(codes0.numpy(), v0.float().numpy(), K, NB=2)
+    cnt = dev(torch.from_numpy(cnt_w[:, :, 0].reshape(B, Hkv, M * K).astype(np.float32)))
+    vs32 = dev(torch.from_numpy(vsum_w[:, :, 0].reshape(B, Hkv, M * K, D)))
+    shadow = vs32.bfloat16()
+    api.cache_advance(dev(codes0[:, :, 128:].to(torch.uint8).contiguous()), dev(v0[:, :, 128:].contiguous()), K, cnt, vs32, shadow)
+    np.testing.assert_array_equal(cnt.cpu().numpy(), cnt_w[:, :, 1].reshape(B, Hkv, M * K).astype(np.float32))
+    np.testing.assert_array_equal(vs32.cpu().numpy(), vsum_w[:, :, 1].reshape(B, Hkv, M * K, D))
+    np.testing.assert_array_equal(shadow.float().cpu().numpy(), vo.round_bf16(vsum_w[:, :, 1].reshape(B, Hkv, M * K, D)))
+
+
+# ----------------------------------------------------------------------------- error behaviour on the device
+
+def test_errors_are_reported_not_crashed(api):
+    from vqtree_b200.native import VqError
+    k = torch.zeros(1, 2, 128, 64, device="cuda")
+    with pytest.raises(VqError) as e:
+        api.assign_codes(k, torch.zeros(2, 1, 100, 64, device="cuda"))      # K % 64 != 0
+    assert e.value.status == -8
+    with pytest.raises(VqError) as e:
+        api.assign_codes(k, torch.zeros(3, 1, 128, 64, device="cuda"))      # head count mismatch
+    assert e.value.status == -1
+    with pytest.raises(VqError) as e:
+        api.assign_codes(k, torch.zeros(2, 1, 512, 64, device="cuda"), out_dtype=torch.uint8)  # 9-bit codes into uint8
+    assert e.value.status == -2
+    q = torch.zeros(1, 2, 256, 64, device="cuda")
+    with pytest.raises(VqError) as e:
+        api.prefill_from_aggregates(q, q, q, q, q, None, None, None, window=100)  # window % 128 != 0
+    assert e.value.status == -7

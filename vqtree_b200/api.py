@@ -1,0 +1,217 @@
+"""Tensor-level entry points of the fused VQ-attention path (thin wrappers over the C ABI).
+
+Every function here allocates its outputs with torch, fills C descriptors and calls
+``libvqattn.so`` on the current CUDA stream of the tensors' device.  No arithmetic of the path
+is done in Python or by torch operators.  Host (CPU) tensors are accepted by the ``*_host``
+helpers, which stage them through pinned memory to the device and bring the result back.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import native
+from .native import BLOCK, VqDecodeArgs, VqPrefillArgs, check, desc, lib, stream_ptr
+
+_IMPL = {"auto": native.IMPL_AUTO, "simt": native.IMPL_SIMT, "tensor": native.IMPL_TENSOR}
+
+
+def _require_cuda(*ts):
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("expected CUDA tensors (use the *_host helpers for CPU tensors)")
+        dev = dev or t.device
+        if t.device != dev:
+            raise ValueError("all tensors must be on the same device")
+    return dev
+
+
+def code_dtype_for(K: int) -> torch.dtype:
+    """uint8 when a code fits (K <= 256), else uint16."""
+    return torch.uint8 if K <= 256 else torch.uint16
+
+
+def assign_codes(k: torch.Tensor, codebooks: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Key -> code assignment (replaces ops/mini_vq.py:4-18; greedy residual for M > 1).
+
+    k [B,Hkv,L,D] f32|bf16, codebooks [Hkv,M,K,D] f32, bias None|[Hkv,M,K] f32 -> codes [B,Hkv,L,M].
+    """
+    dev = _require_cuda(k, codebooks, bias)
+    B, Hkv, L, _ = k.shape
+    M, K = codebooks.shape[1], codebooks.shape[2]
+    codes = torch.empty((B, Hkv, L, M), dtype=out_dtype or code_dtype_for(K), device=dev)
+    with torch.cuda.device(dev):
+        dk, dc, db, do = desc(k), desc(codebooks), desc(bias), desc(codes)
+        check(lib.vqattn_assign_codes(dk, dc, db if bias is not None else None, do, stream_ptr(dev)), "vqattn_assign_codes")
+    return codes
+
+
+def far_blocks(L: int, window: int) -> int:
+    """Number of aggregate blocks a prefill of length L reads (0 when the far set is empty)."""
+    return max(0, (L + BLOCK - 1) // BLOCK - window // BLOCK - 1)
+
+
+def build_aggregates(codes: torch.Tensor, v: torch.Tensor, K: int, nb: Optional[int] = None,
+                     out_dtype: Optional[torch.dtype] = None):
+    """Per-block counts and value sums (replaces ops/attn_vq.py:352-384,411-417).
+
+    codes [B,Hkv,L,M], v [B,Hkv,L,D] -> cnt [B,Hkv,NB,M*K] f32, vsum [B,Hkv,NB,M*K,D] (v's dtype).
+    """
+    dev = _require_cuda(codes, v)
+    B, Hkv, L, M = codes.shape
+    D = v.shape[-1]
+    nb = L // BLOCK if nb is None else nb
+    cnt = torch.empty((B, Hkv, nb, M * K), dtype=torch.float32, device=dev)
+    vsum = torch.empty((B, Hkv, nb, M * K, D), dtype=out_dtype or v.dtype, device=dev)
+    if nb > 0:
+        with torch.cuda.device(dev):
+            check(lib.vqattn_build_aggregates(desc(codes), desc(v), K, desc(cnt), desc(vsum), stream_ptr(dev)),
+                  "vqattn_build_aggregates")
+    return cnt, vsum
+
+
+def gather_aggregates(v_vq: torch.Tensor, vi: torch.Tensor, nb: int) -> torch.Tensor:
+    """Dense value sums from the reference's sorted-prefix format (v_vq [B,H,L+1,D], vi [B,H,NB,C])."""
+    dev = _require_cuda(v_vq, vi)
+    B, H, _, D = v_vq.shape
+    C = vi.shape[-1]
+    if vi.dtype not in (torch.int32, torch.int64):
+        vi = vi.to(torch.int64)
+    vsum = torch.empty((B, H, nb, C, D), dtype=v_vq.dtype, device=dev)
+    if nb > 0:
+        with torch.cuda.device(dev):
+            check(lib.vqattn_gather_aggregates(desc(v_vq), desc(vi), desc(vsum), stream_ptr(dev)), "vqattn_gather_aggregates")
+    return vsum
+
+
+def prefill_from_aggregates(q1, q2, k1, k3, v, codebook_act, cnt, vsum, window: int, scale: Optional[float] = None,
+                            impl: str = "auto", return_lse: bool = False, status_word: Optional[torch.Tensor] = None):
+    """Fused prefill attention from ready aggregates (replaces ops/triton_fused_vq_attn.py:190-251).
+
+    codebook_act [Hkv,MK,D] in the activation dtype (None: local part only).
+    """
+    dev = _require_cuda(q1, q2, k1, k3, v, codebook_act, cnt, vsum)
+    B, Hq, L, D = q1.shape
+    out = torch.empty((B, Hq, L, D), dtype=q1.dtype, device=dev)
+    lse = torch.empty((B, Hq, L), dtype=torch.float32, device=dev) if return_lse else None
+    a = VqPrefillArgs()
+    a.q1, a.q2, a.k1, a.k3, a.v = desc(q1), desc(q2), desc(k1), desc(k3), desc(v)
+    a.codebook, a.cnt, a.vsum = desc(codebook_act), desc(cnt), desc(vsum)
+    a.out, a.lse2 = desc(out), desc(lse)
+    a.window = int(window)
+    a.scale = float(scale) if scale else 0.0
+    a.impl = _IMPL[impl]
+    a.status_word = status_word.data_ptr() if status_word is not None else None
+    with torch.cuda.device(dev):
+        check(lib.vqattn_prefill(ctypes.byref(a), stream_ptr(dev)), "vqattn_prefill")
+    return (out, lse) if return_lse else out
+
+
+def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window: int, scale: Optional[float] = None,
+                         bias: Optional[torch.Tensor] = None, impl: str = "auto", return_state: bool = False):
+    """The whole prefill path: assign codes to k3, build aggregates of v, fused attention.
+
+    q1,q2 [B,Hq,L,D]; k1,k3,v [B,Hkv,L,D] (f32 or bf16); codebooks [Hkv,M,K,D] f32.
+    ReRoPE mode: q1,k1 rotated by position, q2 rotated to the constant position window+1, k3 un-rotated
+    (ops/attn_vq.py:402-407).  Plain-RoPE mode: pass q2 = q1 and k3 = k1.
+    """
+    B, Hq, L, D = q1.shape
+    Hkv, M, K, _ = codebooks.shape
+    nb = far_blocks(L, window)
+    codes = cnt = vsum = cb_act = None
+    if nb > 0 or return_state:
+        codes = assign_codes(k3, codebooks, bias)
+    if nb > 0:
+        cnt, vsum = build_aggregates(codes, v, K, nb)
+        cb_act = codebooks.reshape(Hkv, M * K, D).to(q1.dtype)
+    out = prefill_from_aggregates(q1, q2, k1, k3, v, cb_act, cnt, vsum, window, scale, impl)
+    if return_state:
+        return out, dict(codes=codes, cnt=cnt, vsum=vsum)
+    return out
+
+
+def decode_workspace(B: int, Hq: int, Hkv: int, D: int, device) -> torch.Tensor:
+    """Zero-filled workspace for vq_attention_decode; reusable across calls on one stream."""
+    n = lib.vqattn_decode_workspace_bytes(B, Hq, Hkv, D)
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def vq_attention_decode(q1, q2, k1_win, k3_win, v_win, codebook, cnt, vsum, n_valid: Optional[int] = None, n_bd: int = 0,
+                        scale: Optional[float] = None, workspace: Optional[torch.Tensor] = None,
+                        out: Optional[torch.Tensor] = None):
+    """Single-query decode (seqlen_q == 1) over a window cache plus far aggregates.
+
+    q1,q2 [B,Hq,D]; k1_win,k3_win,v_win [B,Hkv,Nwin,D]; codebook [Hkv,MK,D] (f32 or activation dtype) or None;
+    cnt [B,Hkv,MK] f32; vsum [B,Hkv,MK,D].
+    """
+    dev = _require_cuda(q1, q2, k1_win, k3_win, v_win, codebook, cnt, vsum)
+    B, Hq, D = q1.shape
+    Hkv, Nwin = k1_win.shape[1], k1_win.shape[2]
+    if workspace is None:
+        workspace = decode_workspace(B, Hq, Hkv, D, dev)
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=q1.dtype, device=dev)
+    a = VqDecodeArgs()
+    a.q1, a.q2, a.k1_win, a.k3_win, a.v_win = desc(q1), desc(q2), desc(k1_win), desc(k3_win), desc(v_win)
+    a.codebook, a.cnt, a.vsum, a.out = desc(codebook), desc(cnt), desc(vsum), desc(out)
+    a.n_valid = Nwin if n_valid is None else int(n_valid)
+    a.n_bd = int(n_bd)
+    a.use_far = 1 if codebook is not None else 0
+    a.scale = float(scale) if scale else 0.0
+    a.workspace = workspace.data_ptr()
+    a.workspace_bytes = workspace.numel() * workspace.element_size()
+    with torch.cuda.device(dev):
+        check(lib.vqattn_decode(ctypes.byref(a), stream_ptr(dev)), "vqattn_decode")
+    return out
+
+
+def cache_advance(codes, v_new, K: int, cnt, vsum_f32, vsum_act=None):
+    """Fold keys that crossed the boundary into a decode cache's aggregates (in place)."""
+    dev = _require_cuda(codes, v_new, cnt, vsum_f32, vsum_act)
+    with torch.cuda.device(dev):
+        check(lib.vqattn_cache_advance(desc(codes), desc(v_new), K, desc(cnt), desc(vsum_f32),
+                                       desc(vsum_act) if vsum_act is not None else None, stream_ptr(dev)),
+              "vqattn_cache_advance")
+
+
+# ---------------------------------------------------------------------------------------------
+# Host-buffer entry points: CPU tensors in, CPU tensor out, copies included.
+
+def _to_device(t, dev):
+    if t is None:
+        return None
+    if not t.is_pinned():
+        t = t.pin_memory()
+    return t.to(dev, non_blocking=True)
+
+
+def vq_attention_prefill_host(q1, q2, k1, k3, v, codebooks, window: int, scale: Optional[float] = None,
+                              device="cuda:0", impl: str = "auto", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """vq_attention_prefill for host tensors: host->device copies, the three kernels, device->host copy.
+
+    q2 / k3 may be the same objects as q1 / k1 (plain-RoPE mode): they are then copied once.
+    """
+    dev = torch.device(device)
+    dq1 = _to_device(q1, dev)
+    dq2 = dq1 if q2 is q1 else _to_device(q2, dev)
+    dk1 = _to_device(k1, dev)
+    dk3 = dk1 if k3 is k1 else _to_device(k3, dev)
+    dv = _to_device(v, dev)
+    dcb = codebooks if codebooks.is_cuda else _to_device(codebooks, dev)
+    res = vq_attention_prefill(dq1, dq2, dk1, dk3, dv, dcb, window, scale, impl=impl)
+    if out is None:
+        out = torch.empty(res.shape, dtype=res.dtype, pin_memory=True)
+    out.copy_(res, non_blocking=True)
+    torch.cuda.current_stream(dev).synchronize()
+    return out
+
+
+def default_scale(D: int) -> float:
+    return 1.0 / math.sqrt(D)

@@ -1,0 +1,281 @@
+// Per-block aggregates of the quantised keys: replaces the host preparation of the reference
+// (ops/attn_vq.py:352-384,411-417: one-hot cumsum over [B,H,L,C], argsort, gather, prefix sums).
+//
+// For every 128-key block n the outputs describe the keys [0, 128(n+1)):
+//   cnt[n][r]  = number of keys whose code in codebook m is c   (r = m*K + c)
+//   vsum[n][r] = sum of their value rows, fp32, added in position order, stored in the output dtype.
+// One CTA owns (batch*kv-head, codebook m, a part of <= 256 codes, a 64-column slice of D), keeps
+// the running fp32 sums of its rows in shared memory, walks the blocks in order and writes a
+// snapshot after each.  A row is always updated by the same thread in position order, so the
+// sums are deterministic and equal a scalar left-to-right loop.
+#include "vq_common.cuh"
+
+namespace vq {
+
+constexpr int kAggThreads = 256;
+constexpr int kAggCols = 64;    // D-slice per CTA
+constexpr int kAggRows = 256;   // code rows per CTA
+
+template <typename T> __device__ __forceinline__ float4 ld4(const T *p);
+template <> __device__ __forceinline__ float4 ld4<float>(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+template <> __device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16 *p)
+{
+    uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162 *>(&raw.x);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162 *>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void st4(T *p, float4 x);
+template <> __device__ __forceinline__ void st4<float>(float *p, float4 x) { *reinterpret_cast<float4 *>(p) = x; }
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16 *p, float4 x)
+{
+    __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y);
+    __nv_bfloat162 b = __floats2bfloat162_rn(x.z, x.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t *>(&a);
+    raw.y = *reinterpret_cast<uint32_t *>(&b);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+
+template <typename TV, typename TO>
+__global__ void __launch_bounds__(kAggThreads)
+build_aggregates_kernel(const void *__restrict__ codes, int code_dtype, int64_t c_sb, int64_t c_sh, int64_t c_sl,
+                        const TV *__restrict__ v, int64_t v_sb, int64_t v_sh, int64_t v_sl,
+                        float *__restrict__ cnt,  // [B,Hkv,NB,MK] dense
+                        TO *__restrict__ vsum,    // [B,Hkv,NB,MK,D] dense
+                        int Hkv, int D, int M, int K, int NB, int parts, int rows_per_part)
+{
+    extern __shared__ __align__(16) float smem[];
+    float *acc = smem;                               // [rows_per_part][64]
+    float *vt = smem + rows_per_part * kAggCols;     // [128][64]
+    __shared__ int s_code[kBlock];
+    __shared__ int s_cnt[kAggRows];
+
+    const int tid = threadIdx.x;
+    const int slices = D / kAggCols;
+    int bx = blockIdx.x;
+    const int ds = bx % slices; bx /= slices;
+    const int kp = bx % parts;  bx /= parts;
+    const int m = bx % M;
+    const int u = blockIdx.y;
+    const int b = u / Hkv, h = u % Hkv;
+    const int MK = M * K;
+    const int row0 = kp * rows_per_part;  // first code of this part (within codebook m)
+
+    for (int i = tid; i < rows_per_part * kAggCols; i += kAggThreads) acc[i] = 0.f;
+    for (int i = tid; i < kAggRows; i += kAggThreads) s_cnt[i] = 0;
+    __syncthreads();
+
+    const int col = tid & (kAggCols - 1);
+    const int grp = tid / kAggCols;  // 4 groups; group g owns rows with (row & 3) == g
+
+    for (int n = 0; n < NB; ++n) {
+        const int64_t j0 = static_cast<int64_t>(n) * kBlock;
+        if (tid < kBlock) {
+            const int code = load_code(codes, code_dtype, b * c_sb + h * c_sh + (j0 + tid) * c_sl + m);
+            const int local = code - row0;
+            const bool mine = local >= 0 && local < rows_per_part;
+            s_code[tid] = mine ? local : -1;
+            if (mine) atomicAdd(&s_cnt[local], 1);
+        }
+        // value tile [128][64] -> fp32
+        for (int i = tid; i < kBlock * (kAggCols / 4); i += kAggThreads) {
+            const int r = i / (kAggCols / 4), c4 = i % (kAggCols / 4);
+            const float4 x = ld4<TV>(v + b * v_sb + h * v_sh + (j0 + r) * v_sl + ds * kAggCols + 4 * c4);
+            *reinterpret_cast<float4 *>(vt + r * kAggCols + 4 * c4) = x;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = 0; j < kBlock; ++j) {
+            const int lc = s_code[j];
+            if (lc >= 0 && (lc & 3) == grp) acc[lc * kAggCols + col] = __fadd_rn(acc[lc * kAggCols + col], vt[j * kAggCols + col]);
+        }
+        __syncthreads();
+        const int64_t out_row0 = (static_cast<int64_t>(u) * NB + n) * MK + m * K + row0;
+        for (int i = tid; i < rows_per_part * (kAggCols / 4); i += kAggThreads) {
+            const int r = i / (kAggCols / 4), c4 = i % (kAggCols / 4);
+            const float4 x = *reinterpret_cast<const float4 *>(acc + r * kAggCols + 4 * c4);
+            st4<TO>(vsum + (out_row0 + r) * D + ds * kAggCols + 4 * c4, x);
+        }
+        if (ds == 0)
+            for (int i = tid; i < rows_per_part; i += kAggThreads) cnt[out_row0 + i] = static_cast<float>(s_cnt[i]);
+        // s_code / vt are rewritten only after the next iteration's loads, which follow this
+        // barrier-separated read phase: one more barrier keeps slow readers of vt safe.
+        __syncthreads();
+    }
+}
+
+template <typename T>
+__global__ void gather_aggregates_kernel(const T *__restrict__ v_vq, int64_t s_b, int64_t s_h, int64_t s_n,
+                                         const void *__restrict__ vi, int vi_dtype, int64_t i_b, int64_t i_h, int64_t i_n,
+                                         T *__restrict__ vsum, int H, int NB, int C, int D, int64_t rows_in)
+{
+    // one warp per output row
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    const int lane = threadIdx.x & 31;
+    const int u = blockIdx.y;
+    if (row >= static_cast<int64_t>(NB) * C) return;
+    const int n = static_cast<int>(row / C), c = static_cast<int>(row % C);
+    const int b = u / H, h = u % H;
+    const int64_t at = b * i_b + h * i_h + n * i_n + c;
+    const int64_t src = vi_dtype == VQ_I64 ? static_cast<const int64_t *>(vi)[at] : static_cast<const int32_t *>(vi)[at];
+    T *dst = vsum + ((static_cast<int64_t>(u) * NB + n) * C + c) * D;
+    const bool ok = src >= 0 && src < rows_in;
+    const T *s = v_vq + b * s_b + h * s_h + (ok ? src : 0) * s_n;
+    for (int d = lane; d < D; d += 32) dst[d] = ok ? s[d] : from_f32<T>(0.f);
+}
+
+template <typename TV>
+__global__ void cache_advance_kernel(const void *__restrict__ codes, int code_dtype, int64_t c_sb, int64_t c_sh, int64_t c_sl,
+                                     const TV *__restrict__ v, int64_t v_sb, int64_t v_sh, int64_t v_sl,
+                                     float *__restrict__ cnt, float *__restrict__ vsum, __nv_bfloat16 *__restrict__ shadow,
+                                     int Hkv, int D, int M, int K, int n_new)
+{
+    const int u = blockIdx.y, m = blockIdx.x;
+    const int b = u / Hkv, h = u % Hkv;
+    const int64_t MK = static_cast<int64_t>(M) * K;
+    const int d = threadIdx.x;
+    for (int j = 0; j < n_new; ++j) {
+        const int code = load_code(codes, code_dtype, b * c_sb + h * c_sh + j * c_sl + m);
+        const int64_t row = static_cast<int64_t>(u) * MK + m * K + code;
+        if (d < D) {
+            const float s = __fadd_rn(vsum[row * D + d], to_f32(v[b * v_sb + h * v_sh + j * v_sl + d]));
+            vsum[row * D + d] = s;
+            if (shadow) shadow[row * D + d] = __float2bfloat16_rn(s);
+        }
+        if (d == 0) cnt[row] += 1.f;
+    }
+}
+
+}  // namespace vq
+
+extern "C" int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
+                                       VqTensorDesc *vsum, void *stream)
+{
+    using namespace vq;
+    int st;
+    if ((st = check_basic(codes, 4)) != VQ_OK) return st;
+    if ((st = check_basic(v, 4)) != VQ_OK) return st;
+    if ((st = check_basic(cnt, 4)) != VQ_OK) return st;
+    if ((st = check_basic(vsum, 5)) != VQ_OK) return st;
+    const VqTensorDesc *all[] = {codes, v, cnt, vsum};
+    if ((st = check_device(all, 4)) != VQ_OK) return st;
+    if (!is_code_dtype(codes->dtype) || !is_act_dtype(v->dtype) || cnt->dtype != VQ_F32 || !is_act_dtype(vsum->dtype))
+        return VQ_EINVAL_DTYPE;
+    const int64_t B = codes->shape[0], Hkv = codes->shape[1], L = codes->shape[2], M = codes->shape[3];
+    const int64_t D = v->shape[3], NB = cnt->shape[2], MK = cnt->shape[3];
+    if (K <= 0 || MK != M * K) return VQ_EINVAL_SHAPE;
+    if (v->shape[0] != B || v->shape[1] != Hkv || v->shape[2] != L) return VQ_EINVAL_SHAPE;
+    if (cnt->shape[0] != B || cnt->shape[1] != Hkv) return VQ_EINVAL_SHAPE;
+    if (vsum->shape[0] != B || vsum->shape[1] != Hkv || vsum->shape[2] != NB || vsum->shape[3] != MK || vsum->shape[4] != D)
+        return VQ_EINVAL_SHAPE;
+    if (NB * kBlock > L) return VQ_EINVAL_SHAPE;
+    if (!is_dense(*cnt) || !is_dense(*vsum)) return VQ_EINVAL_STRIDE;
+    if (D % kAggCols != 0 || D > 256) return VQ_EUNSUPPORTED;
+    if (v->stride[0] % 4 || v->stride[1] % 4 || v->stride[2] % 4 || reinterpret_cast<uintptr_t>(v->ptr) % 16) return VQ_EINVAL_STRIDE;
+    if (reinterpret_cast<uintptr_t>(vsum->ptr) % 16) return VQ_EINVAL_STRIDE;
+    if (B * Hkv > 65535) return VQ_EUNSUPPORTED;
+    int rows = static_cast<int>(K < kAggRows ? K : kAggRows);
+    if (K % rows != 0) return VQ_EUNSUPPORTED;
+    const int parts = static_cast<int>(K / rows);
+    const size_t smem = sizeof(float) * (static_cast<size_t>(rows) * kAggCols + kBlock * kAggCols);
+    dim3 grid(static_cast<unsigned>(M * parts * (D / kAggCols)), static_cast<unsigned>(B * Hkv));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define VQ_LAUNCH_AGG(TV, TO)                                                                                          \
+    do {                                                                                                               \
+        auto kern = build_aggregates_kernel<TV, TO>;                                                                   \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=        \
+            cudaSuccess)                                                                                               \
+            return VQ_ELAUNCH;                                                                                         \
+        kern<<<grid, kAggThreads, smem, s>>>(codes->ptr, codes->dtype, codes->stride[0], codes->stride[1],            \
+                                             codes->stride[2], static_cast<const TV *>(v->ptr), v->stride[0],         \
+                                             v->stride[1], v->stride[2], static_cast<float *>(cnt->ptr),              \
+                                             static_cast<TO *>(vsum->ptr), static_cast<int>(Hkv), static_cast<int>(D), \
+                                             static_cast<int>(M), static_cast<int>(K), static_cast<int>(NB), parts, rows); \
+    } while (0)
+    if (v->dtype == VQ_F32 && vsum->dtype == VQ_F32) VQ_LAUNCH_AGG(float, float);
+    else if (v->dtype == VQ_F32) VQ_LAUNCH_AGG(float, __nv_bfloat16);
+    else if (vsum->dtype == VQ_F32) VQ_LAUNCH_AGG(__nv_bfloat16, float);
+    else VQ_LAUNCH_AGG(__nv_bfloat16, __nv_bfloat16);
+#undef VQ_LAUNCH_AGG
+    return launch_status();
+}
+
+extern "C" int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensorDesc *vi, VqTensorDesc *vsum, void *stream)
+{
+    using namespace vq;
+    int st;
+    if ((st = check_basic(v_vq, 4)) != VQ_OK) return st;
+    if ((st = check_basic(vi, 4)) != VQ_OK) return st;
+    if ((st = check_basic(vsum, 5)) != VQ_OK) return st;
+    const VqTensorDesc *all[] = {v_vq, vi, vsum};
+    if ((st = check_device(all, 3)) != VQ_OK) return st;
+    if (!is_act_dtype(v_vq->dtype) || vsum->dtype != v_vq->dtype) return VQ_EINVAL_DTYPE;
+    if (vi->dtype != VQ_I32 && vi->dtype != VQ_I64) return VQ_EINVAL_DTYPE;
+    const int64_t B = v_vq->shape[0], H = v_vq->shape[1], D = v_vq->shape[3];
+    const int64_t NB = vsum->shape[2], C = vsum->shape[3];
+    if (vi->shape[0] != B || vi->shape[1] != H || vi->shape[2] < NB || vi->shape[3] != C) return VQ_EINVAL_SHAPE;
+    if (vsum->shape[0] != B || vsum->shape[1] != H || vsum->shape[4] != D) return VQ_EINVAL_SHAPE;
+    if (!is_dense(*vsum)) return VQ_EINVAL_STRIDE;
+    if (B * H > 65535) return VQ_EUNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int warps = 8;
+    dim3 grid(static_cast<unsigned>((NB * C + warps - 1) / warps), static_cast<unsigned>(B * H));
+    if (v_vq->dtype == VQ_F32)
+        gather_aggregates_kernel<float><<<grid, warps * 32, 0, s>>>(
+            static_cast<const float *>(v_vq->ptr), v_vq->stride[0], v_vq->stride[1], v_vq->stride[2], vi->ptr, vi->dtype,
+            vi->stride[0], vi->stride[1], vi->stride[2], static_cast<float *>(vsum->ptr), static_cast<int>(H),
+            static_cast<int>(NB), static_cast<int>(C), static_cast<int>(D), v_vq->shape[2]);
+    else
+        gather_aggregates_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
+            static_cast<const __nv_bfloat16 *>(v_vq->ptr), v_vq->stride[0], v_vq->stride[1], v_vq->stride[2], vi->ptr,
+            vi->dtype, vi->stride[0], vi->stride[1], vi->stride[2], static_cast<__nv_bfloat16 *>(vsum->ptr),
+            static_cast<int>(H), static_cast<int>(NB), static_cast<int>(C), static_cast<int>(D), v_vq->shape[2]);
+    return launch_status();
+}
+
+extern "C" int vqattn_cache_advance(const VqTensorDesc *codes, const VqTensorDesc *v_new, int32_t K, VqTensorDesc *cnt,
+                                    VqTensorDesc *vsum_f32, VqTensorDesc *vsum_act, void *stream)
+{
+    using namespace vq;
+    int st;
+    if ((st = check_basic(codes, 4)) != VQ_OK) return st;
+    if ((st = check_basic(v_new, 4)) != VQ_OK) return st;
+    if ((st = check_basic(cnt, 3)) != VQ_OK) return st;
+    if ((st = check_basic(vsum_f32, 4)) != VQ_OK) return st;
+    if (vsum_act != nullptr && vsum_act->ptr == nullptr) vsum_act = nullptr;
+    if (vsum_act && (st = check_basic(vsum_act, 4)) != VQ_OK) return st;
+    const VqTensorDesc *all[] = {codes, v_new, cnt, vsum_f32, vsum_act};
+    if ((st = check_device(all, 5)) != VQ_OK) return st;
+    if (!is_code_dtype(codes->dtype) || !is_act_dtype(v_new->dtype) || cnt->dtype != VQ_F32 || vsum_f32->dtype != VQ_F32)
+        return VQ_EINVAL_DTYPE;
+    if (vsum_act && vsum_act->dtype != VQ_BF16) return VQ_EINVAL_DTYPE;
+    const int64_t B = codes->shape[0], Hkv = codes->shape[1], n_new = codes->shape[2], M = codes->shape[3];
+    const int64_t D = v_new->shape[3], MK = cnt->shape[2];
+    if (K <= 0 || MK != M * K) return VQ_EINVAL_SHAPE;
+    if (v_new->shape[0] != B || v_new->shape[1] != Hkv || v_new->shape[2] != n_new) return VQ_EINVAL_SHAPE;
+    if (cnt->shape[0] != B || cnt->shape[1] != Hkv) return VQ_EINVAL_SHAPE;
+    if (vsum_f32->shape[0] != B || vsum_f32->shape[1] != Hkv || vsum_f32->shape[2] != MK || vsum_f32->shape[3] != D)
+        return VQ_EINVAL_SHAPE;
+    if (vsum_act && (vsum_act->shape[0] != B || vsum_act->shape[1] != Hkv || vsum_act->shape[2] != MK || vsum_act->shape[3] != D))
+        return VQ_EINVAL_SHAPE;
+    if (!is_dense(*cnt) || !is_dense(*vsum_f32) || (vsum_act && !is_dense(*vsum_act))) return VQ_EINVAL_STRIDE;
+    if (D > 1024 || B * Hkv > 65535) return VQ_EUNSUPPORTED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    dim3 grid(static_cast<unsigned>(M), static_cast<unsigned>(B * Hkv));
+    const int threads = static_cast<int>((D + 31) / 32 * 32);
+    __nv_bfloat16 *shadow = vsum_act ? static_cast<__nv_bfloat16 *>(vsum_act->ptr) : nullptr;
+    if (v_new->dtype == VQ_F32)
+        cache_advance_kernel<float><<<grid, threads, 0, s>>>(
+            codes->ptr, codes->dtype, codes->stride[0], codes->stride[1], codes->stride[2],
+            static_cast<const float *>(v_new->ptr), v_new->stride[0], v_new->stride[1], v_new->stride[2],
+            static_cast<float *>(cnt->ptr), static_cast<float *>(vsum_f32->ptr), shadow, static_cast<int>(Hkv),
+            static_cast<int>(D), static_cast<int>(M), static_cast<int>(K), static_cast<int>(n_new));
+    else
+        cache_advance_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(
+            codes->ptr, codes->dtype, codes->stride[0], codes->stride[1], codes->stride[2],
+            static_cast<const __nv_bfloat16 *>(v_new->ptr), v_new->stride[0], v_new->stride[1], v_new->stride[2],
+            static_cast<float *>(cnt->ptr), static_cast<float *>(vsum_f32->ptr), shadow, static_cast<int>(Hkv),
+            static_cast<int>(D), static_cast<int>(M), static_cast<int>(K), static_cast<int>(n_new));
+    return launch_status();
+}
