@@ -111,6 +111,7 @@ def _run_prefill(api, case, impl):
     k3 = d["k1"] if case["k3"] is case["k1"] else d["k3"]
     out, st = api.vq_attention_prefill(d["q1"], q2, d["k1"], k3, d["v"], d["cb"], case["W"], impl=impl, return_state=True)
     torch.cuda.synchronize()
+    api.check_status()
     return out.float().cpu().numpy(), st
 
 

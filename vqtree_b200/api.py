@@ -32,6 +32,25 @@ def _require_cuda(*ts):
     return dev
 
 
+_STATUS = {}
+
+
+def device_status_word(dev) -> torch.Tensor:
+    """Per-device int32 word a kernel sets when one of its bounded waits expires."""
+    key = torch.device(dev).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _STATUS[key]
+
+
+def check_status(dev="cuda") -> None:
+    """Synchronises and raises VqError(VQ_ETIMEOUT) if a kernel reported an expired wait."""
+    w = device_status_word(dev)
+    if int(w.item()) != 0:
+        w.zero_()
+        raise native.VqError(-6, "device status word")
+
+
 def code_dtype_for(K: int) -> torch.dtype:
     """uint8 when a code fits (K <= 256), else uint16."""
     return torch.uint8 if K <= 256 else torch.uint16
@@ -108,7 +127,7 @@ def prefill_from_aggregates(q1, q2, k1, k3, v, codebook_act, cnt, vsum, window: 
     a.window = int(window)
     a.scale = float(scale) if scale else 0.0
     a.impl = _IMPL[impl]
-    a.status_word = status_word.data_ptr() if status_word is not None else None
+    a.status_word = (status_word if status_word is not None else device_status_word(dev)).data_ptr()
     with torch.cuda.device(dev):
         check(lib.vqattn_prefill(ctypes.byref(a), stream_ptr(dev)), "vqattn_prefill")
     return (out, lse) if return_lse else out

@@ -1,4 +1,418 @@
+// Fused VQ-attention prefill on the sm_100a tensor cores (bf16 operands, fp32 accumulation).
+//
+// One CTA owns one 128-row query tile of one (batch, query head) and walks a list of 128-wide
+// work items with ONE online softmax (this replaces the far kernel, the local ReRoPE kernel and the
+// log-sum-exp merge of the reference: ops/triton_fused_vq_attn.py:88-251,
+// ops/triton_fused_local_attn_rerope.py:121-226):
+//   FAR    q2 . codebook tile       value = vsum tile of the block   weights cnt   (:38-68)
+//   BD_A   q2 . k3 (boundary block) keys older than the window      (rerope mode)  (:68-75)
+//   BD_B   q1 . k1 (boundary block) keys inside the window
+//   FULL   q1 . k1 interior block, no mask
+//   DIAG   q1 . k1 diagonal block, causal mask                                        (:76-78)
+// Per item: TMA loads the K-like and V-like tiles (128B-swizzled) into a 2-stage ring,
+// tcgen05.mma forms S = Q K^T in tensor memory, the four warps read their rows of S with
+// tcgen05.ld (one thread = one query row), apply mask / max / exp2, write P back to tensor memory
+// as packed bf16, rescale the accumulator O when the row maximum moved, and a second tcgen05.mma
+// (A = P from tensor memory, B = V tile, MN-major) adds P V into O.
+#include "tc_ptx.cuh"
 #include "vq_common.cuh"
+
 namespace vq {
-int launch_prefill_tensor(const VqPrefillArgs *a, cudaStream_t stream) { (void)a; (void)stream; return VQ_EUNSUPPORTED; }
+
+using namespace ptx;
+
+constexpr int kTcThreads = 128;
+constexpr int kHalfBytes = kBlock * 64 * 2;  // one TMA box: 128 rows x 64 bf16 (128 B per row)
+
+enum ItemKind : int { kFar = 0, kBdA = 1, kBdB = 2, kFull = 3, kDiag = 4 };
+
+struct TcParams {
+    int Hq, Hkv, NB, MK, rerope, ntiles;
+    int64_t L;
+    int wblocks;  // window / 128
+    float scale_log2;
+    const float *cnt;  // [B*Hkv, NB, MK]
+    __nv_bfloat16 *out;
+    int64_t o_sb, o_sh, o_sl;
+    float *lse2;
+    int32_t *status;
+};
+
+// TMEM column map: S fp32 [0,128), P bf16x2 [128,192), O fp32 [kColO, kColO+D)
+constexpr uint32_t kColS = 0, kColP = 128;
+template <int D> struct TcTmem {
+    static constexpr uint32_t kColO = D == 128 ? 256 : 192;
+    static constexpr uint32_t kCols = D == 128 ? 512 : 256;  // power of two >= kColO + D
+};
+
+template <int D>
+struct TcSmem {
+    static constexpr int NH = D / 64;
+    static constexpr int kTile = NH * kHalfBytes;       // bytes of one 128 x D bf16 tile
+    static constexpr int kQ1 = 0, kQ2 = kTile;
+    static constexpr int kStage0 = 2 * kTile;           // per stage: K tile then V tile
+    static constexpr int kStageBytes = 2 * kTile;
+    static constexpr int kTotal = kStage0 + 2 * kStageBytes + 1024;  // + slack for 1024-byte alignment
+};
+
+template <int D>
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
+                  const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k3,
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_cb,
+                  const __grid_constant__ CUtensorMap tm_vs, TcParams p)
+{
+    using SM = TcSmem<D>;
+    constexpr int NH = SM::NH;
+    constexpr uint32_t kColO = TcTmem<D>::kColO, kTmemCols = TcTmem<D>::kCols;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_o;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_err;
+    __shared__ __align__(16) float s_cnt[2][kBlock];
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int m = p.ntiles - 1 - static_cast<int>(blockIdx.x);  // heavy tiles first
+    const int bh = blockIdx.y;
+    const int b = bh / p.Hq, hq = bh % p.Hq;
+    const int hk = hq / (p.Hq / p.Hkv);
+    const int u = b * p.Hkv + hk;
+
+    // ---- work list of this tile ----
+    const int kb0 = m - p.wblocks;                        // boundary block (exists when >= 0)
+    const bool has_far = kb0 >= 1 && p.MK > 0;
+    const int far_blk = kb0 - 1;
+    const int n_far = has_far ? p.MK / kBlock : 0;
+    const int n_bd = (kb0 >= 0) ? (p.rerope ? 2 : 1) : 0;
+    const int first_full = kb0 >= 0 ? kb0 + 1 : 0;
+    const int n_full = m - first_full;                    // interior blocks
+    const int n_items = n_far + n_bd + n_full + 1;
+
+    auto item_kind = [&](int it) -> int {
+        if (it < n_far) return kFar;
+        it -= n_far;
+        if (it < n_bd) return p.rerope ? (it == 0 ? kBdA : kBdB) : kFull;
+        it -= n_bd;
+        return it < n_full ? kFull : kDiag;
+    };
+    auto item_block = [&](int it) -> int {  // far: codebook tile index; local: key block index
+        if (it < n_far) return it;
+        it -= n_far;
+        if (it < n_bd) return kb0;
+        it -= n_bd;
+        return first_full + it;
+    };
+
+    if (tid == 0) {
+        mbar_init(&bar_q, 1);
+        mbar_init(&bar_kv[0], 1);
+        mbar_init(&bar_kv[1], 1);
+        mbar_init(&bar_s, 1);
+        mbar_init(&bar_o, 1);
+        fence_mbar_init();
+        s_err = 0;
+        prefetch_tmap(&tm_q1); prefetch_tmap(&tm_q2); prefetch_tmap(&tm_k1); prefetch_tmap(&tm_k3);
+        prefetch_tmap(&tm_v); prefetch_tmap(&tm_cb); prefetch_tmap(&tm_vs);
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tmem_alloc(&s_tmem, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    // producer: issue the loads of item `it` into stage `st`
+    auto issue_item = [&](int it, int st) {
+        const int kind = item_kind(it), blk = item_block(it);
+        uint8_t *kdst = smem + SM::kStage0 + st * SM::kStageBytes;
+        uint8_t *vdst = kdst + SM::kTile;
+        mbar_expect_tx(&bar_kv[st], 2 * SM::kTile);
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+            if (kind == kFar) {
+                tma_load_3d(kdst + h * kHalfBytes, &tm_cb, &bar_kv[st], 64 * h, blk * kBlock, hk);
+                tma_load_3d(vdst + h * kHalfBytes, &tm_vs, &bar_kv[st], 64 * h, blk * kBlock, u * p.NB + far_blk);
+            } else {
+                tma_load_4d(kdst + h * kHalfBytes, kind == kBdA ? &tm_k3 : &tm_k1, &bar_kv[st], 64 * h, blk * kBlock, hk, b);
+                tma_load_4d(vdst + h * kHalfBytes, &tm_v, &bar_kv[st], 64 * h, blk * kBlock, hk, b);
+            }
+        }
+    };
+
+    if (tid == 0) {
+        mbar_expect_tx(&bar_q, (p.rerope ? 2 : 1) * SM::kTile);
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+            tma_load_4d(smem + SM::kQ1 + h * kHalfBytes, &tm_q1, &bar_q, 64 * h, m * kBlock, hq, b);
+            if (p.rerope) tma_load_4d(smem + SM::kQ2 + h * kHalfBytes, &tm_q2, &bar_q, 64 * h, m * kBlock, hq, b);
+        }
+        issue_item(0, 0);
+    }
+
+    const uint32_t q1_addr = smem_u32(smem + SM::kQ1);
+    const uint32_t q2_addr = p.rerope ? smem_u32(smem + SM::kQ2) : q1_addr;
+    constexpr uint32_t idesc_qk = idesc_bf16(128, 128, 0, 0);
+    constexpr uint32_t idesc_pv = idesc_bf16(128, D, 0, 1);
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;  // this warp's TMEM lanes
+
+    float row_m = -INFINITY, row_l = 0.f;
+    bool ok = true;
+    if (!mbar_wait(&bar_q, 0)) ok = false;
+
+    for (int it = 0; it < n_items; ++it) {
+        const int st = it & 1;
+        const int kind = item_kind(it), blk = item_block(it);
+        const uint32_t kv_parity = (it >> 1) & 1, it_parity = it & 1;
+        // prefetch the next item: its stage was last read by the PV product of item it-1, already complete
+        if (tid == 0 && it + 1 < n_items) issue_item(it + 1, st ^ 1);
+        if (kind == kFar)
+            s_cnt[st][tid] = p.cnt[(static_cast<int64_t>(u) * p.NB + far_blk) * p.MK + blk * kBlock + tid];
+
+        // ---- S = Q K^T ----
+        if (tid == 0) {
+            if (!mbar_wait(&bar_kv[st], kv_parity)) ok = false;
+            tc_fence_after();
+            const uint32_t qa = (kind == kFar || kind == kBdA) ? q2_addr : q1_addr;
+            const uint32_t ka = smem_u32(smem + SM::kStage0 + st * SM::kStageBytes);
+#pragma unroll
+            for (int h = 0; h < NH; ++h)
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const uint64_t ad = smem_desc_sw128(qa + h * kHalfBytes + k4 * 32, 16, 1024);
+                    const uint64_t bd = smem_desc_sw128(ka + h * kHalfBytes + k4 * 32, 16, 1024);
+                    mma_ss(tmem + kColS, ad, bd, idesc_qk, (h | k4) ? 1u : 0u);
+                }
+            tc_commit(&bar_s);
+        }
+        __syncthreads();  // s_cnt visible; also orders the producer's error flag
+        if (!mbar_wait(&bar_s, it_parity)) ok = false;
+        tc_fence_after();
+
+        // ---- softmax on this thread's row ----
+        float s[kBlock];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_off + kColS + 32 * c, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) s[32 * c + j] = __uint_as_float(r[j]);
+        }
+        // column window of valid keys for this row: [lo, hi)
+        int lo = 0, hi = kBlock;
+        if (kind == kDiag) hi = tid + 1;
+        else if (kind == kBdA) hi = tid;
+        else if (kind == kBdB) lo = tid;
+        float mx = -INFINITY;
+        if (kind == kFar) {
+#pragma unroll
+            for (int c = 0; c < kBlock; ++c) {
+                if (!(s_cnt[st][c] > 0.f)) s[c] = -INFINITY;
+                mx = fmaxf(mx, s[c]);
+            }
+        } else if (kind == kFull) {
+#pragma unroll
+            for (int c = 0; c < kBlock; ++c) mx = fmaxf(mx, s[c]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < kBlock; ++c) {
+                if (c < lo || c >= hi) s[c] = -INFINITY;
+                mx = fmaxf(mx, s[c]);
+            }
+        }
+        const float m_new = fmaxf(row_m, mx * p.scale_log2);
+        const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = ex2(row_m - m_safe);  // row_m = -inf -> 0
+        float lsum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float p0 = ex2(fmaf(s[32 * c + 2 * j], p.scale_log2, -m_safe));
+                const float p1 = ex2(fmaf(s[32 * c + 2 * j + 1], p.scale_log2, -m_safe));
+                if (kind == kFar) {
+                    lsum = fmaf(p0, s_cnt[st][32 * c + 2 * j], lsum);
+                    lsum = fmaf(p1, s_cnt[st][32 * c + 2 * j + 1], lsum);
+                } else {
+                    lsum += p0 + p1;
+                }
+                pk[j] = pack_bf16(p0, p1);
+            }
+            tmem_st16(tmem + lane_off + kColP + 16 * c, pk);
+        }
+        row_l = row_l * alpha + lsum;
+        row_m = m_new;
+        // ---- rescale O where the maximum moved (O is idle: the previous P V product has completed) ----
+        if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_off + kColO + 32 * c, r);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                tmem_st32(tmem + lane_off + kColO + 32 * c, r);
+            }
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncthreads();
+
+        // ---- O += P V ----
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t va = smem_u32(smem + SM::kStage0 + st * SM::kStageBytes + SM::kTile);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                const uint64_t bd = smem_desc_sw128(va + kk * 2048, kHalfBytes, 1024);
+                mma_ts(tmem + kColO, tmem + kColP + 8 * kk, bd, idesc_pv, (it | kk) ? 1u : 0u);
+            }
+            tc_commit(&bar_o);
+        }
+        if (!mbar_wait(&bar_o, it_parity)) ok = false;
+        tc_fence_after();
+        if (!ok) s_err = 1;
+        __syncthreads();
+        if (s_err) break;
+    }
+
+    // ---- epilogue: out = O / l ----
+    if (!s_err) {
+        const int64_t row = static_cast<int64_t>(m) * kBlock + tid;
+        const float inv = 1.f / row_l;
+        __nv_bfloat16 *o = p.out + b * p.o_sb + hq * p.o_sh + row * p.o_sl;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            __syncwarp();
+            tmem_ld32(tmem + lane_off + kColO + 32 * c, r);
+            tc_wait_ld();
+            if (row < p.L) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 w;
+                    w.x = pack_bf16(__uint_as_float(r[8 * j + 0]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
+                    w.y = pack_bf16(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
+                    w.z = pack_bf16(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
+                    w.w = pack_bf16(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(o + 32 * c + 8 * j) = w;
+                }
+            }
+        }
+        if (p.lse2 && row < p.L) p.lse2[static_cast<int64_t>(bh) * p.L + row] = row_m + log2f(row_l);
+    } else if (tid == 0) {
+        if (p.status) atomicExch(p.status, 1);
+        // a bounded wait expired: give the tile loads still in flight time to land before the
+        // shared memory is handed back (a few milliseconds, then leave regardless)
+        for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem, kTmemCols);
+    }
 }
+
+// ------------------------------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// bf16 tensor with up to 4 dims given innermost-first; box = 64 x 128 (x 1 x 1), 128-byte swizzle.
+static bool make_map(CUtensorMap *out, const void *ptr, int rank, const uint64_t *dims, const uint64_t *strides_elems)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t gdim[4], gstride[3];
+    cuuint32_t box[4], estr[4];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        box[i] = i == 0 ? 64 : (i == 1 ? kBlock : 1);
+        estr[i] = 1;
+        if (i > 0) gstride[i - 1] = strides_elems[i] * 2;
+    }
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(ptr), gdim, gstride, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool map_bhld(CUtensorMap *out, const VqTensorDesc &t)
+{
+    const uint64_t dims[4] = {static_cast<uint64_t>(t.shape[3]), static_cast<uint64_t>(t.shape[2]),
+                              static_cast<uint64_t>(t.shape[1]), static_cast<uint64_t>(t.shape[0])};
+    const uint64_t str[4] = {1, static_cast<uint64_t>(t.stride[2]), static_cast<uint64_t>(t.stride[1]),
+                             static_cast<uint64_t>(t.stride[0])};
+    return make_map(out, t.ptr, 4, dims, str);
+}
+
+template <int D>
+static int launch_tc(const VqPrefillArgs *a, cudaStream_t stream)
+{
+    using SM = TcSmem<D>;
+    const int64_t B = a->q1.shape[0], Hq = a->q1.shape[1], L = a->q1.shape[2], Hkv = a->k1.shape[1];
+    const bool far = a->codebook.ptr != nullptr && a->cnt.ptr != nullptr;
+    CUtensorMap mq1, mq2, mk1, mk3, mv, mcb, mvs;
+    if (!map_bhld(&mq1, a->q1) || !map_bhld(&mq2, a->q2) || !map_bhld(&mk1, a->k1) || !map_bhld(&mk3, a->k3) ||
+        !map_bhld(&mv, a->v))
+        return VQ_ELAUNCH;
+    TcParams p{};
+    if (far) {
+        const uint64_t MK = a->codebook.shape[1], NB = a->cnt.shape[2];
+        const uint64_t cd[3] = {static_cast<uint64_t>(D), MK, static_cast<uint64_t>(Hkv)};
+        const uint64_t cs[3] = {1, static_cast<uint64_t>(D), MK * D};
+        const uint64_t vd[3] = {static_cast<uint64_t>(D), MK, static_cast<uint64_t>(B * Hkv) * NB};
+        if (!make_map(&mcb, a->codebook.ptr, 3, cd, cs) || !make_map(&mvs, a->vsum.ptr, 3, vd, cs)) return VQ_ELAUNCH;
+        p.MK = static_cast<int>(MK);
+        p.NB = static_cast<int>(NB);
+        p.cnt = static_cast<const float *>(a->cnt.ptr);
+    } else {
+        mcb = mk1;  // never dereferenced: the work list has no far items
+        mvs = mv;
+    }
+    p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv);
+    p.L = L;
+    p.ntiles = static_cast<int>((L + kBlock - 1) / kBlock);
+    p.wblocks = static_cast<int>(a->window / kBlock);
+    p.rerope = (a->q2.ptr != a->q1.ptr || a->k3.ptr != a->k1.ptr) ? 1 : 0;
+    const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(D));
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.out = static_cast<__nv_bfloat16 *>(a->out.ptr);
+    p.o_sb = a->out.stride[0]; p.o_sh = a->out.stride[1]; p.o_sl = a->out.stride[2];
+    p.lse2 = static_cast<float *>(a->lse2.ptr);
+    p.status = a->status_word;
+    auto kern = prefill_tc_kernel<D>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal) != cudaSuccess) return VQ_ELAUNCH;
+    dim3 grid(static_cast<unsigned>(p.ntiles), static_cast<unsigned>(B * Hq));
+    kern<<<grid, kTcThreads, SM::kTotal, stream>>>(mq1, mq2, mk1, mk3, mv, mcb, mvs, p);
+    return launch_status();
+}
+
+int launch_prefill_tensor(const VqPrefillArgs *a, cudaStream_t stream)
+{
+    const int D = static_cast<int>(a->q1.shape[3]);
+    // 16-byte aligned rows for the output stores and the tensor maps
+    if (a->out.stride[2] % 8 || a->out.stride[1] % 8 || a->out.stride[0] % 8) return VQ_EINVAL_STRIDE;
+    return D == 64 ? launch_tc<64>(a, stream) : launch_tc<128>(a, stream);
+}
+
+}  // namespace vq
