@@ -1,0 +1,64 @@
+"""GPU tests of the mirrors of the reference's Python entry points, against golden vectors
+produced by the reference itself (tests/golden/gen_golden.py)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_multi_head_single_quantize_matches_reference(golden_dir):
+    from vqtree_b200.mini_vq import multi_head_single_quantize
+    gd = np.load(golden_dir / "assign_a.npz")
+    k, cb = torch.from_numpy(gd["k"]).cuda(), torch.from_numpy(gd["codebook"]).cuda()
+    quantized, ids, onehot = multi_head_single_quantize(k, cb)
+    assert ids.dtype == torch.int64 and ids.shape == k.shape[:3]
+    assert onehot.shape == (*k.shape[:3], cb.shape[1]) and int(onehot.sum()) == ids.numel()
+    assert (ids.cpu().numpy() != gd["ids"]).mean() < 1e-3
+    np.testing.assert_array_equal(quantized[:, :, :8].cpu().numpy()[ids[:, :, :8].cpu().numpy() == gd["ids"][:, :, :8]],
+                                  gd["quantized_head"][ids[:, :, :8].cpu().numpy() == gd["ids"][:, :, :8]])
+
+
+def test_vq_attn_forward_on_reference_arguments(golden_dir):
+    """Feed the exact tensors the reference handed to its fused kernel; compare with its merged output."""
+    from vqtree_b200.fused_vq_attn import vq_attn_forward
+    f = np.load(golden_dir / "fast_w128.npz")
+    gd = np.load(golden_dir / "naive_w128.npz")
+    cu = lambda a: torch.from_numpy(a).cuda()
+    out = vq_attn_forward(cu(f["q1"]), cu(f["q2"]), cu(f["k1"]), cu(gd["codebook"]), cu(f["k_vq_cnt"]).float(), cu(gd["k"]),
+                          cu(gd["v"]), cu(f["v_vq"]), cu(f["vi"]).long(), int(gd["window"]))
+    np.testing.assert_allclose(out.cpu().numpy(), f["out"], atol=1e-4, rtol=0)
+    np.testing.assert_allclose(out.cpu().numpy(), gd["out"], atol=1e-4, rtol=0)
+    # bf16, the dtype the reference's kernels are written for (tolerance of its sibling self-tests)
+    b = lambda a: torch.from_numpy(a).cuda().bfloat16()
+    out16 = vq_attn_forward(b(f["q1"]), b(f["q2"]), b(f["k1"]), b(gd["codebook"]), cu(f["k_vq_cnt"]).bfloat16(), b(gd["k"]),
+                            b(gd["v"]), b(f["v_vq"]), cu(f["vi"]).long(), int(gd["window"]))
+    np.testing.assert_allclose(out16.float().cpu().numpy(), f["out"], atol=2e-2, rtol=0)
+
+
+def test_local_flash_attn_func(golden_dir):
+    from vqtree_b200.fused_local_attn_rerope import flash_attn_func
+    f = np.load(golden_dir / "fast_w128.npz")
+    gd = np.load(golden_dir / "naive_w128.npz")
+    t = lambda a: torch.from_numpy(a).cuda().transpose(1, 2).contiguous()   # [B,L,H,D]
+    o, lse = flash_attn_func(t(f["q1"]), t(f["q2"]), t(f["k1"]), t(gd["k"]), t(gd["v"]), int(gd["window"]), return_lse=True)
+    assert o.shape == t(f["q1"]).shape
+    np.testing.assert_allclose(o.transpose(1, 2).cpu().numpy(), f["o_local"], atol=1e-4, rtol=0)
+    np.testing.assert_allclose(lse.cpu().numpy(), f["lse_local"], atol=1e-3, rtol=0)
+    o16 = flash_attn_func(*(x.bfloat16() for x in (t(f["q1"]), t(f["q2"]), t(f["k1"]), t(gd["k"]), t(gd["v"]))), int(gd["window"]))
+    np.testing.assert_allclose(o16.float().transpose(1, 2).cpu().numpy(), f["o_local"], atol=2e-2, rtol=0)
+
+
+def test_long_prefilling_entry_point(golden_dir):
+    from vqtree_b200.attn_vq import AttentionMode, VectorQuantizedReRoPECache, long_prefilling_sort_based_linear, BLOCK_SIZE
+    assert BLOCK_SIZE == 128
+    gd = np.load(golden_dir / "naive_w128.npz")
+    q, k, v, cb = (torch.from_numpy(gd[n]).cuda() for n in ("q", "k", "v", "codebook"))
+    B, H, L, D = q.shape
+    cache = VectorQuantizedReRoPECache(int(gd["window"]), cb, False, attention_mode=AttentionMode.SORT_BASED_LINEAR)
+    pos = torch.arange(L, device="cuda")[None].expand(B, -1)
+    out = long_prefilling_sort_based_linear(q, k, v, pos, cache)
+    assert out.shape == (B, L, H * D)
+    want = torch.from_numpy(gd["out"]).transpose(1, 2).reshape(B, L, H * D)
+    np.testing.assert_allclose(out.cpu().numpy(), want.numpy(), atol=1e-4, rtol=0)
+    assert cache.get_seq_length(0) == L

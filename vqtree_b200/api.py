@@ -111,14 +111,16 @@ def gather_aggregates(v_vq: torch.Tensor, vi: torch.Tensor, nb: int) -> torch.Te
 
 
 def prefill_from_aggregates(q1, q2, k1, k3, v, codebook_act, cnt, vsum, window: int, scale: Optional[float] = None,
-                            impl: str = "auto", return_lse: bool = False, status_word: Optional[torch.Tensor] = None):
+                            impl: str = "auto", return_lse: bool = False, status_word: Optional[torch.Tensor] = None,
+                            out: Optional[torch.Tensor] = None):
     """Fused prefill attention from ready aggregates (replaces ops/triton_fused_vq_attn.py:190-251).
 
     codebook_act [Hkv,MK,D] in the activation dtype (None: local part only).
     """
     dev = _require_cuda(q1, q2, k1, k3, v, codebook_act, cnt, vsum)
     B, Hq, L, D = q1.shape
-    out = torch.empty((B, Hq, L, D), dtype=q1.dtype, device=dev)
+    if out is None:
+        out = torch.empty((B, Hq, L, D), dtype=q1.dtype, device=dev)
     lse = torch.empty((B, Hq, L), dtype=torch.float32, device=dev) if return_lse else None
     a = VqPrefillArgs()
     a.q1, a.q2, a.k1, a.k3, a.v = desc(q1), desc(q2), desc(k1), desc(k3), desc(v)

@@ -1,0 +1,86 @@
+"""Mirror of the reference's ``ops/attn_vq.py`` for the VQ path: block size, attention modes, the
+cache object and the prefill / decode dispatch, on the CUDA library.
+
+The HF ``LlamaAttention`` subclass of the reference (ops/attn_vq.py:176-248) depends on a
+transformers API (``LlamaFlashAttention2``, ``LLAMA_ATTENTION_CLASSES``) that newer releases removed;
+the functions here take the projected ``[B,H,L,D]`` states that class hands to its dispatch
+(``_dispatch_attn_impl``, :225-248) and can be called from any attention module.
+"""
+from __future__ import annotations
+
+import math
+from enum import Enum
+from typing import Optional
+
+import torch
+
+from . import api
+
+BLOCK_SIZE = 128  # ops/attn_vq.py:23
+
+
+class AttentionMode(Enum):  # ops/attn_vq.py:26-28 (the spelling of the first member is the reference's)
+    SLOW_REFERNECE = 0
+    SORT_BASED_LINEAR = 1
+
+
+def rotate_half(x):
+    x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2:]
+    return torch.cat((-x2, x1), dim=-1)
+
+
+def rope_cos_sin(n_pos: int, dim: int, device, base: float = 10000.0):
+    inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float64, device=device) / dim))
+    ang = torch.outer(torch.arange(n_pos, dtype=torch.float64, device=device), inv)
+    ang = torch.cat((ang, ang), dim=-1)
+    return ang.cos().float(), ang.sin().float()
+
+
+class VectorQuantizedReRoPECache:
+    """State the reference passes as ``past_key_value`` (ops/attn_vq.py:31-52) plus what decode needs.
+
+    ``codebook`` is [H,C,D] (the reference's single codebook) or [H,M,K,D].  After a prefill the cache
+    holds, per layer, the newest window of rotated keys, un-rotated keys and values, the running
+    counts and fp32 value sums of everything older, and the number of tokens seen.
+    """
+
+    def __init__(self, window_length: int, codebook: torch.Tensor, sphere: bool = False, *,
+                 attention_mode: AttentionMode = AttentionMode.SORT_BASED_LINEAR):
+        assert window_length % BLOCK_SIZE == 0
+        assert not sphere, "Not implemented"  # ops/attn_vq.py:198
+        self.window_length = window_length
+        self.codebook = codebook if codebook.dim() == 4 else codebook[:, None]
+        assert (self.codebook.shape[1] * self.codebook.shape[2]) % BLOCK_SIZE == 0  # ops/attn_vq.py:45
+        self.sphere = sphere
+        self.attention_mode = attention_mode
+        self.layers = {}
+        self.seen_tokens = 0
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        st = self.layers.get(layer_idx)
+        return 0 if st is None else st["n"]
+
+
+def long_prefilling_sort_based_linear(query_states, key_states, value_states, position_ids,
+                                      past_key_value: VectorQuantizedReRoPECache, layer_idx: int = 0,
+                                      rope_base: float = 10000.0):
+    """ops/attn_vq.py:336-443: RoPE / ReRoPE rotation, code assignment, aggregates, fused attention.
+
+    query_states [B,Hq,L,D], key/value_states [B,Hkv,L,D] (un-rotated), position_ids [B,L].
+    Returns [B, L, Hq*D] like the reference (:442).
+    """
+    bsz, hq, q_len, d = query_states.shape
+    W = past_key_value.window_length
+    cos, sin = rope_cos_sin(max(q_len, W + 2), d, query_states.device, rope_base)
+    c, s = cos[position_ids].unsqueeze(1), sin[position_ids].unsqueeze(1)
+    dt = query_states.dtype
+    q1 = (query_states.float() * c + rotate_half(query_states.float()) * s).to(dt)
+    k1 = (key_states.float() * c + rotate_half(key_states.float()) * s).to(dt)
+    q2 = (query_states.float() * cos[W + 1] + rotate_half(query_states.float()) * sin[W + 1]).to(dt)  # :405-407
+    cb = past_key_value.codebook.float().contiguous()
+    out, st = api.vq_attention_prefill(q1, q2, k1, key_states.contiguous(), value_states.contiguous(), cb, W,
+                                       scale=1.0 / math.sqrt(d), return_state=True)
+    past_key_value.layers[layer_idx] = dict(n=q_len, k1=k1, k3=key_states, v=value_states, codes=st["codes"])
+    if layer_idx == 0:
+        past_key_value.seen_tokens += q_len
+    return out.transpose(1, 2).contiguous().flatten(2)
