@@ -148,6 +148,7 @@ typedef struct VqDecodeArgs {
     float scale;
     void *workspace;
     size_t workspace_bytes;
+    int32_t *status_word;  /* device int32 or NULL: set non-zero by a kernel whose bounded wait expired */
 } VqDecodeArgs;
 
 size_t vqattn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t D);

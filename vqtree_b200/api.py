@@ -188,6 +188,7 @@ def vq_attention_decode(q1, q2, k1_win, k3_win, v_win, codebook, cnt, vsum, n_va
     a.scale = float(scale) if scale else 0.0
     a.workspace = workspace.data_ptr()
     a.workspace_bytes = workspace.numel() * workspace.element_size()
+    a.status_word = device_status_word(dev).data_ptr()
     with torch.cuda.device(dev):
         check(lib.vqattn_decode(ctypes.byref(a), stream_ptr(dev)), "vqattn_decode")
     return out

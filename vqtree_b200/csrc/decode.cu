@@ -7,164 +7,142 @@
 //
 // Work split: grid = (splits, head groups, batch*kv-head).  A CTA owns a contiguous share of the
 // window rows and of the far rows of one (batch, kv head) and up to GH query heads of its group:
-//   pass 1  every row is read once with 16-byte loads by a group of lanes (one row per group),
-//           the dot products are reduced with shuffles, scores land in shared memory;
-//   pass 2  block max, p = exp2(s - max), denominator (far rows weighted by cnt);
-//   pass 3  value rows streamed the same way, fp32 accumulators in registers, reduced across
-//           lane groups by shuffles and across warps in shared memory.
-// Partial (max, denominator, numerator) triples go to a workspace; the last CTA of a unit to
-// finish (atomic ticket) merges them and writes the output row, then re-arms the ticket.
-#include "vq_common.cuh"
+// and streams them once: a group of lanes (D*sizeof/16 of them) owns one row per step, loads its
+// 16-byte slice of the key row and of the value row together (several rows in flight per lane),
+// reduces the dot product with shuffles and folds the row into its own running softmax state
+// (max, denominator, D/lanes output columns).  No block-wide barrier sits between loads.
+// The lane groups of a warp, then the warps (shared memory), then the splits (workspace; the last
+// CTA of a unit to finish takes an atomic ticket, merges and re-arms it) are merged at the end.
+#include "decode_common.cuh"
 
 namespace vq {
 
-constexpr int kDecThreads = 256;
-constexpr int kDecMaxSplits = 16;
-constexpr int kDecUnroll = 4;
+int launch_decode_bulk(const DecodeParams &p, int64_t units, int D, int GH, bool cb32, void *workspace, size_t workspace_bytes,
+                       int32_t *status, cudaStream_t s);
+size_t decode_bulk_workspace_bytes(int64_t units_times_groups, int64_t heads_per_group, int64_t D);
 
-template <typename TR> struct Slice;  // 16-byte slice of a row as floats
-template <> struct Slice<float> {
-    static constexpr int E = 4;
-    static __device__ __forceinline__ void ld(const float *p, float (&x)[4])
-    {
-        const float4 v = __ldcs(reinterpret_cast<const float4 *>(p));
-        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-    }
-    static __device__ __forceinline__ void ld_cached(const float *p, float (&x)[4])
-    {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
-        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-    }
-};
-template <> struct Slice<__nv_bfloat16> {
-    static constexpr int E = 8;
-    static __device__ __forceinline__ void unpack(const uint4 &raw, float (&x)[8])
-    {
-        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            x[2 * i] = __low2float(h[i]);
-            x[2 * i + 1] = __high2float(h[i]);
-        }
-    }
-    static __device__ __forceinline__ void ld(const __nv_bfloat16 *p, float (&x)[8])
-    {
-        unpack(__ldcs(reinterpret_cast<const uint4 *>(p)), x);
-    }
-    static __device__ __forceinline__ void ld_cached(const __nv_bfloat16 *p, float (&x)[8])
-    {
-        unpack(__ldg(reinterpret_cast<const uint4 *>(p)), x);
-    }
-};
-
-// Scores rows [r0, r1) of `base` against GH query vectors held in shared memory (fp32, [GH][D]).
-// s_out[g * sstride + (r - r0)] receives scale_log2 * q_g . row, or -inf where wts[r] <= 0.
-template <typename TR, int D, int GH, bool kCached>
-__device__ __forceinline__ void score_rows(const TR *__restrict__ base, int64_t row_stride, int r0, int r1,
-                                           const float *__restrict__ qs, float *__restrict__ s_out, int sstride,
-                                           float scale_log2, const float *__restrict__ wts)
+// Window rows [r0,r1): key row and value row have the same type, one row per lane group per step.
+template <typename T, int D, int GH, int U>
+__device__ __forceinline__ void stream_rows(DecState<GH, Slice<T>::E> &st, const T *__restrict__ K, int64_t ks,
+                                            const T *__restrict__ V, int64_t vs, int r0, int r1,
+                                            const float *__restrict__ qs, float scale_log2, const float *__restrict__ wts)
 {
-    constexpr int E = Slice<TR>::E;
-    constexpr int LPR = D / E;  // lanes per row
-    constexpr int GROUPS = kDecThreads / LPR;
-    const int gid = threadIdx.x / LPR, sub = threadIdx.x % LPR;
+    constexpr int E = Slice<T>::E, LPR = D / E, GPW = 32 / LPR, NG = (kDecThreads / 32) * GPW;
+    const int lane = threadIdx.x & 31, gidx = (threadIdx.x >> 5) * GPW + lane / LPR, sub = lane % LPR;
     float q[GH][E];
 #pragma unroll
     for (int g = 0; g < GH; ++g)
 #pragma unroll
         for (int e = 0; e < E; ++e) q[g][e] = qs[g * D + sub * E + e];
-    for (int rb = r0; rb < r1; rb += GROUPS * kDecUnroll) {
-        float x[kDecUnroll][E];
-        bool ok[kDecUnroll];
+    const int iters = (r1 - r0 + NG * U - 1) / (NG * U);
+    for (int it = 0; it < iters; ++it) {
+        float kx[U][E], vx[U][E];
+        bool ok[U];
 #pragma unroll
-        for (int uu = 0; uu < kDecUnroll; ++uu) {
-            const int r = rb + uu * GROUPS + gid;
+        for (int uu = 0; uu < U; ++uu) {
+            const int r = r0 + (it * U + uu) * NG + gidx;
             ok[uu] = r < r1;
             if (ok[uu]) {
-                if (kCached) Slice<TR>::ld_cached(base + static_cast<int64_t>(r) * row_stride + sub * E, x[uu]);
-                else Slice<TR>::ld(base + static_cast<int64_t>(r) * row_stride + sub * E, x[uu]);
+                Slice<T>::ld(K + static_cast<int64_t>(r) * ks + sub * E, kx[uu]);
+                Slice<T>::ld(V + static_cast<int64_t>(r) * vs + sub * E, vx[uu]);
             } else {
 #pragma unroll
-                for (int e = 0; e < E; ++e) x[uu][e] = 0.f;
+                for (int e = 0; e < E; ++e) kx[uu][e] = vx[uu][e] = 0.f;
             }
         }
 #pragma unroll
-        for (int uu = 0; uu < kDecUnroll; ++uu) {
-            const int r = rb + uu * GROUPS + gid;
+        for (int uu = 0; uu < U; ++uu) {
+            const int r = r0 + (it * U + uu) * NG + gidx;
+            float w = 1.f;
+            if (wts != nullptr && ok[uu]) w = wts[r];
 #pragma unroll
             for (int g = 0; g < GH; ++g) {
                 float s = 0.f;
 #pragma unroll
-                for (int e = 0; e < E; ++e) s = fmaf(q[g][e], x[uu][e], s);
+                for (int e = 0; e < E; ++e) s = fmaf(q[g][e], kx[uu][e], s);
 #pragma unroll
                 for (int off = LPR / 2; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-                if (sub == 0 && ok[uu]) {
-                    float val = s * scale_log2;
-                    if (wts != nullptr && wts[r] <= 0.f) val = -INFINITY;
-                    s_out[g * sstride + (r - r0)] = val;
-                }
+                s = (ok[uu] && w > 0.f) ? s * scale_log2 : -INFINITY;
+                st.update(g, s, w, vx[uu]);
             }
         }
     }
 }
 
-// acc[g][e] += sum over rows [r0,r1) of p[g*sstride + (r-r0)] * row[r][sub*E + e]
-template <typename TR, int D, int GH>
-__device__ __forceinline__ void accum_rows(const TR *__restrict__ base, int64_t row_stride, int r0, int r1,
-                                           const float *__restrict__ p, int sstride, float (&acc)[GH][Slice<TR>::E])
+// Far rows [r0,r1) with an fp32 codebook (512-byte rows for D = 128) and bf16 value sums: a step
+// covers GPW rows of the warp; their scores are formed by groups of D/4 lanes in GPW/GPWC sub-steps.
+template <int D, int GH, int U>
+__device__ __forceinline__ void stream_far_f32cb(DecState<GH, 8> &st, const float *__restrict__ C,
+                                                 const __nv_bfloat16 *__restrict__ V, int r0, int r1,
+                                                 const float *__restrict__ qs, float scale_log2, const float *__restrict__ wts)
 {
-    constexpr int E = Slice<TR>::E;
-    constexpr int LPR = D / E;
-    constexpr int GROUPS = kDecThreads / LPR;
-    const int gid = threadIdx.x / LPR, sub = threadIdx.x % LPR;
-    for (int rb = r0; rb < r1; rb += GROUPS * kDecUnroll) {
-        float x[kDecUnroll][E];
-        bool ok[kDecUnroll];
+    constexpr int LPR = D / 8, GPW = 32 / LPR;     // value-row lane groups
+    constexpr int LPRC = D / 4, GPWC = 32 / LPRC;  // codebook-row lane groups
+    constexpr int SUB = GPW / GPWC;                // = 2
+    constexpr int NW = kDecThreads / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int vg = lane / LPR, sub = lane % LPR, cg = lane / LPRC, csub = lane % LPRC;
+    float q[GH][4];
 #pragma unroll
-        for (int uu = 0; uu < kDecUnroll; ++uu) {
-            const int r = rb + uu * GROUPS + gid;
-            ok[uu] = r < r1;
-            if (ok[uu]) Slice<TR>::ld(base + static_cast<int64_t>(r) * row_stride + sub * E, x[uu]);
+    for (int g = 0; g < GH; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) q[g][e] = qs[g * D + csub * 4 + e];
+    const int rows_per_step = NW * GPW;
+    const int iters = (r1 - r0 + rows_per_step * U - 1) / (rows_per_step * U);
+    for (int it = 0; it < iters; ++it) {
+        float cx[U][SUB][4], vx[U][8];
+#pragma unroll
+        for (int uu = 0; uu < U; ++uu) {
+            const int base = r0 + ((it * U + uu) * NW + warp) * GPW;  // first of this warp's GPW rows
+#pragma unroll
+            for (int ss = 0; ss < SUB; ++ss) {
+                const int r = base + ss * GPWC + cg;
+                if (r < r1) Slice<float>::ld_cached(C + static_cast<int64_t>(r) * D + csub * 4, cx[uu][ss]);
+                else cx[uu][ss][0] = cx[uu][ss][1] = cx[uu][ss][2] = cx[uu][ss][3] = 0.f;
+            }
+            const int rv = base + vg;
+            if (rv < r1) Slice<__nv_bfloat16>::ld(V + static_cast<int64_t>(rv) * D + sub * 8, vx[uu]);
+            else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) vx[uu][e] = 0.f;
+            }
         }
 #pragma unroll
-        for (int uu = 0; uu < kDecUnroll; ++uu) {
-            if (!ok[uu]) continue;
-            const int r = rb + uu * GROUPS + gid;
+        for (int uu = 0; uu < U; ++uu) {
+            const int base = r0 + ((it * U + uu) * NW + warp) * GPW;
+            const int rv = base + vg;
+            const bool ok = rv < r1;
+            const float w = ok ? wts[rv] : 0.f;
 #pragma unroll
             for (int g = 0; g < GH; ++g) {
-                const float pv = p[g * sstride + (r - r0)];
+                float mine = 0.f;
 #pragma unroll
-                for (int e = 0; e < E; ++e) acc[g][e] = fmaf(pv, x[uu][e], acc[g][e]);
+                for (int ss = 0; ss < SUB; ++ss) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s = fmaf(q[g][e], cx[uu][ss][e], s);
+#pragma unroll
+                    for (int off = LPRC / 2; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+                    // the score of value group vg was formed in sub-step vg / GPWC by codebook group vg % GPWC
+                    const float got = __shfl_sync(0xffffffffu, s, (vg % GPWC) * LPRC);
+                    if (ss == vg / GPWC) mine = got;
+                }
+                const float s = (ok && w > 0.f) ? mine * scale_log2 : -INFINITY;
+                st.update(g, s, w, vx[uu]);
             }
         }
     }
 }
-
-struct DecodeParams {
-    const void *q1, *q2, *k1w, *k3w, *vw, *codebook, *vsum;
-    const float *cnt;
-    void *out;
-    float *partial;   // [units][G][splits][D + 2]
-    int *ticket;      // [units * head_groups]
-    int64_t q_sb, q_sh, q2_sb, q2_sh, o_sb, o_sh;
-    int64_t k_sb, k_sh, k_sl, k3_sb, k3_sh, k3_sl, v_sb, v_sh, v_sl;
-    int Hq, Hkv, G, MK, n_valid, n_bd, use_far, splits, rows_w, rows_f;
-    float scale_log2;
-};
 
 template <typename T, typename TC, int D, int GH>
 __global__ void __launch_bounds__(kDecThreads) decode_kernel(DecodeParams p)
 {
     constexpr int E = Slice<T>::E;
     constexpr int LPR = D / E;
-    extern __shared__ __align__(16) float dsm[];
-    // layout: q [2][GH][D] | scores [GH][rows_w + rows_f] | red [8][GH][D] | stats
-    float *s_q = dsm;
-    const int nrows = p.rows_w + p.rows_f;
-    float *s_sc = s_q + 2 * GH * D;
-    float *s_red = s_sc + GH * nrows;
-    __shared__ float s_stat[kDecThreads / 32][GH];
-    __shared__ float s_m[GH], s_l[GH];
+    constexpr int NW = kDecThreads / 32;
+    constexpr int U = GH >= 4 ? 2 : 4;
+    __shared__ __align__(16) float s_q[2 * GH * D];
+    __shared__ __align__(16) float s_red[NW * GH * (D + 2)];
     __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -182,7 +160,6 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(DecodeParams p)
     // this CTA's share of the rows
     const int w0 = min(split * p.rows_w, p.n_valid), w1 = min(w0 + p.rows_w, p.n_valid);
     const int f0 = p.use_far ? min(split * p.rows_f, p.MK) : 0, f1 = p.use_far ? min(f0 + p.rows_f, p.MK) : 0;
-    const int nw = w1 - w0, nf = f1 - f0;
 
     const T *k1w = static_cast<const T *>(p.k1w) + b * p.k_sb + hk * p.k_sh;
     const T *k3w = static_cast<const T *>(p.k3w) + b * p.k3_sb + hk * p.k3_sh;
@@ -191,130 +168,32 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(DecodeParams p)
     const T *vs = static_cast<const T *>(p.vsum) + static_cast<int64_t>(u) * p.MK * D;
     const float *cn = p.cnt + static_cast<int64_t>(u) * p.MK;
 
-    // ---- pass 1: scores ----
-    {
-        const int wb = min(max(p.n_bd, w0), w1);  // rows [w0,wb) use q2.k3, [wb,w1) use q1.k1
-        if (wb > w0)
-            score_rows<T, D, GH, false>(k3w, p.k3_sl, w0, wb, s_q + GH * D, s_sc, nrows, p.scale_log2, nullptr);
-        if (w1 > wb)
-            score_rows<T, D, GH, false>(k1w, p.k_sl, wb, w1, s_q, s_sc + (wb - w0), nrows, p.scale_log2, nullptr);
-        if (nf > 0)
-            score_rows<TC, D, GH, true>(cbk, D, f0, f1, s_q + GH * D, s_sc + nw, nrows, p.scale_log2, cn);
+    DecState<GH, E> st;
+    st.init();
+    const int wb = min(max(p.n_bd, w0), w1);  // rows [w0,wb) use q2.k3, [wb,w1) use q1.k1
+    if (wb > w0) stream_rows<T, D, GH, U>(st, k3w, p.k3_sl, vw, p.v_sl, w0, wb, s_q + GH * D, p.scale_log2, nullptr);
+    if (w1 > wb) stream_rows<T, D, GH, U>(st, k1w, p.k_sl, vw, p.v_sl, wb, w1, s_q, p.scale_log2, nullptr);
+    if (f1 > f0) {
+        if constexpr (sizeof(TC) == sizeof(T))
+            stream_rows<T, D, GH, U>(st, reinterpret_cast<const T *>(cbk), D, vs, D, f0, f1, s_q + GH * D, p.scale_log2, cn);
+        else
+            stream_far_f32cb<D, GH, U>(st, reinterpret_cast<const float *>(cbk), reinterpret_cast<const __nv_bfloat16 *>(vs),
+                                       f0, f1, s_q + GH * D, p.scale_log2, cn);
     }
-    __syncthreads();
-
-    // ---- pass 2: max, exponentials, denominator ----
-    float mx[GH];
+    // merge the lane groups of a warp, then the warps
 #pragma unroll
-    for (int g = 0; g < GH; ++g) {
-        float m = -INFINITY;
-        for (int i = tid; i < nw + nf; i += kDecThreads) m = fmaxf(m, s_sc[g * nrows + i]);
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-        if (lane == 0) s_stat[warp][g] = m;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GH; ++g) {
-        float m = s_stat[0][g];
-#pragma unroll
-        for (int w = 1; w < kDecThreads / 32; ++w) m = fmaxf(m, s_stat[w][g]);
-        mx[g] = m;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GH; ++g) {
-        float l = 0.f;
-        for (int i = tid; i < nw + nf; i += kDecThreads) {
-            const float s = s_sc[g * nrows + i];
-            const float e = (mx[g] == -INFINITY) ? 0.f : exp2f(s - mx[g]);
-            s_sc[g * nrows + i] = e;
-            l += (i >= nw) ? e * cn[f0 + (i - nw)] : e;
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
-        if (lane == 0) s_stat[warp][g] = l;
-    }
-    __syncthreads();
-    if (tid < GH) {
-        float l = 0.f;
-        for (int w = 0; w < kDecThreads / 32; ++w) l += s_stat[w][tid];
-        s_l[tid] = l;
-    }
-#pragma unroll
-    for (int g = 0; g < GH; ++g)
-        if (tid == g) s_m[g] = mx[g];
-
-    // ---- pass 3: values ----
-    float acc[GH][E];
-#pragma unroll
-    for (int g = 0; g < GH; ++g)
-#pragma unroll
-        for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
-    if (nw > 0) accum_rows<T, D, GH>(vw, p.v_sl, w0, w1, s_sc, nrows, acc);
-    if (nf > 0) accum_rows<T, D, GH>(vs, D, f0, f1, s_sc + nw, nrows, acc);
-    // reduce over the lane groups of a warp, then over warps
-#pragma unroll
-    for (int g = 0; g < GH; ++g)
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-            float x = acc[g][e];
-#pragma unroll
-            for (int off = 16; off >= LPR; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
-            acc[g][e] = x;
-        }
-    if (lane < LPR) {
-#pragma unroll
-        for (int g = 0; g < GH; ++g)
-#pragma unroll
-            for (int e = 0; e < E; ++e) s_red[(warp * GH + g) * D + lane * E + e] = acc[g][e];
-    }
-    __syncthreads();
-    // partial[(u*G + head)][split][D+2]
-    float *part = p.partial + ((static_cast<int64_t>(u) * p.G + hg * GH) * p.splits) * (D + 2);
-    for (int i = tid; i < GH * D; i += kDecThreads) {
-        const int g = i / D, d = i % D;
-        float x = 0.f;
-#pragma unroll
-        for (int w = 0; w < kDecThreads / 32; ++w) x += s_red[(w * GH + g) * D + d];
-        part[(static_cast<int64_t>(g) * p.splits + split) * (D + 2) + d] = x;
-    }
-    if (tid < GH) {
-        part[(static_cast<int64_t>(tid) * p.splits + split) * (D + 2) + D] = s_m[tid];
-        part[(static_cast<int64_t>(tid) * p.splits + split) * (D + 2) + D + 1] = s_l[tid];
-    }
-    __threadfence();
-    __syncthreads();
-    int *ticket = p.ticket + u * gridDim.y + hg;
-    if (tid == 0) {
-        const int t = atomicAdd(ticket, 1);
-        s_last = (t == p.splits - 1);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // merge the splits
-    for (int i = tid; i < GH * D; i += kDecThreads) {
-        const int g = i / D, d = i % D;
-        const float *pg = part + static_cast<int64_t>(g) * p.splits * (D + 2);
-        float M = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(pg + s * (D + 2) + D));
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-            const float ms = __ldcg(pg + s * (D + 2) + D);
-            const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-            num += w * __ldcg(pg + s * (D + 2) + d);
-            den += w * __ldcg(pg + s * (D + 2) + D + 1);
-        }
-        static_cast<T *>(p.out)[b * p.o_sb + (hq0 + g) * p.o_sh + d] = from_f32<T>(num / den);
-    }
-    if (tid == 0) *ticket = 0;  // ready for the next call on this stream
+    for (int off = LPR; off < 32; off <<= 1) st.merge_xor(off);
+    decode_finish<T, D, GH, NW, E>(p, st, s_red, &s_last, split, hg, u, b, hq0);
 }
 
-static int pick_splits(int64_t units, int n_valid, int MK)
+#ifndef VQ_DECODE_TARGET_CTAS
+#define VQ_DECODE_TARGET_CTAS 2048
+#endif
+
+static int pick_splits(int64_t ctas_per_split, int n_valid, int MK)
 {
-    // aim for roughly 4 CTAs per SM (148 SMs) without making a split smaller than 128 rows
-    int64_t s = (592 + units - 1) / units;
+    // enough CTAs for several waves over 148 SMs, but at least ~256 rows per CTA
+    int64_t s = (VQ_DECODE_TARGET_CTAS + ctas_per_split - 1) / ctas_per_split;
     int64_t cap = (static_cast<int64_t>(n_valid) + MK + 255) / 256;
     if (s > cap) s = cap;
     if (s > kDecMaxSplits) s = kDecMaxSplits;
@@ -328,7 +207,9 @@ extern "C" size_t vqattn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t H
 {
     (void)Hkv;
     const size_t tickets = (static_cast<size_t>(B) * Hq * sizeof(int) + 255) / 256 * 256;
-    return tickets + static_cast<size_t>(B) * Hq * vq::kDecMaxSplits * (D + 2) * sizeof(float);
+    const size_t split_kernel = tickets + static_cast<size_t>(B) * Hq * vq::kDecMaxSplits * (D + 2) * sizeof(float);
+    const size_t stream_kernel = vq::decode_bulk_workspace_bytes(B * Hq, 4, D);
+    return split_kernel > stream_kernel ? split_kernel : stream_kernel;
 }
 
 extern "C" int vqattn_decode(const VqDecodeArgs *a, void *stream)
@@ -405,25 +286,26 @@ extern "C" int vqattn_decode(const VqDecodeArgs *a, void *stream)
     p.v_sb = a->v_win.stride[0]; p.v_sh = a->v_win.stride[1]; p.v_sl = a->v_win.stride[2];
     p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv); p.G = G; p.MK = static_cast<int>(MK);
     p.n_valid = static_cast<int>(a->n_valid); p.n_bd = static_cast<int>(a->n_bd); p.use_far = far ? 1 : 0;
-    p.splits = pick_splits(B * Hkv, p.n_valid, p.MK);
-    p.rows_w = (p.n_valid + p.splits - 1) / p.splits;
-    p.rows_f = far ? (p.MK + p.splits - 1) / p.splits : 0;
+    p.splits = pick_splits(B * Hkv * (G / GH), p.n_valid, p.MK);
+    // rows per split, rounded to whole 32-row tiles (keeps every tile copy 16-byte aligned)
+    p.rows_w = ((p.n_valid + p.splits - 1) / p.splits + 31) / 32 * 32;
+    p.rows_f = far ? ((p.MK + p.splits - 1) / p.splits + 31) / 32 * 32 : 0;
     const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(D));
     p.scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = sizeof(float) * (static_cast<size_t>(2 * GH * D) + static_cast<size_t>(GH) * (p.rows_w + p.rows_f) +
-                                         static_cast<size_t>(kDecThreads / 32) * GH * D);
-    if (smem > 200 * 1024) return VQ_EUNSUPPORTED;
     dim3 grid(static_cast<unsigned>(p.splits), static_cast<unsigned>(G / GH), static_cast<unsigned>(B * Hkv));
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool cb32 = far ? a->codebook.dtype == VQ_F32 : dt == VQ_F32;
+    // bf16 caches with dense rows take the bulk-copy kernel; anything else the register-streaming one
+    const bool dense_rows = a->k1_win.stride[2] == D && a->k3_win.stride[2] == D && a->v_win.stride[2] == D &&
+                            a->q1.stride[1] == D && a->q2.stride[1] == D && a->q1.stride[0] % 8 == 0 && a->q2.stride[0] % 8 == 0 &&
+                            reinterpret_cast<uintptr_t>(a->q1.ptr) % 16 == 0 && reinterpret_cast<uintptr_t>(a->q2.ptr) % 16 == 0;
+    if (dt == VQ_BF16 && dense_rows)
+        return launch_decode_bulk(p, B * Hkv, static_cast<int>(D), GH, far && cb32, a->workspace, a->workspace_bytes,
+                                  a->status_word, s);
 
 #define VQ_DEC(T, TC, DD, GG)                                                                                   \
     do {                                                                                                         \
-        auto kern = decode_kernel<T, TC, DD, GG>;                                                                \
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=  \
-            cudaSuccess)                                                                                         \
-            return VQ_ELAUNCH;                                                                                   \
-        kern<<<grid, kDecThreads, smem, s>>>(p);                                                                 \
+        decode_kernel<T, TC, DD, GG><<<grid, kDecThreads, 0, s>>>(p);                                            \
         return launch_status();                                                                                  \
     } while (0)
 #define VQ_DEC_G(T, TC, DD)                     \

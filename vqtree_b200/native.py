@@ -6,11 +6,13 @@ module raises at import time - there is no fallback implementation.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libvqattn.so"
+# VQATTN_LIB overrides the location of the shared library (e.g. an out-of-tree build of the same sources)
+_LIB_PATH = Path(os.environ.get("VQATTN_LIB") or Path(__file__).resolve().parent / "lib" / "libvqattn.so")
 
 MAX_DIMS = 5
 BLOCK = 128
@@ -62,6 +64,7 @@ class VqDecodeArgs(ctypes.Structure):
         ("scale", ctypes.c_float),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
+        ("status_word", ctypes.c_void_p),
     ]
 
 
