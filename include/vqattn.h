@@ -56,8 +56,9 @@ typedef struct VqTensorDesc {
     int32_t device;
 } VqTensorDesc;
 
-/* Which prefill kernel to run; AUTO picks the tensor-core kernel for bf16 and the fp32 kernel for f32. */
-typedef enum VqPrefillImpl { VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2 } VqPrefillImpl;
+/* Which prefill kernel to run; AUTO picks the pipelined tensor-core kernel for bf16 and the fp32
+ * kernel for f32.  TENSOR_SERIAL is the non-pipelined tensor-core kernel (same arithmetic). */
+typedef enum VqPrefillImpl { VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2, VQ_IMPL_TENSOR_SERIAL = 3 } VqPrefillImpl;
 
 int vqattn_version(void);
 const char *vqattn_status_string(int status);

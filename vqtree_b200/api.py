@@ -16,7 +16,8 @@ import torch
 from . import native
 from .native import BLOCK, VqDecodeArgs, VqPrefillArgs, check, desc, lib, stream_ptr
 
-_IMPL = {"auto": native.IMPL_AUTO, "simt": native.IMPL_SIMT, "tensor": native.IMPL_TENSOR}
+_IMPL = {"auto": native.IMPL_AUTO, "simt": native.IMPL_SIMT, "tensor": native.IMPL_TENSOR,
+         "tensor_serial": native.IMPL_TENSOR_SERIAL}
 
 
 def _require_cuda(*ts):

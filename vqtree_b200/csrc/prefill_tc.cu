@@ -14,29 +14,13 @@
 // tcgen05.ld (one thread = one query row), apply mask / max / exp2, write P back to tensor memory
 // as packed bf16, rescale the accumulator O when the row maximum moved, and a second tcgen05.mma
 // (A = P from tensor memory, B = V tile, MN-major) adds P V into O.
-#include "tc_ptx.cuh"
-#include "vq_common.cuh"
+#include "prefill_tc_common.cuh"
 
 namespace vq {
 
 using namespace ptx;
 
 constexpr int kTcThreads = 128;
-constexpr int kHalfBytes = kBlock * 64 * 2;  // one TMA box: 128 rows x 64 bf16 (128 B per row)
-
-enum ItemKind : int { kFar = 0, kBdA = 1, kBdB = 2, kFull = 3, kDiag = 4 };
-
-struct TcParams {
-    int Hq, Hkv, NB, MK, rerope, ntiles;
-    int64_t L;
-    int wblocks;  // window / 128
-    float scale_log2;
-    const float *cnt;  // [B*Hkv, NB, MK]
-    __nv_bfloat16 *out;
-    int64_t o_sb, o_sh, o_sl;
-    float *lse2;
-    int32_t *status;
-};
 
 // TMEM column map: S fp32 [0,128), P bf16x2 [128,192), O fp32 [kColO, kColO+D)
 constexpr uint32_t kColS = 0, kColP = 128;
@@ -79,30 +63,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_consta
     const int hk = hq / (p.Hq / p.Hkv);
     const int u = b * p.Hkv + hk;
 
-    // ---- work list of this tile ----
-    const int kb0 = m - p.wblocks;                        // boundary block (exists when >= 0)
-    const bool has_far = kb0 >= 1 && p.MK > 0;
-    const int far_blk = kb0 - 1;
-    const int n_far = has_far ? p.MK / kBlock : 0;
-    const int n_bd = (kb0 >= 0) ? (p.rerope ? 2 : 1) : 0;
-    const int first_full = kb0 >= 0 ? kb0 + 1 : 0;
-    const int n_full = m - first_full;                    // interior blocks
-    const int n_items = n_far + n_bd + n_full + 1;
-
-    auto item_kind = [&](int it) -> int {
-        if (it < n_far) return kFar;
-        it -= n_far;
-        if (it < n_bd) return p.rerope ? (it == 0 ? kBdA : kBdB) : kFull;
-        it -= n_bd;
-        return it < n_full ? kFull : kDiag;
-    };
-    auto item_block = [&](int it) -> int {  // far: codebook tile index; local: key block index
-        if (it < n_far) return it;
-        it -= n_far;
-        if (it < n_bd) return kb0;
-        it -= n_bd;
-        return first_full + it;
-    };
+    const TcWork work(p, m);
+    const int n_items = work.n_items, far_blk = work.far_blk;
+    auto item_kind = [&](int it) -> int { return work.kind(it); };
+    auto item_block = [&](int it) -> int { return work.block(it); };
 
     if (tid == 0) {
         mbar_init(&bar_q, 1);
@@ -319,98 +283,26 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_consta
     }
 }
 
-// ------------------------------------------------------------------------------------------ host side
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void *sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
-// bf16 tensor with up to 4 dims given innermost-first; box = 64 x 128 (x 1 x 1), 128-byte swizzle.
-static bool make_map(CUtensorMap *out, const void *ptr, int rank, const uint64_t *dims, const uint64_t *strides_elems)
-{
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return false;
-    cuuint64_t gdim[4], gstride[3];
-    cuuint32_t box[4], estr[4];
-    for (int i = 0; i < rank; ++i) {
-        gdim[i] = dims[i];
-        box[i] = i == 0 ? 64 : (i == 1 ? kBlock : 1);
-        estr[i] = 1;
-        if (i > 0) gstride[i - 1] = strides_elems[i] * 2;
-    }
-    return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(ptr), gdim, gstride, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-static bool map_bhld(CUtensorMap *out, const VqTensorDesc &t)
-{
-    const uint64_t dims[4] = {static_cast<uint64_t>(t.shape[3]), static_cast<uint64_t>(t.shape[2]),
-                              static_cast<uint64_t>(t.shape[1]), static_cast<uint64_t>(t.shape[0])};
-    const uint64_t str[4] = {1, static_cast<uint64_t>(t.stride[2]), static_cast<uint64_t>(t.stride[1]),
-                             static_cast<uint64_t>(t.stride[0])};
-    return make_map(out, t.ptr, 4, dims, str);
-}
-
 template <int D>
 static int launch_tc(const VqPrefillArgs *a, cudaStream_t stream)
 {
     using SM = TcSmem<D>;
-    const int64_t B = a->q1.shape[0], Hq = a->q1.shape[1], L = a->q1.shape[2], Hkv = a->k1.shape[1];
-    const bool far = a->codebook.ptr != nullptr && a->cnt.ptr != nullptr;
-    CUtensorMap mq1, mq2, mk1, mk3, mv, mcb, mvs;
-    if (!map_bhld(&mq1, a->q1) || !map_bhld(&mq2, a->q2) || !map_bhld(&mk1, a->k1) || !map_bhld(&mk3, a->k3) ||
-        !map_bhld(&mv, a->v))
-        return VQ_ELAUNCH;
-    TcParams p{};
-    if (far) {
-        const uint64_t MK = a->codebook.shape[1], NB = a->cnt.shape[2];
-        const uint64_t cd[3] = {static_cast<uint64_t>(D), MK, static_cast<uint64_t>(Hkv)};
-        const uint64_t cs[3] = {1, static_cast<uint64_t>(D), MK * D};
-        const uint64_t vd[3] = {static_cast<uint64_t>(D), MK, static_cast<uint64_t>(B * Hkv) * NB};
-        if (!make_map(&mcb, a->codebook.ptr, 3, cd, cs) || !make_map(&mvs, a->vsum.ptr, 3, vd, cs)) return VQ_ELAUNCH;
-        p.MK = static_cast<int>(MK);
-        p.NB = static_cast<int>(NB);
-        p.cnt = static_cast<const float *>(a->cnt.ptr);
-    } else {
-        mcb = mk1;  // never dereferenced: the work list has no far items
-        mvs = mv;
-    }
-    p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv);
-    p.L = L;
-    p.ntiles = static_cast<int>((L + kBlock - 1) / kBlock);
-    p.wblocks = static_cast<int>(a->window / kBlock);
-    p.rerope = (a->q2.ptr != a->q1.ptr || a->k3.ptr != a->k1.ptr) ? 1 : 0;
-    const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(D));
-    p.scale_log2 = scale * 1.4426950408889634f;
-    p.out = static_cast<__nv_bfloat16 *>(a->out.ptr);
-    p.o_sb = a->out.stride[0]; p.o_sh = a->out.stride[1]; p.o_sl = a->out.stride[2];
-    p.lse2 = static_cast<float *>(a->lse2.ptr);
-    p.status = a->status_word;
+    TcMaps m;
+    TcParams p;
+    const int st = tc_setup<D>(a, m, p);
+    if (st != VQ_OK) return st;
     auto kern = prefill_tc_kernel<D>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal) != cudaSuccess) return VQ_ELAUNCH;
-    dim3 grid(static_cast<unsigned>(p.ntiles), static_cast<unsigned>(B * Hq));
-    kern<<<grid, kTcThreads, SM::kTotal, stream>>>(mq1, mq2, mk1, mk3, mv, mcb, mvs, p);
+    dim3 grid(static_cast<unsigned>(p.ntiles), static_cast<unsigned>(a->q1.shape[0] * a->q1.shape[1]));
+    kern<<<grid, kTcThreads, SM::kTotal, stream>>>(m.q1, m.q2, m.k1, m.k3, m.v, m.cb, m.vs, p);
     return launch_status();
 }
 
-int launch_prefill_tensor(const VqPrefillArgs *a, cudaStream_t stream)
+// The serial form: one warpgroup does MMA issue, softmax and rescaling in turn (kept as a second
+// implementation of the same arithmetic; the pipelined kernel is the default).
+int launch_prefill_tensor_serial(const VqPrefillArgs *a, cudaStream_t stream)
 {
     const int D = static_cast<int>(a->q1.shape[3]);
-    // 16-byte aligned rows for the output stores and the tensor maps
     if (a->out.stride[2] % 8 || a->out.stride[1] % 8 || a->out.stride[0] % 8) return VQ_EINVAL_STRIDE;
     return D == 64 ? launch_tc<64>(a, stream) : launch_tc<128>(a, stream);
 }
