@@ -6,12 +6,13 @@
 // memory and its own running (max, denominator); the streams are merged once at the end (this is
 // the single online softmax that replaces the reference's two kernels and its log-sum-exp merge,
 // ops/triton_fused_vq_attn.py:202-250).  Roles:
-//   warps 0-3 / 4-7  softmax of stream 0 / 1: one thread per query row reads S with tcgen05.ld,
-//                    masks, exponentiates, writes P (packed bf16) over S, rescales O only when the
-//                    row maximum grew by more than 2^8 (lazy rescaling), and does the epilogue;
-//   warp 8           one thread issues every tcgen05.mma: S = Q K^T (operands in shared memory),
+//   warps 0-7 / 8-15 softmax of stream 0 / 1: TWO threads per query row (64 key columns each) read
+//                    S with tcgen05.ld, mask, agree on the row maximum through shared memory,
+//                    exponentiate, write P (packed bf16) over S, rescale their half of O only when
+//                    the maximum grew by more than 2^8 (lazy rescaling), and do the epilogue;
+//   warp 16          one thread issues every tcgen05.mma: S = Q K^T (operands in shared memory),
 //                    O += P V (P from tensor memory, V MN-major in shared memory);
-//   warp 9           one thread issues the TMA tile loads into a ring of 32 KB slots, in the order
+//   warp 17          one thread issues the TMA tile loads into a ring of 32 KB slots, in the order
 //                    the tensor pipe consumes them (K0 K1 V0 K2 V1 K3 ...).
 // While stream 0 runs its softmax the tensor pipe works for stream 1 and vice versa.
 // Hand-offs are mbarriers (tcgen05.commit arrives for the MMA side); every wait is bounded and a
@@ -22,7 +23,8 @@ namespace vq {
 
 using namespace ptx;
 
-constexpr int kT2Threads = 320;
+constexpr int kT2Threads = 576;   // 16 softmax warps + MMA warp + TMA warp
+constexpr int kWarpMma = 16, kWarpTma = 17;
 constexpr float kLazyThreshold = 8.f;  // log2 units: P stays below 2^8, exact in fp32, fine in bf16
 
 template <int D>
@@ -37,34 +39,43 @@ struct T2Cfg {
     static constexpr uint32_t kCols = 512;
 };
 
-// Softmax of one 128-column work item for this thread's row.  MODE 0: no mask; 1: columns
-// [lo,hi) valid; 2: far tile - column c valid iff cw[c] > 0 and the denominator is weighted by cw[c].
-// s_addr / o_addr: this warp's lanes at the first column of S (P is written over its first 64
-// columns) and of O.  Two passes over S in tensor memory keep the register footprint small.
+// Softmax of one work item for one HALF row: this thread owns 64 of the 128 key columns of its
+// query row, its partner (same lane, warp + 4) the other 64.  MODE 0: no mask; 1: columns [lo,hi)
+// valid (lo/hi relative to this half); 2: far tile - column c valid iff cw[c] > 0, denominator
+// weighted by cw[c] (cw already offset to this half).
+//   s_addr  this warp's lanes at this half's first S column      p_addr  where its 32 packed P columns go (= s_addr)
+//   o_addr  this warp's lanes at this half's first O column (it rescales D/2 columns of O)
+//   xch     shared float[2] of this row: partial maxima of the two halves; pub/pub_val: optional
+//           extra shared word published before the barrier (the next far tile's count)
+// P (32 packed columns per half) is written over the half's own S columns only, so the two
+// threads of a row never touch each other's columns; S is read twice (maximum, then exponentials).
 template <int D, int MODE>
-__device__ __forceinline__ void softmax_item(uint32_t s_addr, uint32_t o_addr, bool rescale_o, const float *__restrict__ cw,
-                                             int lo, int hi, float scale_log2, float &row_m, float &row_l)
+__device__ __forceinline__ void softmax_half(uint32_t s_addr, uint32_t p_addr, uint32_t o_addr, bool rescale_o,
+                                             const float *__restrict__ cw, int lo, int hi, float scale_log2, float &row_m,
+                                             float &row_l, float *xch, int hf, int bar_id, float *pub, float pub_val)
 {
     auto masked = [&](float x, int c) -> float {
         if (MODE == 2) return cw[c] > 0.f ? x : -INFINITY;
         if (MODE == 1) return (c >= lo && c < hi) ? x : -INFINITY;
         return x;
     };
-    // pass 1: row maximum over the 128 columns (two 64-column reads of S)
+    // pass 1: partial row maximum over this half's 64 columns
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int hb = 0; hb < 2; ++hb) {
-        uint32_t r[2][32];
-        tmem_ld32(s_addr + 64 * hb, r[0]);
-        tmem_ld32(s_addr + 64 * hb + 32, r[1]);
+    {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(s_addr, r0);
+        tmem_ld32(s_addr + 32, r1);
         tc_wait_ld();
 #pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2)
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                mx4[j & 3] = fmaxf(mx4[j & 3], masked(__uint_as_float(r[c2][j]), 64 * hb + 32 * c2 + j));
+        for (int j = 0; j < 32; ++j) {
+            mx4[j & 3] = fmaxf(mx4[j & 3], masked(__uint_as_float(r0[j]), j));
+            mx4[j & 3] = fmaxf(mx4[j & 3], masked(__uint_as_float(r1[j]), 32 + j));
+        }
     }
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    xch[hf] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    if (pub != nullptr) *pub = pub_val;
+    asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+    const float mx = fmaxf(xch[0], xch[1]);
     // lazy rescaling: keep the old reference maximum unless the new one is far above it
     const float m_tile = mx * scale_log2;
     float m_use = row_m;
@@ -74,7 +85,7 @@ __device__ __forceinline__ void softmax_item(uint32_t s_addr, uint32_t o_addr, b
     if (rescale_o && __any_sync(0xffffffffu, alpha != 1.f)) {
         // O of this stream is idle here: its last product finished before S was handed over
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 64; ++c) {
             uint32_t r[32];
             tmem_ld32(o_addr + 32 * c, r);
             tc_wait_ld();
@@ -83,11 +94,12 @@ __device__ __forceinline__ void softmax_item(uint32_t s_addr, uint32_t o_addr, b
             tmem_st32(o_addr + 32 * c, r);
         }
     }
-    // pass 2: P = exp2(S*scale - m) as packed bf16 over the first 64 columns of S.  Chunk c reads
-    // columns [32c, 32c+32) and writes [16c, 16c+16): never ahead of what has been read.
+    // pass 2: P = exp2(S*scale - m) as packed bf16 over the first 32 of this half's own 64 columns.
+    // Chunk c reads columns [32c, 32c+32) and writes [16c, 16c+16): never ahead of what has been read,
+    // and never inside the partner's columns.
     float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
         uint32_t r[32], pk[16];
         tmem_ld32(s_addr + 32 * c, r);
         tc_wait_ld();
@@ -105,7 +117,7 @@ __device__ __forceinline__ void softmax_item(uint32_t s_addr, uint32_t o_addr, b
             }
             pk[j] = pack_bf16(p0, p1);
         }
-        tmem_st16(s_addr + 16 * c, pk);
+        tmem_st16(p_addr + 16 * c, pk);
     }
     row_l = row_l * alpha + (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
     row_m = m_use;
@@ -126,7 +138,8 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
     __shared__ __align__(16) float s_cnt[2][2][kBlock];  // [stream][item parity][code]: counts of a far tile
-    __shared__ float s_ml[2][kBlock][2];
+    __shared__ float s_xch[2][kBlock][2];                // [stream][row][half]: partial row maxima of an item
+    __shared__ float s_m[2][kBlock], s_l[2][2][kBlock];  // final (max, partial denominators) per stream / half
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m = p.ntiles - 1 - static_cast<int>(blockIdx.x);  // heavy tiles first
@@ -145,13 +158,13 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 128);
+            mbar_init(&p_full[i], 256);
             mbar_init(&o_done[i], 1);
         }
         fence_mbar_init();
         s_err = 0;
     }
-    if (warp == 9) {
+    if (warp == kWarpTma) {
         __syncwarp();
         tmem_alloc(&s_tmem, C::kCols);
         tmem_relinquish();
@@ -161,7 +174,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     tc_fence_after();
     const uint32_t tmem = s_tmem;
 
-    if (warp == 9) {
+    if (warp == kWarpTma) {
         // ================================================================== TMA producer
         if (lane == 0) {
             prefetch_tmap(&tm_q1); prefetch_tmap(&tm_k1); prefetch_tmap(&tm_v);
@@ -203,7 +216,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             }
             if (!ok) s_err = 1;
         }
-    } else if (warp == 8) {
+    } else if (warp == kWarpMma) {
         // ================================================================== MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_bf16(128, 128, 0, 0);
@@ -247,7 +260,8 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
                 const uint32_t psrc = tmem + (s ? C::kColS1 : C::kColS0);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)
-                    mma_ts(odst, psrc + 8 * kk, smem_desc_sw128(va + kk * 2048, kHalfBytes, 1024), idesc_pv,
+                    mma_ts(odst, psrc + (kk < 4 ? 8 * kk : 64 + 8 * (kk - 4)),  // keys 0-63 at columns 0.., keys 64-127 at columns 64..
+                           smem_desc_sw128(va + kk * 2048, kHalfBytes, 1024), idesc_pv,
                            ((it >> 1) | kk) ? 1u : 0u);
                 tc_commit(&kv_empty[slot]);
                 if (it + 2 >= n) tc_commit(&o_done[s]);  // last product of this stream
@@ -263,39 +277,48 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         }
     } else {
         // ================================================================== softmax streams
-        const int s = warp >> 2;                       // stream 0 / 1
-        const int row = tid & 127;                     // query row inside the tile (= TMEM lane)
+        const int s = warp >> 3;                       // stream 0 / 1
+        const int hf = (warp >> 2) & 1;                // which 64 key columns of the row
+        const int row = (warp & 3) * 32 + lane;        // query row inside the tile (= TMEM lane)
         const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t col_s = s ? C::kColS1 : C::kColS0, col_o = s ? C::kColO1 : C::kColO0;
+        const uint32_t s_addr = tmem + lane_off + col_s + 64 * hf, p_addr = s_addr;  // P of a half goes over that half's own S columns
+        const uint32_t o_addr = tmem + lane_off + col_o + hf * (D / 2);
+        const int bar_id = 2 + s;
         float row_m = -INFINITY, row_l = 0.f;          // row_m: the maximum P is currently scaled by
         bool ok = true;
-        // far tiles are items 0..n_far-1: this thread fetches count `row` of its stream's first far tile
-        float cnt_next = 0.f;
-        if (s < work.n_far) cnt_next = __ldg(p.cnt + (static_cast<int64_t>(u) * p.NB + work.far_blk) * p.MK + s * kBlock + row);
+        // Counts of far tiles (items 0..n_far-1) reach the stream through shared memory: the hf == 0
+        // thread of row r fetches count r of the tile two items ahead and publishes it before the
+        // item's barrier; the first tile's counts are published up front.
+        const float *cnt_base = p.cnt + (static_cast<int64_t>(u) * p.NB + work.far_blk) * p.MK;
+        if (s < work.n_far) {
+            if (hf == 0) s_cnt[s][0][row] = __ldg(cnt_base + s * kBlock + row);
+            asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
+        }
         for (int it = s; it < n && ok; it += 2) {
             const int kind = work.kind(it);
-            if (!mbar_wait(&s_full[s], (it >> 1) & 1)) {
+            const int par = (it >> 1) & 1;
+            float cnt_next = 0.f;
+            float *pub = nullptr;
+            if (hf == 0 && it + 2 < work.n_far) {
+                cnt_next = __ldg(cnt_base + (it + 2) * kBlock + row);
+                pub = &s_cnt[s][par ^ 1][row];
+            }
+            if (!mbar_wait(&s_full[s], par)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            const float *cw = &s_cnt[s][(it >> 1) & 1][0];
-            if (kind == kFar) {
-                // publish this thread's prefetched count of the tile to the stream's warps
-                s_cnt[s][(it >> 1) & 1][row] = cnt_next;
-                asm volatile("bar.sync %0, 128;" ::"r"(2 + s) : "memory");
-            }
-            // prefetch the count this thread contributes to the stream's next far tile
-            if (it + 2 < work.n_far)
-                cnt_next = __ldg(p.cnt + (static_cast<int64_t>(u) * p.NB + work.far_blk) * p.MK + (it + 2) * kBlock + row);
-            int lo = 0, hi = kBlock;                   // valid key columns of this row: [lo, hi)
-            if (kind == kDiag) hi = row + 1;
-            else if (kind == kBdA) hi = row;
-            else if (kind == kBdB) lo = row;
-            const uint32_t s_addr = tmem + lane_off + col_s, o_addr = tmem + lane_off + col_o;
-            if (kind == kFar) softmax_item<D, 2>(s_addr, o_addr, it >= 2, cw, lo, hi, p.scale_log2, row_m, row_l);
-            else if (kind == kFull) softmax_item<D, 0>(s_addr, o_addr, it >= 2, cw, lo, hi, p.scale_log2, row_m, row_l);
-            else softmax_item<D, 1>(s_addr, o_addr, it >= 2, cw, lo, hi, p.scale_log2, row_m, row_l);
+            const float *cw = &s_cnt[s][par][64 * hf];
+            // valid key columns of this row, relative to this half: [lo, hi)
+            int lo = 0, hi = 64;
+            if (kind == kDiag) hi = row + 1 - 64 * hf;
+            else if (kind == kBdA) hi = row - 64 * hf;
+            else if (kind == kBdB) lo = row - 64 * hf;
+            float *xch = &s_xch[s][row][0];
+            if (kind == kFar) softmax_half<D, 2>(s_addr, p_addr, o_addr, it >= 2, cw, lo, hi, p.scale_log2, row_m, row_l, xch, hf, bar_id, pub, cnt_next);
+            else if (kind == kFull) softmax_half<D, 0>(s_addr, p_addr, o_addr, it >= 2, cw, lo, hi, p.scale_log2, row_m, row_l, xch, hf, bar_id, pub, cnt_next);
+            else softmax_half<D, 1>(s_addr, p_addr, o_addr, it >= 2, cw, lo, hi, p.scale_log2, row_m, row_l, xch, hf, bar_id, pub, cnt_next);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(&p_full[s]);
@@ -304,49 +327,52 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         const int my_items = (n - s + 1) / 2;
         if (ok && my_items > 0 && !mbar_wait(&o_done[s], 0)) ok = false;
         tc_fence_after();
-        s_ml[s][row][0] = row_m;
-        s_ml[s][row][1] = (ok && my_items > 0) ? row_l : 0.f;
+        if (hf == 0) s_m[s][row] = row_m;
+        s_l[s][hf][row] = (ok && my_items > 0) ? row_l : 0.f;
         if (!ok) s_err = 1;
-        asm volatile("bar.sync 1, 256;" ::: "memory");   // the 256 softmax threads
+        asm volatile("bar.sync 1, 512;" ::: "memory");   // the 512 softmax threads
         tc_fence_after();
         if (!s_err) {
-            const float m0 = s_ml[0][row][0], l0 = s_ml[0][row][1], m1 = s_ml[1][row][0], l1 = s_ml[1][row][1];
+            const float m0 = s_m[0][row], l0 = s_l[0][0][row] + s_l[0][1][row];
+            const float m1 = s_m[1][row], l1 = s_l[1][0][row] + s_l[1][1][row];
             const float mm = fmaxf(l0 > 0.f ? m0 : -INFINITY, l1 > 0.f ? m1 : -INFINITY);
             const float e0 = l0 > 0.f ? ex2(m0 - mm) : 0.f, e1 = l1 > 0.f ? ex2(m1 - mm) : 0.f;
             const float den = l0 * e0 + l1 * e1;
             const float f0 = e0 / den, f1 = e1 / den;
             const int64_t grow = static_cast<int64_t>(m) * kBlock + row;
             __nv_bfloat16 *o = p.out + b * p.o_sb + hq * p.o_sh + grow * p.o_sl;
-            // stream s's warps write the column half [s*D/2, (s+1)*D/2) of every row
-            constexpr int HC = D / 2;
-#pragma unroll
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t r0[32], r1[32];
-                __syncwarp();
-                const int col = s * HC + 32 * c;
+            // thread (stream s, half hf) writes the column quarter [(2s+hf)*D/4, +D/4) of its row
+            constexpr int QC = D / 4;
+            const int col = (2 * s + hf) * QC;
+            uint32_t r0[QC], r1[QC];
+            __syncwarp();
+            if constexpr (QC == 32) {
                 tmem_ld32(tmem + lane_off + C::kColO0 + col, r0);
                 tmem_ld32(tmem + lane_off + C::kColO1 + col, r1);
-                tc_wait_ld();
-                if (grow < p.L) {
+            } else {
+                tmem_ld16(tmem + lane_off + C::kColO0 + col, r0);
+                tmem_ld16(tmem + lane_off + C::kColO1 + col, r1);
+            }
+            tc_wait_ld();
+            if (grow < p.L) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float x[8];
+                for (int j = 0; j < QC / 8; ++j) {
+                    float x[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const float a0 = l0 > 0.f ? __uint_as_float(r0[8 * j + e]) * f0 : 0.f;
-                            const float a1 = l1 > 0.f ? __uint_as_float(r1[8 * j + e]) * f1 : 0.f;
-                            x[e] = a0 + a1;
-                        }
-                        uint4 w;
-                        w.x = pack_bf16(x[0], x[1]);
-                        w.y = pack_bf16(x[2], x[3]);
-                        w.z = pack_bf16(x[4], x[5]);
-                        w.w = pack_bf16(x[6], x[7]);
-                        *reinterpret_cast<uint4 *>(o + col + 8 * j) = w;
+                    for (int e = 0; e < 8; ++e) {
+                        const float a0 = l0 > 0.f ? __uint_as_float(r0[8 * j + e]) * f0 : 0.f;
+                        const float a1 = l1 > 0.f ? __uint_as_float(r1[8 * j + e]) * f1 : 0.f;
+                        x[e] = a0 + a1;
                     }
+                    uint4 w;
+                    w.x = pack_bf16(x[0], x[1]);
+                    w.y = pack_bf16(x[2], x[3]);
+                    w.z = pack_bf16(x[4], x[5]);
+                    w.w = pack_bf16(x[6], x[7]);
+                    *reinterpret_cast<uint4 *>(o + col + 8 * j) = w;
                 }
             }
-            if (s == 0 && p.lse2 && grow < p.L) p.lse2[static_cast<int64_t>(bh) * p.L + grow] = mm + log2f(den);
+            if (s == 0 && hf == 0 && p.lse2 && grow < p.L) p.lse2[static_cast<int64_t>(bh) * p.L + grow] = mm + log2f(den);
         }
     }
     tc_fence_before();
@@ -357,7 +383,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
     }
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kWarpTma) {
         __syncwarp();
         tmem_dealloc(tmem, C::kCols);
     }
