@@ -156,6 +156,24 @@ size_t vqattn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t
 int vqattn_decode(const VqDecodeArgs *args, void *stream);
 
 /*
+ * vqattn_decode for hosts that cannot supply a workspace (no counterpart in the reference, which
+ * lets PyTorch allocate freely): a server whose memory plan gives all spare HBM to its KV-cache pool,
+ * or a runtime that forbids device allocation inside the serving step.  Same arguments and result as
+ * vqattn_decode; `workspace` / `workspace_bytes` are ignored and the scratch is a fixed array of
+ * vqattn_decode_static_capacity() bytes (16 MiB) inside the library, resident on every GPU that loads
+ * it until the process exits.  The call allocates nothing, on the device or through any library.
+ * Limits and rules:
+ *   - returns VQ_EWORKSPACE when vqattn_decode_workspace_bytes(B,Hq,Hkv,D) exceeds the capacity;
+ *   - the first call on a device looks up the array's device address (with that device current);
+ *     make that first call before any stream capture begins on the device;
+ *   - every call on a device shares the one array: calls whose kernels could overlap on the GPU
+ *     (different streams, different host threads) race on it - issue them on one stream, or use
+ *     vqattn_decode with separate workspaces.
+ */
+size_t vqattn_decode_static_capacity(void);
+int vqattn_decode_static(const VqDecodeArgs *args, void *stream);
+
+/*
  * Cache advance: folds `n_new` (a multiple of 128 is not required) keys that cross the boundary
  * into the running aggregates of a decode cache.  Stands in for the unfinished
  * ops/attn_vq.py:128-165 VectorQuantizedReRoPECache.update.

@@ -167,16 +167,18 @@ def decode_workspace(B: int, Hq: int, Hkv: int, D: int, device) -> torch.Tensor:
 
 def vq_attention_decode(q1, q2, k1_win, k3_win, v_win, codebook, cnt, vsum, n_valid: Optional[int] = None, n_bd: int = 0,
                         scale: Optional[float] = None, workspace: Optional[torch.Tensor] = None,
-                        out: Optional[torch.Tensor] = None):
+                        out: Optional[torch.Tensor] = None, static_scratch: bool = False):
     """Single-query decode (seqlen_q == 1) over a window cache plus far aggregates.
 
     q1,q2 [B,Hq,D]; k1_win,k3_win,v_win [B,Hkv,Nwin,D]; codebook [Hkv,MK,D] (f32 or activation dtype) or None;
     cnt [B,Hkv,MK] f32; vsum [B,Hkv,MK,D].
+    static_scratch=True uses ``vqattn_decode_static``: the merge scratch is a fixed 16 MiB array inside
+    the library, for hosts that cannot supply a workspace; one such call at a time per device.
     """
     dev = _require_cuda(q1, q2, k1_win, k3_win, v_win, codebook, cnt, vsum)
     B, Hq, D = q1.shape
     Hkv, Nwin = k1_win.shape[1], k1_win.shape[2]
-    if workspace is None:
+    if workspace is None and not static_scratch:
         workspace = decode_workspace(B, Hq, Hkv, D, dev)
     if out is None:
         out = torch.empty((B, Hq, D), dtype=q1.dtype, device=dev)
@@ -187,9 +189,14 @@ def vq_attention_decode(q1, q2, k1_win, k3_win, v_win, codebook, cnt, vsum, n_va
     a.n_bd = int(n_bd)
     a.use_far = 1 if codebook is not None else 0
     a.scale = float(scale) if scale else 0.0
+    a.status_word = device_status_word(dev).data_ptr()
+    if static_scratch:
+        # the library's built-in scratch array: nothing is allocated for this call (pass `out` too)
+        with torch.cuda.device(dev):
+            check(lib.vqattn_decode_static(ctypes.byref(a), stream_ptr(dev)), "vqattn_decode_static")
+        return out
     a.workspace = workspace.data_ptr()
     a.workspace_bytes = workspace.numel() * workspace.element_size()
-    a.status_word = device_status_word(dev).data_ptr()
     with torch.cuda.device(dev):
         check(lib.vqattn_decode(ctypes.byref(a), stream_ptr(dev)), "vqattn_decode")
     return out

@@ -13,6 +13,8 @@
 // (max, denominator, D/lanes output columns).  No block-wide barrier sits between loads.
 // The lane groups of a warp, then the warps (shared memory), then the splits (workspace; the last
 // CTA of a unit to finish takes an atomic ticket, merges and re-arms it) are merged at the end.
+#include <mutex>
+
 #include "decode_common.cuh"
 
 namespace vq {
@@ -327,4 +329,54 @@ extern "C" int vqattn_decode(const VqDecodeArgs *a, void *stream)
 #undef VQ_DEC_G
 #undef VQ_DEC
     return VQ_ELAUNCH;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode without a caller-provided workspace.
+//
+// Some hosts cannot hand this library a workspace buffer: an inference server that gives every free
+// byte of HBM to its KV-cache pool at start-up, or a runtime whose plugin contract forbids device
+// allocation once serving has begun, has nowhere to take the split/merge scratch of the decode kernel
+// from.  For them the scratch lives in the library image itself: one fixed array per GPU that loads
+// the library, held until the process exits.
+#define VQATTN_DECODE_STATIC_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_decode_static_scratch[VQATTN_DECODE_STATIC_BYTES];
+
+extern "C" size_t vqattn_decode_static_capacity(void) { return VQATTN_DECODE_STATIC_BYTES; }
+
+extern "C" int vqattn_decode_static(const VqDecodeArgs *a, void *stream)
+{
+    using namespace vq;
+    if (a == nullptr) return VQ_EINVAL_ARG;
+    if (a->q1.ndim != 3 || a->k1_win.ndim != 4) return VQ_EINVAL_SHAPE;
+    const int64_t B = a->q1.shape[0], Hq = a->q1.shape[1], D = a->q1.shape[2], Hkv = a->k1_win.shape[1];
+    if (B <= 0 || Hq <= 0 || D <= 0 || Hkv <= 0) return VQ_EINVAL_SHAPE;
+    // the built-in scratch has a fixed size: larger problems must use vqattn_decode with their own workspace
+    if (vqattn_decode_workspace_bytes(B, Hq, Hkv, D) > VQATTN_DECODE_STATIC_BYTES) return VQ_EWORKSPACE;
+
+    // In host code the array's name is only a handle; the device address is looked up once per
+    // device, with that device current, and cached.
+    static std::mutex mu;
+    static void *dev_ptr[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return VQ_EDEVICE;
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev_ptr[dev] == nullptr) {
+            void *ptr = nullptr;
+            if (cudaGetSymbolAddress(&ptr, g_decode_static_scratch) != cudaSuccess || ptr == nullptr) return VQ_ELAUNCH;
+            dev_ptr[dev] = ptr;
+        }
+        scratch = dev_ptr[dev];
+    }
+    // The array keeps whatever the last call left.  The merge tickets at its start must be zero when
+    // a launch begins (a call that was cut short could have left some raised), so clear them here.
+    const size_t tickets = (static_cast<size_t>(B) * Hq * sizeof(int) + 255) / 256 * 256;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(scratch, 0, tickets, s) != cudaSuccess) return VQ_ELAUNCH;
+    VqDecodeArgs b = *a;
+    b.workspace = scratch;
+    b.workspace_bytes = VQATTN_DECODE_STATIC_BYTES;
+    return vqattn_decode(&b, stream);
 }

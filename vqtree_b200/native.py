@@ -32,7 +32,7 @@ _DTYPES = {
 EXPORTS = (
     "vqattn_version", "vqattn_status_string", "vqattn_assign_codes", "vqattn_build_aggregates",
     "vqattn_gather_aggregates", "vqattn_prefill", "vqattn_decode_workspace_bytes", "vqattn_decode",
-    "vqattn_cache_advance",
+    "vqattn_cache_advance", "vqattn_decode_static_capacity", "vqattn_decode_static",
 )
 
 
@@ -88,10 +88,12 @@ def _load() -> ctypes.CDLL:
     lib.vqattn_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.vqattn_decode_workspace_bytes.argtypes = [ctypes.c_int64] * 4
     lib.vqattn_decode.argtypes = [P(VqDecodeArgs), ctypes.c_void_p]
+    lib.vqattn_decode_static.argtypes = [P(VqDecodeArgs), ctypes.c_void_p]
+    lib.vqattn_decode_static_capacity.restype = ctypes.c_size_t
     lib.vqattn_cache_advance.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc),
                                          P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
     for name in EXPORTS:
-        if name not in ("vqattn_status_string", "vqattn_decode_workspace_bytes"):
+        if name not in ("vqattn_status_string", "vqattn_decode_workspace_bytes", "vqattn_decode_static_capacity"):
             getattr(lib, name).restype = ctypes.c_int
     return lib
 
