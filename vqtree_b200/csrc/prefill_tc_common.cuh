@@ -77,8 +77,9 @@ inline EncodeTiledFn encode_fn()
     return fn;
 }
 
-// bf16 tensor with up to 4 dims given innermost-first; box = 64 x 128 (x 1 x 1), 128-byte swizzle.
-inline bool make_map(CUtensorMap *out, const void *ptr, int rank, const uint64_t *dims, const uint64_t *strides_elems)
+// bf16 tensor with up to 4 dims given innermost-first; box = 64 x box_rows (x 1 x 1), 128-byte swizzle.
+inline bool make_map(CUtensorMap *out, const void *ptr, int rank, const uint64_t *dims, const uint64_t *strides_elems,
+                     int box_rows = kBlock)
 {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
@@ -86,7 +87,7 @@ inline bool make_map(CUtensorMap *out, const void *ptr, int rank, const uint64_t
     cuuint32_t box[4], estr[4];
     for (int i = 0; i < rank; ++i) {
         gdim[i] = dims[i];
-        box[i] = i == 0 ? 64 : (i == 1 ? kBlock : 1);
+        box[i] = i == 0 ? 64 : (i == 1 ? box_rows : 1);
         estr[i] = 1;
         if (i > 0) gstride[i - 1] = strides_elems[i] * 2;
     }

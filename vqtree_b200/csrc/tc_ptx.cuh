@@ -107,9 +107,11 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 accumulation.
 // bits: c_format[4,6)=1(f32)  a_format[7,10)=1(bf16)  b_format[10,13)=1(bf16)  a_major[15]  b_major[16]
 //       n_dim[17,23)=N>>3  m_dim[24,29)=M>>4        (major: 0 = K-major, 1 = MN-major)
-__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major)
+//       a_negate[13]: multiply A by -1
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major, int a_negate = 0)
 {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_negate) << 13) |
+           (static_cast<uint32_t>(a_mn_major) << 15) |
            (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
            (static_cast<uint32_t>(M >> 4) << 24);
 }
@@ -180,6 +182,9 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+
+// generic-proxy writes to shared memory made visible to the async proxy (TMA / tcgen05 operand reads)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ float ex2(float x)
 {
