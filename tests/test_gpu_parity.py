@@ -251,3 +251,44 @@ def test_errors_are_reported_not_crashed(api):
     with pytest.raises(VqError) as e:
         api.prefill_from_aggregates(q, q, q, q, q, None, None, None, window=100)  # window % 128 != 0
     assert e.value.status == -7
+
+
+# ----------------------------------------------------------------------------- tensor-core assignment
+
+@pytest.mark.parametrize("B,Hkv,L,D,M,K", [
+    (1, 4, 2048, 128, 4, 256),     # config 2 shape, scaled down
+    (2, 2, 700, 128, 4, 512),      # config 4 codebooks (9-bit codes), ragged length
+    (1, 2, 1024, 128, 8, 256),     # config 5 codebooks
+    (1, 3, 515, 64, 2, 128),       # D = 64
+    (1, 1, 128, 128, 1, 64),       # single chunk
+])
+def test_assign_tensor_path_is_bit_exact(api, B, Hkv, L, D, M, K):
+    g = torch.Generator().manual_seed(77 + L + K + M)
+    k = torch.randn(B, Hkv, L, D, generator=g).bfloat16()
+    cb = torch.randn(Hkv, M, K, D, generator=g) * D ** -0.25
+    want = vo.assign_codes(k.float().numpy(), cb.numpy())
+    got = api.assign_codes(dev(k), dev(cb), out_dtype=torch.int32, impl="auto")
+    torch.cuda.synchronize()
+    api.check_status()
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+    simt = api.assign_codes(dev(k), dev(cb), out_dtype=torch.int32, impl="simt")
+    np.testing.assert_array_equal(simt.cpu().numpy(), want)
+
+
+def test_assign_tensor_path_ties_zero_keys_and_bias(api):
+    """Exact ties (duplicated codewords), all-zero keys, near-duplicates and a bias: the first maximum wins."""
+    g = torch.Generator().manual_seed(5150)
+    B, Hkv, L, D, M, K = 1, 2, 512, 128, 3, 128
+    k = torch.randn(B, Hkv, L, D, generator=g).bfloat16()
+    k[:, :, 10:20] = 0                                   # every score ties at zero
+    cb = torch.randn(Hkv, M, K, D, generator=g) * 0.3
+    cb[:, :, 64:96] = cb[:, :, 0:32]                      # exact duplicates: ties between c and c + 64
+    cb[:, :, 100] = cb[:, :, 7] * (1 + 2 ** -22)          # a near-duplicate, far inside the error bound
+    bias = torch.randn(Hkv, M, K, generator=g) * 0.1
+    bias[:, :, 64:96] = bias[:, :, 0:32]
+    for bs in (None, bias):
+        want = vo.assign_codes(k.float().numpy(), cb.numpy(), None if bs is None else bs.numpy())
+        got = api.assign_codes(dev(k), dev(cb), dev(bs), out_dtype=torch.int32)
+        torch.cuda.synchronize()
+        api.check_status()
+        np.testing.assert_array_equal(got.cpu().numpy(), want)

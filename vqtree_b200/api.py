@@ -58,7 +58,8 @@ def code_dtype_for(K: int) -> torch.dtype:
 
 
 def assign_codes(k: torch.Tensor, codebooks: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                 out_dtype: Optional[torch.dtype] = None, impl: str = "auto",
+                 workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Key -> code assignment (replaces ops/mini_vq.py:4-18; greedy residual for M > 1).
 
     k [B,Hkv,L,D] f32|bf16, codebooks [Hkv,M,K,D] f32, bias None|[Hkv,M,K] f32 -> codes [B,Hkv,L,M].
@@ -69,7 +70,15 @@ def assign_codes(k: torch.Tensor, codebooks: torch.Tensor, bias: Optional[torch.
     codes = torch.empty((B, Hkv, L, M), dtype=out_dtype or code_dtype_for(K), device=dev)
     with torch.cuda.device(dev):
         dk, dc, db, do = desc(k), desc(codebooks), desc(bias), desc(codes)
-        check(lib.vqattn_assign_codes(dk, dc, db if bias is not None else None, do, stream_ptr(dev)), "vqattn_assign_codes")
+        if impl == "simt":
+            check(lib.vqattn_assign_codes(dk, dc, db if bias is not None else None, do, stream_ptr(dev)), "vqattn_assign_codes")
+        else:
+            # tensor-core scoring + exact re-score where it applies (bf16 keys); same codes either way
+            need = lib.vqattn_assign_workspace_bytes(Hkv, M, K, k.shape[3])
+            if workspace is None or workspace.numel() < need:
+                workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+            check(lib.vqattn_assign_codes_ws(dk, dc, db if bias is not None else None, do, workspace.data_ptr(), workspace.numel(),
+                                             device_status_word(dev).data_ptr(), stream_ptr(dev)), "vqattn_assign_codes_ws")
     return codes
 
 

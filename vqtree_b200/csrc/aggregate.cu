@@ -4,7 +4,7 @@
 // For every 128-key block n the outputs describe the keys [0, 128(n+1)):
 //   cnt[n][r]  = number of keys whose code in codebook m is c   (r = m*K + c)
 //   vsum[n][r] = sum of their value rows, fp32, added in position order, stored in the output dtype.
-// One CTA owns (batch*kv-head, codebook m, a part of <= 256 codes, a 64-column slice of D), keeps
+// One CTA owns (batch*kv-head, codebook m, a part of <= 256 codes, a 32-column slice of D), keeps
 // the running fp32 sums of its rows in shared memory, walks the blocks in order and writes a
 // snapshot after each.  A row is always updated by the same thread in position order, so the
 // sums are deterministic and equal a scalar left-to-right loop.
@@ -13,7 +13,7 @@
 namespace vq {
 
 constexpr int kAggThreads = 256;
-constexpr int kAggCols = 64;    // D-slice per CTA
+constexpr int kAggCols = 32;    // D-slice per CTA
 constexpr int kAggRows = 256;   // code rows per CTA
 
 template <typename T> __device__ __forceinline__ float4 ld4(const T *p);
@@ -37,8 +37,26 @@ template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16 *p,
     *reinterpret_cast<uint2 *>(p) = raw;
 }
 
+template <typename T> __device__ __forceinline__ void st8(T *p, float4 x, float4 y);
+template <> __device__ __forceinline__ void st8<float>(float *p, float4 x, float4 y)
+{
+    *reinterpret_cast<float4 *>(p) = x;
+    *reinterpret_cast<float4 *>(p + 4) = y;
+}
+template <> __device__ __forceinline__ void st8<__nv_bfloat16>(__nv_bfloat16 *p, float4 x, float4 y)
+{
+    __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y), b = __floats2bfloat162_rn(x.z, x.w);
+    __nv_bfloat162 c = __floats2bfloat162_rn(y.x, y.y), d = __floats2bfloat162_rn(y.z, y.w);
+    uint4 raw;
+    raw.x = *reinterpret_cast<uint32_t *>(&a);
+    raw.y = *reinterpret_cast<uint32_t *>(&b);
+    raw.z = *reinterpret_cast<uint32_t *>(&c);
+    raw.w = *reinterpret_cast<uint32_t *>(&d);
+    *reinterpret_cast<uint4 *>(p) = raw;
+}
+
 template <typename TV, typename TO>
-__global__ void __launch_bounds__(kAggThreads)
+__global__ void __launch_bounds__(kAggThreads, 4)
 build_aggregates_kernel(const void *__restrict__ codes, int code_dtype, int64_t c_sb, int64_t c_sh, int64_t c_sl,
                         const TV *__restrict__ v, int64_t v_sb, int64_t v_sh, int64_t v_sl,
                         float *__restrict__ cnt,  // [B,Hkv,NB,MK] dense
@@ -46,8 +64,8 @@ build_aggregates_kernel(const void *__restrict__ codes, int code_dtype, int64_t 
                         int Hkv, int D, int M, int K, int NB, int parts, int rows_per_part)
 {
     extern __shared__ __align__(16) float smem[];
-    float *acc = smem;                               // [rows_per_part][64]
-    float *vt = smem + rows_per_part * kAggCols;     // [128][64]
+    float *acc = smem;                               // [rows_per_part][32]
+    float *vt = smem + rows_per_part * kAggCols;     // [128][32]
     __shared__ int s_code[kBlock];
     __shared__ int s_cnt[kAggRows];
 
@@ -64,43 +82,65 @@ build_aggregates_kernel(const void *__restrict__ codes, int code_dtype, int64_t 
 
     for (int i = tid; i < rows_per_part * kAggCols; i += kAggThreads) acc[i] = 0.f;
     for (int i = tid; i < kAggRows; i += kAggThreads) s_cnt[i] = 0;
-    __syncthreads();
 
     const int col = tid & (kAggCols - 1);
-    const int grp = tid / kAggCols;  // 4 groups; group g owns rows with (row & 3) == g
+    const int grp = tid / kAggCols;  // 8 groups; group g owns the code rows with (row & 7) == g
+    constexpr int kVecPerThread = kBlock * (kAggCols / 4) / kAggThreads;  // 4
+
+    // the next block's codes and value tile travel in registers while the current block is summed
+    float4 nv[kVecPerThread];
+    int ncode = -1;
+    auto fetch = [&](int n) {
+        const int64_t j0 = static_cast<int64_t>(n) * kBlock;
+        if (tid < kBlock) ncode = load_code(codes, code_dtype, b * c_sb + h * c_sh + (j0 + tid) * c_sl + m);
+#pragma unroll
+        for (int t = 0; t < kVecPerThread; ++t) {
+            const int i = tid + t * kAggThreads;
+            const int r = i / (kAggCols / 4), c4 = i % (kAggCols / 4);
+            nv[t] = ld4<TV>(v + b * v_sb + h * v_sh + (j0 + r) * v_sl + ds * kAggCols + 4 * c4);
+        }
+    };
+    if (NB > 0) fetch(0);
+    __syncthreads();
 
     for (int n = 0; n < NB; ++n) {
-        const int64_t j0 = static_cast<int64_t>(n) * kBlock;
         if (tid < kBlock) {
-            const int code = load_code(codes, code_dtype, b * c_sb + h * c_sh + (j0 + tid) * c_sl + m);
-            const int local = code - row0;
+            const int local = ncode - row0;
             const bool mine = local >= 0 && local < rows_per_part;
             s_code[tid] = mine ? local : -1;
             if (mine) atomicAdd(&s_cnt[local], 1);
         }
-        // value tile [128][64] -> fp32
-        for (int i = tid; i < kBlock * (kAggCols / 4); i += kAggThreads) {
-            const int r = i / (kAggCols / 4), c4 = i % (kAggCols / 4);
-            const float4 x = ld4<TV>(v + b * v_sb + h * v_sh + (j0 + r) * v_sl + ds * kAggCols + 4 * c4);
-            *reinterpret_cast<float4 *>(vt + r * kAggCols + 4 * c4) = x;
+#pragma unroll
+        for (int t = 0; t < kVecPerThread; ++t) {
+            const int i = tid + t * kAggThreads;
+            *reinterpret_cast<float4 *>(vt + (i / (kAggCols / 4)) * kAggCols + 4 * (i % (kAggCols / 4))) = nv[t];
         }
         __syncthreads();
-#pragma unroll 4
-        for (int j = 0; j < kBlock; ++j) {
-            const int lc = s_code[j];
-            if (lc >= 0 && (lc & 3) == grp) acc[lc * kAggCols + col] = __fadd_rn(acc[lc * kAggCols + col], vt[j * kAggCols + col]);
+        if (n + 1 < NB) fetch(n + 1);
+        // warp `grp` owns the code rows with (row & 7) == grp: it picks its keys out of the block with
+        // ballots and adds them in position order (lowest bit first), 32 columns wide
+#pragma unroll
+        for (int t = 0; t < kBlock / 32; ++t) {
+            const int lc_t = s_code[32 * t + (tid & 31)];
+            unsigned bal = __ballot_sync(0xffffffffu, lc_t >= 0 && (lc_t & 7) == grp);
+            while (bal) {
+                const int bit = __ffs(bal) - 1;
+                bal &= bal - 1;
+                const int lc = __shfl_sync(0xffffffffu, lc_t, bit);
+                acc[lc * kAggCols + col] = __fadd_rn(acc[lc * kAggCols + col], vt[(32 * t + bit) * kAggCols + col]);
+            }
         }
         __syncthreads();
         const int64_t out_row0 = (static_cast<int64_t>(u) * NB + n) * MK + m * K + row0;
-        for (int i = tid; i < rows_per_part * (kAggCols / 4); i += kAggThreads) {
-            const int r = i / (kAggCols / 4), c4 = i % (kAggCols / 4);
-            const float4 x = *reinterpret_cast<const float4 *>(acc + r * kAggCols + 4 * c4);
-            st4<TO>(vsum + (out_row0 + r) * D + ds * kAggCols + 4 * c4, x);
+        for (int i = tid; i < rows_per_part * (kAggCols / 8); i += kAggThreads) {
+            const int r = i / (kAggCols / 8), c8 = i % (kAggCols / 8);
+            const float4 x = *reinterpret_cast<const float4 *>(acc + r * kAggCols + 8 * c8);
+            const float4 y = *reinterpret_cast<const float4 *>(acc + r * kAggCols + 8 * c8 + 4);
+            st8<TO>(vsum + (out_row0 + r) * D + ds * kAggCols + 8 * c8, x, y);
         }
         if (ds == 0)
             for (int i = tid; i < rows_per_part; i += kAggThreads) cnt[out_row0 + i] = static_cast<float>(s_cnt[i]);
-        // s_code / vt are rewritten only after the next iteration's loads, which follow this
-        // barrier-separated read phase: one more barrier keeps slow readers of vt safe.
+        // the next iteration rewrites s_code, vt and s_cnt right away: wait for this snapshot's readers
         __syncthreads();
     }
 }

@@ -33,6 +33,7 @@ EXPORTS = (
     "vqattn_version", "vqattn_status_string", "vqattn_assign_codes", "vqattn_build_aggregates",
     "vqattn_gather_aggregates", "vqattn_prefill", "vqattn_decode_workspace_bytes", "vqattn_decode",
     "vqattn_cache_advance", "vqattn_decode_static_capacity", "vqattn_decode_static",
+    "vqattn_assign_workspace_bytes", "vqattn_assign_codes_ws",
 )
 
 
@@ -81,6 +82,10 @@ def _load() -> ctypes.CDLL:
     lib.vqattn_status_string.restype = ctypes.c_char_p
     lib.vqattn_status_string.argtypes = [ctypes.c_int]
     lib.vqattn_assign_codes.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
+    lib.vqattn_assign_workspace_bytes.restype = ctypes.c_size_t
+    lib.vqattn_assign_workspace_bytes.argtypes = [ctypes.c_int64] * 4
+    lib.vqattn_assign_codes_ws.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p,
+                                           ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
     lib.vqattn_build_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc),
                                             P(VqTensorDesc), ctypes.c_void_p]
     lib.vqattn_gather_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
@@ -93,7 +98,8 @@ def _load() -> ctypes.CDLL:
     lib.vqattn_cache_advance.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc),
                                          P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
     for name in EXPORTS:
-        if name not in ("vqattn_status_string", "vqattn_decode_workspace_bytes", "vqattn_decode_static_capacity"):
+        if name not in ("vqattn_status_string", "vqattn_decode_workspace_bytes", "vqattn_decode_static_capacity",
+                        "vqattn_assign_workspace_bytes"):
             getattr(lib, name).restype = ctypes.c_int
     return lib
 
