@@ -79,14 +79,14 @@ int vqattn_assign_codes(const VqTensorDesc *k, const VqTensorDesc *codebooks, co
 
 /*
  * The same assignment, bit for bit the same codes, with the score matrix on the tensor cores
- * (bf16 keys, K <= 512, M <= 8): approximate scores by tcgen05.mma over a bf16 hi/lo split of the
- * codebook, then an exact fp32 re-score of every key whose two best approximate scores are closer
- * than the proven error bound.  Needs `workspace` (256-byte aligned) of
- * vqattn_assign_workspace_bytes(Hkv, M, K, D) bytes for the split codebook.  Inputs outside the
+ * (bf16 keys, K a multiple of 128 up to 512, M <= 8): approximate scores by tcgen05.mma over a bf16 hi/lo split of the
+ * codebook, then an exact fp32 re-score of every key whose two best approximate
+ * scores are closer than the proven error bound.  Needs `workspace` (256-byte aligned) of
+ * vqattn_assign_workspace_bytes(B, Hkv, L, M, K, D) bytes for the split codebook.  Inputs outside the
  * tensor-core path (fp32 keys, larger K or M) are forwarded to vqattn_assign_codes.
  * `status_word`: device int32 or NULL, raised if a bounded device-side wait expires.
  */
-size_t vqattn_assign_workspace_bytes(int64_t Hkv, int64_t M, int64_t K, int64_t D);
+size_t vqattn_assign_workspace_bytes(int64_t B, int64_t Hkv, int64_t L, int64_t M, int64_t K, int64_t D);
 int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc *codebooks, const VqTensorDesc *bias_or_null,
                            VqTensorDesc *codes, void *workspace, size_t workspace_bytes, int32_t *status_word,
                            void *stream);

@@ -74,7 +74,7 @@ def assign_codes(k: torch.Tensor, codebooks: torch.Tensor, bias: Optional[torch.
             check(lib.vqattn_assign_codes(dk, dc, db if bias is not None else None, do, stream_ptr(dev)), "vqattn_assign_codes")
         else:
             # tensor-core scoring + exact re-score where it applies (bf16 keys); same codes either way
-            need = lib.vqattn_assign_workspace_bytes(Hkv, M, K, k.shape[3])
+            need = lib.vqattn_assign_workspace_bytes(B, Hkv, L, M, K, k.shape[3])
             if workspace is None or workspace.numel() < need:
                 workspace = torch.empty(need, dtype=torch.uint8, device=dev)
             check(lib.vqattn_assign_codes_ws(dk, dc, db if bias is not None else None, do, workspace.data_ptr(), workspace.numel(),

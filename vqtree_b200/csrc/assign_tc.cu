@@ -8,26 +8,25 @@
 //      fp32 codebook is split into two bf16 terms (C ~ Chi + Clo, error <= 2^-16 |C|), a bf16 key is
 //      exact, and for m > 0 the part already quantised, q_m = sum_{m'<m} C_m'[code], is kept as two
 //      bf16 terms too and subtracted with negated MMAs:  s~ = k.Chi + k.Clo - qh.Chi - ql.Chi - qh.Clo.
-//   2. Every approximate score is within eps = 2^-13 (|k| + sum_m' max|C_m'|) max|C_m| of the exact
-//      chain (split error 2^-16, dropped ql.Clo 2^-18, fp32 accumulation < 2^-16 each side: a 4x
-//      margin).  A key whose best approximate score leads the runner-up by more than 2 eps has a
+//   2. Every approximate score is within eps = 2^-15 (|k| + sum_m' max|C_m'|) max|C_m| of the exact
+//      chain (split error 2^-18, dropped ql.Clo 2^-18, fp32 accumulation < 2^-17 on each side).  A key whose best approximate score leads the runner-up by more than 2 eps has a
 //      unique arg-max: that code is final.
-//   3. The other keys (about 1 % for random data) are settled exactly: their candidates (all codes
-//      within 2 eps of the best) are re-scored by the warp with the defining fp32 chain, first
-//      maximum wins.
+//   3. The other keys (about 1 % for random data) are settled exactly on the spot: their candidates
+//      (all codes within 2 eps of the best) are re-scored by the warp with the defining fp32 chain,
+//      first maximum wins.
 // One CTA = 128 keys of one (batch, kv head); warps 0-3 own one key each per thread, warp 4 issues
-// TMA loads (codebook chunks of 64 codewords, two stages) and the MMAs.  Every wait is bounded.
+// TMA loads (hi / lo terms of 128-codeword chunks through a 3-slot ring) and the MMAs.  Every wait is bounded.
 #include "prefill_tc_common.cuh"
 
 namespace vq {
 
 using namespace ptx;
 
-constexpr int kAtChunk = 64;       // codewords per MMA chunk
+constexpr int kAtChunk = 128;      // codewords per MMA chunk (one N = 128 instruction)
 constexpr int kAtThreads = 160;    // 4 scan warps + 1 control warp
 constexpr int kAtMaxM = 8;
 constexpr int kAtMaxK = 512;
-constexpr float kAtEps = 1.220703125e-4f;  // 2^-13
+constexpr float kAtEps = 3.0517578125e-5f;  // 2^-15
 
 // ------------------------------------------------------------------------------------------------
 // fp32 codebook -> bf16 hi / lo terms [Hkv, M*K, D] and the largest row norm of every codebook.
@@ -81,11 +80,11 @@ template <int D>
 struct AtCfg {
     static constexpr int NH = D / 64;
     static constexpr int kATile = NH * kHalfBytes;               // 128 keys x D bf16
-    static constexpr int kBHalf = kAtChunk * 64 * 2;              // 64 codewords x 64 bf16
-    static constexpr int kBTile = NH * kBHalf;                    // one term (hi or lo) of a chunk
+    static constexpr int kBHalf = kAtChunk * 64 * 2;              // 128 codewords x 64 bf16
+    static constexpr int kUnit = NH * kBHalf;                     // one term (hi or lo) of a chunk = one ring slot
+    static constexpr int kSlots = 3;
     static constexpr int kAk = 0, kAqh = kATile, kAql = 2 * kATile, kB = 3 * kATile;
-    static constexpr int kStage = 2 * kBTile;                     // hi then lo
-    static constexpr int kTotal = kB + 2 * kStage + 1024;
+    static constexpr int kTotal = kB + kSlots * kUnit + 1024;
 };
 
 // The defining score: one fp32 FMA chain over d of the residual r (shared memory, fp32) against
@@ -115,7 +114,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     constexpr int NH = C::NH;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t bar_k, b_full[2], b_free[2], bar_s, bar_q;
+    __shared__ __align__(8) uint64_t bar_k, b_full[3], b_free[3], bar_c[kAtMaxK / kAtChunk], bar_q;
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
     __shared__ __align__(16) float s_res[4][D];  // per scan warp: exact fp32 residual of the key being re-scored
@@ -125,13 +124,18 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int64_t j0 = static_cast<int64_t>(blockIdx.x) * kBlock;
     const int M = p.M, K = p.K, MK = M * K;
     const int chunks = K / kAtChunk;
-    const uint32_t tmem_cols = K <= 256 ? 256u : 512u;
+    const uint32_t tmem_cols = 512u;
+    // K <= 256: the score columns of consecutive codebooks alternate between two 256-column regions, so
+    // the key term of codebook m may be issued while the scan threads still read codebook m - 1
+    const bool two_regions = K <= 256;
 
     if (tid == 0) {
         mbar_init(&bar_k, 1);
-        mbar_init(&b_full[0], 1); mbar_init(&b_full[1], 1);
-        mbar_init(&b_free[0], 1); mbar_init(&b_free[1], 1);
-        mbar_init(&bar_s, 1);
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&b_full[i], 1);
+            mbar_init(&b_free[i], 1);
+        }
+        for (int i = 0; i < kAtMaxK / kAtChunk; ++i) mbar_init(&bar_c[i], 1);
         mbar_init(&bar_q, 128);
         fence_mbar_init();
         s_err = 0;
@@ -154,57 +158,70 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
             for (int hh = 0; hh < NH; ++hh)
                 tma_load_4d(smem + C::kAk + hh * kHalfBytes, &tm_k, &bar_k, 64 * hh, static_cast<int>(j0), h, b);
-            const int total = M * chunks;
-            auto issue_load = [&](int g) {  // chunk g of the whole sequence (m = g / chunks)
-                const int st = g & 1;
-                if (g >= 2 && !mbar_wait(&b_free[st], ((g >> 1) - 1) & 1)) {
+            // The codebook streams through a 3-slot ring in UNITS: unit 2c is the hi term of chunk c
+            // (128 codewords), unit 2c+1 its lo term, chunks numbered through all M codebooks.
+            const int total = 2 * M * chunks;
+            auto issue_load = [&](int g) {
+                const int slot = g % C::kSlots;
+                if (g >= C::kSlots && !mbar_wait(&b_free[slot], ((g / C::kSlots) - 1) & 1)) {
                     ok = false;
                     return;
                 }
-                const int row = h * MK + (g / chunks) * K + (g % chunks) * kAtChunk;  // row in [Hkv*M*K, D]
-                uint8_t *dst = smem + C::kB + st * C::kStage;
-                mbar_expect_tx(&b_full[st], C::kStage);
+                const int c = g >> 1;
+                const int row = h * MK + (c / chunks) * K + (c % chunks) * kAtChunk;  // row in [Hkv*M*K, D]
+                uint8_t *dst = smem + C::kB + slot * C::kUnit;
+                mbar_expect_tx(&b_full[slot], C::kUnit);
 #pragma unroll
-                for (int hh = 0; hh < NH; ++hh) {
-                    tma_load_3d(dst + hh * C::kBHalf, &tm_hi, &b_full[st], 64 * hh, row, 0);
-                    tma_load_3d(dst + C::kBTile + hh * C::kBHalf, &tm_lo, &b_full[st], 64 * hh, row, 0);
-                }
+                for (int hh = 0; hh < NH; ++hh) tma_load_3d(dst + hh * C::kBHalf, (g & 1) ? &tm_lo : &tm_hi, &b_full[slot], 64 * hh, row, 0);
             };
             constexpr uint32_t id_pos = idesc_bf16(128, kAtChunk, 0, 0, 0), id_neg = idesc_bf16(128, kAtChunk, 0, 0, 1);
-            const uint32_t a_k = smem_u32(smem + C::kAk), a_qh = smem_u32(smem + C::kAqh), a_ql = smem_u32(smem + C::kAql);
+            // descriptors differ only in their 16-byte-granular start address: build the bases once
+            const uint64_t d_k = smem_desc_sw128(smem_u32(smem + C::kAk), 16, 1024);
+            const uint64_t d_qh = smem_desc_sw128(smem_u32(smem + C::kAqh), 16, 1024);
+            const uint64_t d_ql = smem_desc_sw128(smem_u32(smem + C::kAql), 16, 1024);
+            const uint64_t d_b0 = smem_desc_sw128(smem_u32(smem + C::kB), 16, 1024);
             issue_load(0);
+            if (total > 1) issue_load(1);
             if (!mbar_wait(&bar_k, 0)) ok = false;
             for (int g = 0; g < total && ok; ++g) {
-                const int m = g / chunks, ch = g % chunks, st = g & 1;
-                if (g + 1 < total) issue_load(g + 1);
-                if (ch == 0 && m > 0 && !mbar_wait(&bar_q, (m - 1) & 1)) ok = false;  // q terms of this m written
-                if (!ok || !mbar_wait(&b_full[st], (g >> 1) & 1)) {
+                const int c = g >> 1, m = c / chunks, ch = c % chunks, slot = g % C::kSlots;
+                const bool is_lo = g & 1;
+                if (g + 2 < total) issue_load(g + 2);
+                if (!ok || !mbar_wait(&b_full[slot], (g / C::kSlots) & 1)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t bhi = smem_u32(smem + C::kB + st * C::kStage), blo = bhi + C::kBTile;
-                const uint32_t dcol = tmem + ch * kAtChunk;
-                uint32_t acc = 0;
-                auto term = [&](uint32_t a_base, uint32_t b_base, uint32_t idesc) {
+                const uint64_t d_b = d_b0 + static_cast<uint64_t>((slot * C::kUnit) >> 4);
+                const uint32_t dcol = tmem + (two_regions ? (m & 1) * 256 : 0) + ch * kAtChunk;
+                uint32_t acc = is_lo ? 1u : 0u;
+                if (m > 0 && !two_regions && ch == 0 && !is_lo && !mbar_wait(&bar_q, (m - 1) & 1)) {
+                    ok = false;  // one region only: it is free once the scan of codebook m - 1 is over
+                    break;
+                }
+                auto term = [&](uint64_t a_desc, uint32_t idesc) {
 #pragma unroll
                     for (int hh = 0; hh < NH; ++hh)
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4) {
-                            mma_ss(dcol, smem_desc_sw128(a_base + hh * kHalfBytes + k4 * 32, 16, 1024),
-                                   smem_desc_sw128(b_base + hh * C::kBHalf + k4 * 32, 16, 1024), idesc, acc);
+                            mma_ss(dcol, a_desc + static_cast<uint64_t>((hh * kHalfBytes + k4 * 32) >> 4),
+                                   d_b + static_cast<uint64_t>((hh * C::kBHalf + k4 * 32) >> 4), idesc, acc);
                             acc = 1;
                         }
                 };
-                term(a_k, bhi, id_pos);
-                term(a_k, blo, id_pos);
+                term(d_k, id_pos);  // the key term needs nothing from the previous codebook's scan
                 if (m > 0) {
-                    term(a_qh, bhi, id_neg);
-                    term(a_ql, bhi, id_neg);
-                    term(a_qh, blo, id_neg);
+                    // the q terms of codebook m exist once every scan thread has folded in its code of m - 1
+                    if (two_regions && ch == 0 && !is_lo && !mbar_wait(&bar_q, (m - 1) & 1)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    term(d_qh, id_neg);
+                    if (!is_lo) term(d_ql, id_neg);
                 }
-                tc_commit(&b_free[st]);
-                if (ch == chunks - 1) tc_commit(&bar_s);
+                tc_commit(&b_free[slot]);
+                if (is_lo) tc_commit(&bar_c[ch]);  // this chunk's 128 score columns are complete
             }
             if (!ok) s_err = 1;
         }
@@ -231,37 +248,43 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             }
             knorm = sqrtf(ss) * 1.0001f;
         }
+        float qbound = 0.f;
+        bool ok = true;
         int prev[kAtMaxM];
 #pragma unroll
         for (int mm = 0; mm < kAtMaxM; ++mm) prev[mm] = 0;
-        float qbound = 0.f;
-        bool ok = true;
         for (int m = 0; m < M && ok; ++m) {
             const float cm = p.cmax[h * M + m];
             const float thr = 2.f * kAtEps * (knorm + qbound) * cm + 1e-30f;
             const float *bm = p.bias ? p.bias + (static_cast<int64_t>(h) * M + m) * K : nullptr;
-            if (!mbar_wait(&bar_s, m & 1)) {
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            // ---- scan: best (first maximum) and runner-up of the approximate scores
+            const uint32_t region = two_regions ? (m & 1) * 256 : 0;
+            // ---- scan, chunk by chunk as the tensor pipe finishes them: best (first maximum) and runner-up
             float best = -INFINITY, second = -INFINITY;
             int bidx = 0;
-            for (int c0 = 0; c0 < K; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_off + c0, r);
-                tc_wait_ld();
+            for (int ch = 0; ch < chunks && ok; ++ch) {
+                if (!mbar_wait(&bar_c[ch], m & 1)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = __uint_as_float(r[i]);
-                    if (bm) v += __ldg(bm + c0 + i);
-                    const bool gt = v > best;
-                    second = gt ? best : fmaxf(second, v);
-                    bidx = gt ? c0 + i : bidx;
-                    best = gt ? v : best;
+                for (int q4 = 0; q4 < kAtChunk / 32; ++q4) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem + lane_off + region + ch * kAtChunk + 32 * q4, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int c = ch * kAtChunk + 32 * q4 + i;
+                        float v = __uint_as_float(r[i]);
+                        if (bm) v += __ldg(bm + c);
+                        const bool gt = v > best;
+                        second = gt ? best : fmaxf(second, v);
+                        bidx = gt ? c : bidx;
+                        best = gt ? v : best;
+                    }
                 }
             }
+            if (!ok) break;
             int code = bidx;
             const bool flagged = valid && !(best - second > thr);
             unsigned fl = __ballot_sync(0xffffffffu, flagged);
@@ -273,7 +296,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     mask[w] = 0;
                     if (w * 32 < K) {
                         uint32_t r[32];
-                        tmem_ld32(tmem + lane_off + w * 32, r);
+                        tmem_ld32(tmem + lane_off + region + w * 32, r);
                         tc_wait_ld();
                         uint32_t bits = 0;
 #pragma unroll
@@ -345,45 +368,43 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             if (valid) store_code(p.codes, p.code_dtype, b * p.c_sb + h * p.c_sh + j * p.c_sl + m, code);
             qbound += cm;
             if (m + 1 < M) {
-                // ---- q += C_m[code], re-split into bf16 hi / lo, written in the 128B-swizzled operand layout
-                const float *cr = cbh + (static_cast<int64_t>(m) * K + code) * D;
-#pragma unroll
-                for (int hh = 0; hh < NH; ++hh)
-#pragma unroll
-                    for (int ch8 = 0; ch8 < 8; ++ch8) {
-                        const uint32_t off = hh * kHalfBytes + row * 128 + ((ch8 ^ (row & 7)) << 4);
-                        uint4 *ph = reinterpret_cast<uint4 *>(smem + C::kAqh + off);
-                        uint4 *pl = reinterpret_cast<uint4 *>(smem + C::kAql + off);
-                        float q[8];
-                        if (m == 0) {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) q[e] = 0.f;
-                        } else {
-                            const uint4 vh = *ph, vl = *pl;
-                            const __nv_bfloat162 *hh2 = reinterpret_cast<const __nv_bfloat162 *>(&vh);
-                            const __nv_bfloat162 *ll2 = reinterpret_cast<const __nv_bfloat162 *>(&vl);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                q[2 * e] = __low2float(hh2[e]) + __low2float(ll2[e]);
-                                q[2 * e + 1] = __high2float(hh2[e]) + __high2float(ll2[e]);
-                            }
+                // ---- q += C_m[code], re-split into bf16 hi / lo, written in the 128B-swizzled operand layout.
+                // The warp walks its 32 rows together: lane l owns columns 4l..4l+3 of every row, so the
+                // codeword rows are read with coalesced 16-byte loads.
+                {
+                    const int col = (lane * 4) % D, hh = col >> 6, ch8 = (col & 63) >> 3, sub8 = (col & 7) * 2;
+#pragma unroll 8
+                    for (int rr = 0; rr < 32; ++rr) {
+                        const int r_row = warp * 32 + rr;
+                        const int r_code = __shfl_sync(0xffffffffu, code, rr);
+                        if (lane * 4 >= D) continue;  // D = 64: half of the lanes have no column
+                        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(m) * K + r_code) * D + col));
+                        const uint32_t off = hh * kHalfBytes + r_row * 128 + ((ch8 ^ (r_row & 7)) << 4) + sub8;
+                        uint2 *ph = reinterpret_cast<uint2 *>(smem + C::kAqh + off);
+                        uint2 *pl = reinterpret_cast<uint2 *>(smem + C::kAql + off);
+                        float q[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (m > 0) {
+                            const uint2 vh = *ph, vl = *pl;
+                            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&vh);
+                            const __nv_bfloat162 *l2 = reinterpret_cast<const __nv_bfloat162 *>(&vl);
+                            q[0] = __low2float(h2[0]) + __low2float(l2[0]);
+                            q[1] = __high2float(h2[0]) + __high2float(l2[0]);
+                            q[2] = __low2float(h2[1]) + __low2float(l2[1]);
+                            q[3] = __high2float(h2[1]) + __high2float(l2[1]);
                         }
-                        const float4 c0 = __ldg(reinterpret_cast<const float4 *>(cr + hh * 64 + ch8 * 8));
-                        const float4 c1 = __ldg(reinterpret_cast<const float4 *>(cr + hh * 64 + ch8 * 8 + 4));
-                        q[0] += c0.x; q[1] += c0.y; q[2] += c0.z; q[3] += c0.w;
-                        q[4] += c1.x; q[5] += c1.y; q[6] += c1.z; q[7] += c1.w;
-                        uint32_t wh[4], wl[4];
+                        q[0] += c4.x; q[1] += c4.y; q[2] += c4.z; q[3] += c4.w;
+                        uint32_t wh[2], wl[2];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
+                        for (int e = 0; e < 2; ++e) {
                             const __nv_bfloat16 h0 = __float2bfloat16_rn(q[2 * e]), h1 = __float2bfloat16_rn(q[2 * e + 1]);
-                            const float l0 = q[2 * e] - __bfloat162float(h0), l1 = q[2 * e + 1] - __bfloat162float(h1);
                             __nv_bfloat162 hv = __halves2bfloat162(h0, h1);
                             wh[e] = *reinterpret_cast<uint32_t *>(&hv);
-                            wl[e] = pack_bf16(l0, l1);
+                            wl[e] = pack_bf16(q[2 * e] - __bfloat162float(h0), q[2 * e + 1] - __bfloat162float(h1));
                         }
-                        *ph = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-                        *pl = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                        *ph = make_uint2(wh[0], wh[1]);
+                        *pl = make_uint2(wl[0], wl[1]);
                     }
+                }
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(&bar_q);
@@ -420,7 +441,7 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     CUtensorMap mk, mhi, mlo;
     const uint64_t cd[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(Hkv * MK), 1};
     const uint64_t cs[3] = {1, static_cast<uint64_t>(D), static_cast<uint64_t>(Hkv * MK * D)};
-    if (!map_bhld(&mk, *k) || !make_map(&mhi, hi, 3, cd, cs, kAtChunk) || !make_map(&mlo, lo, 3, cd, cs, kAtChunk)) return VQ_ELAUNCH;
+    if (!map_bhld(&mk, *k) || !make_map(&mhi, hi, 3, cd, cs) || !make_map(&mlo, lo, 3, cd, cs)) return VQ_ELAUNCH;
     AtParams p{};
     p.k = static_cast<const __nv_bfloat16 *>(k->ptr);
     p.k_sb = k->stride[0]; p.k_sh = k->stride[1]; p.k_sl = k->stride[2];
@@ -441,9 +462,13 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
 
 }  // namespace vq
 
-extern "C" size_t vqattn_assign_workspace_bytes(int64_t Hkv, int64_t M, int64_t K, int64_t D)
+extern "C" size_t vqattn_assign_workspace_bytes(int64_t B, int64_t Hkv, int64_t L, int64_t M, int64_t K, int64_t D)
 {
-    return static_cast<size_t>(Hkv) * M * K * D * 2 * 2 + static_cast<size_t>(Hkv) * M * sizeof(float) + 256;
+    (void)B;
+    (void)L;
+    const size_t split = static_cast<size_t>(Hkv) * M * K * D * 2 * 2;                           // bf16 hi / lo codebooks
+    const size_t norms = (static_cast<size_t>(Hkv) * M * sizeof(float) + 255) / 256 * 256;        // max row norm per codebook
+    return split + norms + 256;
 }
 
 extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc *codebooks, const VqTensorDesc *bias,
@@ -477,7 +502,7 @@ extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc 
     if (reinterpret_cast<uintptr_t>(k->ptr) % 16 || reinterpret_cast<uintptr_t>(codebooks->ptr) % 16) return VQ_EINVAL_STRIDE;
     if (B * Hkv > 65535) return VQ_EUNSUPPORTED;
     if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 ||
-        workspace_bytes < vqattn_assign_workspace_bytes(Hkv, M, K, D))
+        workspace_bytes < vqattn_assign_workspace_bytes(B, Hkv, L, M, K, D))
         return VQ_EWORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_assign_tc<64>(k, codebooks, bias, codes, workspace, status_word, s)

@@ -83,7 +83,7 @@ def _load() -> ctypes.CDLL:
     lib.vqattn_status_string.argtypes = [ctypes.c_int]
     lib.vqattn_assign_codes.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
     lib.vqattn_assign_workspace_bytes.restype = ctypes.c_size_t
-    lib.vqattn_assign_workspace_bytes.argtypes = [ctypes.c_int64] * 4
+    lib.vqattn_assign_workspace_bytes.argtypes = [ctypes.c_int64] * 6
     lib.vqattn_assign_codes_ws.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p,
                                            ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
     lib.vqattn_build_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc),
