@@ -54,6 +54,14 @@ def decode_bytes(B, Hq, Hkv, D, W, M, K, **_):
     return B * Hkv * per_unit + Hkv * M * K * D * 4
 
 
+def attention_bytes(w):
+    """Algorithmic HBM bytes of one fused-attention launch: q, k, v, out once; value sums and counts of every far block."""
+    B, Hq, Hkv, L, D, W, M, K = (w[k] for k in ("B", "Hq", "Hkv", "L", "D", "W", "M", "K"))
+    nb = max(0, (L + BLOCK - 1) // BLOCK - W // BLOCK - 1)
+    act = (2 * B * Hq * L * D + 2 * B * Hkv * L * D) * 2
+    return act + B * Hkv * nb * M * K * (D * 2 + 4) + Hkv * M * K * D * 2
+
+
 def load_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -370,10 +378,13 @@ def main():
         warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None,
         dtype="bf16", data="synthetic", config=cfg,
         stages_ms=dict(assign_codes=stage_ms[0], build_aggregates=stage_ms[1], fused_attention=stage_ms[2]),
-        roofline=dict(kernel="prefill_tc_kernel (fused attention)", bound="tensor", achieved=attn_tflops, peak=peaks["tensor"],
+        roofline=dict(kernel="prefill_tc2_kernel (fused attention)", bound="tensor", achieved=attn_tflops, peak=peaks["tensor"],
                       unit="TFLOP/s", frac=attn_tflops / peaks["tensor"], peak_source=f"{peaks['source']} (burst bf16 matmul)",
-                      traffic=None, flops_per_launch=flops),
-        cpu_baseline=cpu, e2e=e2e, gpu_launches=3 * args.steps, clocks=clocks, decode=decode, gather_ms=gather_ms,
+                      traffic=attention_bytes(w) * 1.005, traffic_unit="bytes per launch",
+                      traffic_note="algorithmic bytes x 1.005, the DRAM read+write / algorithmic ratio ncu measured on the c2 "
+                                   "capture (profiles/); traffic grows in proportion to the units processed",
+                      flops_per_launch=flops),
+        cpu_baseline=cpu, e2e=e2e, gpu_launches=4 * args.steps, clocks=clocks, decode=decode, gather_ms=gather_ms,
     )
     print(json.dumps(line))
     if dist is not None:
