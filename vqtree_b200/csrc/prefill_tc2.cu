@@ -54,10 +54,14 @@ __device__ __forceinline__ void softmax_half(uint32_t s_addr, uint32_t p_addr, u
                                              const float *__restrict__ cw, int lo, int hi, float scale_log2, float &row_m,
                                              float &row_l, float *xch, int hf, int bar_id, float *pub, float pub_val)
 {
-    auto masked = [&](float x, int c) -> float {
-        if (MODE == 2) return cw[c] > 0.f ? x : -INFINITY;
-        if (MODE == 1) return (c >= lo && c < hi) ? x : -INFINITY;
-        return x;
+    // MODE 2 masks by adding nb[c] (0 where the code has members, -inf where it has none)
+    const float *nb = cw + 2 * kBlock;
+    auto masked2 = [&](float &x0, float &x1, int c0) {
+        if (MODE == 2) fadd2(x0, x1, x0, x1, nb[c0], nb[c0 + 1]);
+        if (MODE == 1) {
+            x0 = (c0 >= lo && c0 < hi) ? x0 : -INFINITY;
+            x1 = (c0 + 1 >= lo && c0 + 1 < hi) ? x1 : -INFINITY;
+        }
     };
     // pass 1: partial row maximum over this half's 64 columns
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -67,13 +71,20 @@ __device__ __forceinline__ void softmax_half(uint32_t s_addr, uint32_t p_addr, u
         tmem_ld32(s_addr + 32, r1);
         tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            mx4[j & 3] = fmaxf(mx4[j & 3], masked(__uint_as_float(r0[j]), j));
-            mx4[j & 3] = fmaxf(mx4[j & 3], masked(__uint_as_float(r1[j]), 32 + j));
+        for (int j = 0; j < 16; ++j) {
+            float a0 = __uint_as_float(r0[2 * j]), a1 = __uint_as_float(r0[2 * j + 1]);
+            float b0 = __uint_as_float(r1[2 * j]), b1 = __uint_as_float(r1[2 * j + 1]);
+            masked2(a0, a1, 2 * j);
+            masked2(b0, b1, 32 + 2 * j);
+            mx4[j & 1] = fmax3(mx4[j & 1], a0, a1);
+            mx4[2 + (j & 1)] = fmax3(mx4[2 + (j & 1)], b0, b1);
         }
     }
     xch[hf] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    if (pub != nullptr) *pub = pub_val;
+    if (pub != nullptr) {
+        pub[0] = pub_val;
+        pub[2 * kBlock] = pub_val > 0.f ? 0.f : -INFINITY;
+    }
     asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
     const float mx = fmaxf(xch[0], xch[1]);
     // lazy rescaling: keep the old reference maximum unless the new one is far above it
@@ -96,8 +107,9 @@ __device__ __forceinline__ void softmax_half(uint32_t s_addr, uint32_t p_addr, u
     }
     // pass 2: P = exp2(S*scale - m) as packed bf16 over the first 32 of this half's own 64 columns.
     // Chunk c reads columns [32c, 32c+32) and writes [16c, 16c+16): never ahead of what has been read,
-    // and never inside the partner's columns.
+    // and never inside the partner's columns.  Two elements per packed fp32x2 instruction.
     float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+    const float neg_m = -m_safe;
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
         uint32_t r[32], pk[16];
@@ -105,16 +117,20 @@ __device__ __forceinline__ void softmax_half(uint32_t s_addr, uint32_t p_addr, u
         tc_wait_ld();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const int c0 = 32 * c + 2 * j, c1 = c0 + 1;
-            const float p0 = ex2(fmaf(masked(__uint_as_float(r[2 * j]), c0), scale_log2, -m_safe));
-            const float p1 = ex2(fmaf(masked(__uint_as_float(r[2 * j + 1]), c1), scale_log2, -m_safe));
+            const int c0 = 32 * c + 2 * j;
+            float x0 = __uint_as_float(r[2 * j]), x1 = __uint_as_float(r[2 * j + 1]);
+            float t0, t1;
             if (MODE == 2) {
-                ls4[(2 * j) & 3] = fmaf(p0, cw[c0], ls4[(2 * j) & 3]);
-                ls4[(2 * j + 1) & 3] = fmaf(p1, cw[c1], ls4[(2 * j + 1) & 3]);
+                float b0, b1;
+                fadd2(b0, b1, nb[c0], nb[c0 + 1], neg_m, neg_m);
+                ffma2(t0, t1, x0, x1, scale_log2, scale_log2, b0, b1);
             } else {
-                ls4[(2 * j) & 3] += p0;
-                ls4[(2 * j + 1) & 3] += p1;
+                masked2(x0, x1, c0);
+                ffma2(t0, t1, x0, x1, scale_log2, scale_log2, neg_m, neg_m);
             }
+            const float p0 = ex2(t0), p1 = ex2(t1);
+            if (MODE == 2) ffma2(ls4[2 * (j & 1)], ls4[2 * (j & 1) + 1], p0, p1, cw[c0], cw[c0 + 1], ls4[2 * (j & 1)], ls4[2 * (j & 1) + 1]);
+            else fadd2(ls4[2 * (j & 1)], ls4[2 * (j & 1) + 1], ls4[2 * (j & 1)], ls4[2 * (j & 1) + 1], p0, p1);
             pk[j] = pack_bf16(p0, p1);
         }
         tmem_st16(p_addr + 16 * c, pk);
@@ -137,7 +153,8 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     __shared__ __align__(8) uint64_t bar_q, kv_full[NS], kv_empty[NS], s_full[2], p_full[2], o_done[2];
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
-    __shared__ __align__(16) float s_cnt[2][2][kBlock];  // [stream][item parity][code]: counts of a far tile
+    // counts of a far tile and their mask bias (0 / -inf): [stream][item parity][count | unused | bias | unused][code]
+    __shared__ __align__(16) float s_cnt[2][2][4][kBlock];
     __shared__ float s_xch[2][kBlock][2];                // [stream][row][half]: partial row maxima of an item
     __shared__ float s_m[2][kBlock], s_l[2][2][kBlock];  // final (max, partial denominators) per stream / half
 
@@ -292,7 +309,11 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         // item's barrier; the first tile's counts are published up front.
         const float *cnt_base = p.cnt + (static_cast<int64_t>(u) * p.NB + work.far_blk) * p.MK;
         if (s < work.n_far) {
-            if (hf == 0) s_cnt[s][0][row] = __ldg(cnt_base + s * kBlock + row);
+            if (hf == 0) {
+                const float c0v = __ldg(cnt_base + s * kBlock + row);
+                s_cnt[s][0][0][row] = c0v;
+                s_cnt[s][0][2][row] = c0v > 0.f ? 0.f : -INFINITY;
+            }
             asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory");
         }
         for (int it = s; it < n && ok; it += 2) {
@@ -302,14 +323,14 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             float *pub = nullptr;
             if (hf == 0 && it + 2 < work.n_far) {
                 cnt_next = __ldg(cnt_base + (it + 2) * kBlock + row);
-                pub = &s_cnt[s][par ^ 1][row];
+                pub = &s_cnt[s][par ^ 1][0][row];
             }
             if (!mbar_wait(&s_full[s], par)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            const float *cw = &s_cnt[s][par][64 * hf];
+            const float *cw = &s_cnt[s][par][0][64 * hf];
             // valid key columns of this row, relative to this half: [lo, hi)
             int lo = 0, hi = 64;
             if (kind == kDiag) hi = row + 1 - 64 * hf;
