@@ -292,3 +292,28 @@ def test_assign_tensor_path_ties_zero_keys_and_bias(api):
         torch.cuda.synchronize()
         api.check_status()
         np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
+# ------------------------------------------------------------------ host-buffer entry (pipelined copies)
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Hq,Hkv,rerope,chunks", [(2, 8, 4, True, 8), (1, 6, 6, False, 4), (1, 4, 2, False, 1)])
+def test_prefill_host_pipeline_equals_device_path(api, B, Hq, Hkv, rerope, chunks):
+    """Chunked, stream-pipelined host entry == one device call on the same inputs, bit for bit."""
+    case = make_case(B, Hq, Hkv, 1024, 128, 2, 128, 256, 31, rerope, torch.bfloat16)
+    names = ("q1", "q2", "k1", "k3", "v")
+    d = {n: dev(case[n]) for n in names}
+    if not rerope:
+        d["q2"], d["k3"] = d["q1"], d["k1"]
+    cb = dev(case["cb"])
+    want = api.vq_attention_prefill(d["q1"], d["q2"], d["k1"], d["k3"], d["v"], cb, case["W"])
+    h = {n: case[n].pin_memory() for n in names}
+    if not rerope:
+        h["q2"], h["k3"] = h["q1"], h["k1"]
+    got = api.vq_attention_prefill_host(h["q1"], h["q2"], h["k1"], h["k3"], h["v"], cb, case["W"], chunks=chunks)
+    api.check_status()
+    assert not got.is_cuda and got.is_pinned()
+    assert torch.equal(got, want.cpu())
+    # unpinned inputs and a second call into the same output buffer
+    got2 = api.vq_attention_prefill_host(case["q1"], case["q2"] if rerope else case["q1"], case["k1"],
+                                         case["k3"] if rerope else case["k1"], case["v"], cb, case["W"], out=got)
+    assert got2 is got and torch.equal(got2, want.cpu())

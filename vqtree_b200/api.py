@@ -146,7 +146,8 @@ def prefill_from_aggregates(q1, q2, k1, k3, v, codebook_act, cnt, vsum, window: 
 
 
 def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window: int, scale: Optional[float] = None,
-                         bias: Optional[torch.Tensor] = None, impl: str = "auto", return_state: bool = False):
+                         bias: Optional[torch.Tensor] = None, impl: str = "auto", return_state: bool = False,
+                         out: Optional[torch.Tensor] = None):
     """The whole prefill path: assign codes to k3, build aggregates of v, fused attention.
 
     q1,q2 [B,Hq,L,D]; k1,k3,v [B,Hkv,L,D] (f32 or bf16); codebooks [Hkv,M,K,D] f32.
@@ -162,7 +163,7 @@ def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window: int, scale: Optio
     if nb > 0:
         cnt, vsum = build_aggregates(codes, v, K, nb)
         cb_act = codebooks.reshape(Hkv, M * K, D).to(q1.dtype)
-    out = prefill_from_aggregates(q1, q2, k1, k3, v, cb_act, cnt, vsum, window, scale, impl)
+    out = prefill_from_aggregates(q1, q2, k1, k3, v, cb_act, cnt, vsum, window, scale, impl, out=out)
     if return_state:
         return out, dict(codes=codes, cnt=cnt, vsum=vsum)
     return out
@@ -231,24 +232,80 @@ def _to_device(t, dev):
     return t.to(dev, non_blocking=True)
 
 
+_SIDE_STREAMS = {}
+
+
+def _side_streams(dev):
+    key = torch.device(dev).index or 0
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    return _SIDE_STREAMS[key]
+
+
 def vq_attention_prefill_host(q1, q2, k1, k3, v, codebooks, window: int, scale: Optional[float] = None,
-                              device="cuda:0", impl: str = "auto", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                              device="cuda:0", impl: str = "auto", out: Optional[torch.Tensor] = None,
+                              chunks: int = 8) -> torch.Tensor:
     """vq_attention_prefill for host tensors: host->device copies, the three kernels, device->host copy.
 
+    (batch, kv-head) units are independent, so the work is cut into about ``chunks`` groups of kv heads
+    and pipelined: a copy-in stream runs ahead of the kernels (current stream) and a copy-out stream
+    behind them, so both directions of the host link and the kernels overlap.  Returns after everything
+    has landed in ``out`` (pinned host memory).
     q2 / k3 may be the same objects as q1 / k1 (plain-RoPE mode): they are then copied once.
     """
     dev = torch.device(device)
-    dq1 = _to_device(q1, dev)
-    dq2 = dq1 if q2 is q1 else _to_device(q2, dev)
-    dk1 = _to_device(k1, dev)
-    dk3 = dk1 if k3 is k1 else _to_device(k3, dev)
-    dv = _to_device(v, dev)
-    dcb = codebooks if codebooks.is_cuda else _to_device(codebooks, dev)
-    res = vq_attention_prefill(dq1, dq2, dk1, dk3, dv, dcb, window, scale, impl=impl)
-    if out is None:
-        out = torch.empty(res.shape, dtype=res.dtype, pin_memory=True)
-    out.copy_(res, non_blocking=True)
-    torch.cuda.current_stream(dev).synchronize()
+    same_q, same_k = q2 is q1, k3 is k1
+    hq1, hq2, hk1, hk3, hv = [t if (t is None or t.is_pinned()) else t.pin_memory() for t in (q1, q2, k1, k3, v)]
+    if same_q:
+        hq2 = hq1
+    if same_k:
+        hk3 = hk1
+    B, Hq, L, D = q1.shape
+    Hkv = k1.shape[1]
+    group = Hq // Hkv
+    with torch.cuda.device(dev):
+        cur = torch.cuda.current_stream(dev)
+        s_in, s_out = _side_streams(dev)
+        dcb = codebooks if codebooks.is_cuda else _to_device(codebooks, dev)
+        dq1 = torch.empty(q1.shape, dtype=q1.dtype, device=dev)
+        dq2 = dq1 if same_q else torch.empty(q2.shape, dtype=q2.dtype, device=dev)
+        dk1 = torch.empty(k1.shape, dtype=k1.dtype, device=dev)
+        dk3 = dk1 if same_k else torch.empty(k3.shape, dtype=k3.dtype, device=dev)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
+        dout = torch.empty(q1.shape, dtype=q1.dtype, device=dev)
+        if out is None:
+            out = torch.empty(q1.shape, dtype=q1.dtype, pin_memory=True)
+        per_b = max(1, int(chunks) // B)
+        hc = (Hkv + per_b - 1) // per_b
+        parts = [(b, h0, min(Hkv, h0 + hc)) for b in range(B) for h0 in range(0, Hkv, hc)]
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        arrived = []
+        with torch.cuda.stream(s_in):
+            for b, h0, h1 in parts:
+                g0, g1 = h0 * group, h1 * group
+                dq1[b, g0:g1].copy_(hq1[b, g0:g1], non_blocking=True)
+                if not same_q:
+                    dq2[b, g0:g1].copy_(hq2[b, g0:g1], non_blocking=True)
+                dk1[b, h0:h1].copy_(hk1[b, h0:h1], non_blocking=True)
+                if not same_k:
+                    dk3[b, h0:h1].copy_(hk3[b, h0:h1], non_blocking=True)
+                dv[b, h0:h1].copy_(hv[b, h0:h1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+                arrived.append(ev)
+        for (b, h0, h1), ev in zip(parts, arrived):
+            g0, g1 = h0 * group, h1 * group
+            cur.wait_event(ev)
+            vq_attention_prefill(dq1[b:b + 1, g0:g1], dq2[b:b + 1, g0:g1], dk1[b:b + 1, h0:h1], dk3[b:b + 1, h0:h1],
+                                 dv[b:b + 1, h0:h1], dcb[h0:h1], window, scale, impl=impl, out=dout[b:b + 1, g0:g1])
+            done = torch.cuda.Event()
+            done.record(cur)
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                out[b, g0:g1].copy_(dout[b, g0:g1], non_blocking=True)
+        cur.wait_stream(s_out)
+        cur.synchronize()
     return out
 
 

@@ -3,19 +3,27 @@
 // Replaces ops/mini_vq.py:4-18 of the reference (and its greedy-residual extension to M codebooks)
 // for bf16 keys.  The defining arithmetic is unchanged: the code of a key in codebook m is the first
 // arg-max over c of the fp32 fused-multiply-add chain  sum_d r_m[d] * C_m[c][d] (+ bias),
-// r_{m+1} = r_m - C_m[code].  What changes is how the arg-max is found:
+// r_0 = k, r_{m+1} = r_m - C_m[code] (fp32 subtraction).  What changes is how the arg-max is found:
 //   1. APPROXIMATE scores of a 128-key tile against all K codewords come from tcgen05.mma.  The
-//      fp32 codebook is split into two bf16 terms (C ~ Chi + Clo, error <= 2^-16 |C|), a bf16 key is
-//      exact, and for m > 0 the part already quantised, q_m = sum_{m'<m} C_m'[code], is kept as two
-//      bf16 terms too and subtracted with negated MMAs:  s~ = k.Chi + k.Clo - qh.Chi - ql.Chi - qh.Clo.
-//   2. Every approximate score is within eps = 2^-15 (|k| + sum_m' max|C_m'|) max|C_m| of the exact
-//      chain (split error 2^-18, dropped ql.Clo 2^-18, fp32 accumulation < 2^-17 on each side).  A key whose best approximate score leads the runner-up by more than 2 eps has a
-//      unique arg-max: that code is final.
-//   3. The other keys (about 1 % for random data) are settled exactly on the spot: their candidates
-//      (all codes within 2 eps of the best) are re-scored by the warp with the defining fp32 chain,
-//      first maximum wins.
-// One CTA = 128 keys of one (batch, kv head); warps 0-3 own one key each per thread, warp 4 issues
-// TMA loads (hi / lo terms of 128-codeword chunks through a 3-slot ring) and the MMAs.  Every wait is bounded.
+//      fp32 codebook is split into two bf16 terms, C = Ch + Cl + eC with |eC| <= 2^-18 |C|.  The
+//      residual is carried as two bf16 terms as well, rho_m = Rh + Rl (rho_0 = k exactly, Rl = 0);
+//      after the code of codebook m is known, t = (Rh + Rl) - C_m[code] in fp32 is re-split.  The
+//      tensor cores form  s~ = Rh.Ch + Rl.Ch + Rh.Cl  with fp32 accumulation.
+//   2. Error of s~ against the defining chain, in units of |r| |C| (|r| <= R = |k| + sum of the
+//      largest codeword norms of the codebooks before m):  split of C and dropped Rl.Cl: 2 * 2^-18;
+//      re-splits of the residual: m * (2^-18 + 3 * 2^-24);  the fp32 chain itself: D * 2^-24 <= 2^-17;
+//      tensor-core accumulation of 3 D exact products, each addition truncated to fp32:
+//      3 D * 2^-23 <= 12.1 * 2^-18;  index tag in the low five mantissa bits (see tag_score): 2^-18.
+//      For M <= 8 that is below 25 * 2^-18; eps = 2^-13 = 32 * 2^-18.
+//      A key whose best approximate score leads the runner-up by more than thr = 2 eps R max|C_m|
+//      has a unique arg-max: that code is final.
+//   3. The other keys (a few per cent for random data) are settled exactly on the spot: every
+//      (key, candidate code within thr of the best) pair of a warp gets a lane, which runs the
+//      defining fp32 chain from global memory; first maximum wins.
+// One CTA owns NS key tiles of 128 keys ("streams", NS = 2 when K <= 256): per stream four warps
+// with one key per thread scan the scores in tensor memory; one warp issues the MMAs of the
+// streams in turn, so the scan of one stream overlaps the MMAs of the other; one warp issues the
+// TMA loads of the codebook terms (16 KB units, 6-slot ring).  Every wait is bounded.
 #include "prefill_tc_common.cuh"
 
 namespace vq {
@@ -23,10 +31,10 @@ namespace vq {
 using namespace ptx;
 
 constexpr int kAtChunk = 128;      // codewords per MMA chunk (one N = 128 instruction)
-constexpr int kAtThreads = 160;    // 4 scan warps + 1 control warp
 constexpr int kAtMaxM = 8;
 constexpr int kAtMaxK = 512;
-constexpr float kAtEps = 3.0517578125e-5f;  // 2^-15
+constexpr float kAtEps = 1.220703125e-4f;  // 2^-13
+constexpr int kAtPairCap = 32;     // (key, candidate) pairs re-scored per pass of a warp
 
 // ------------------------------------------------------------------------------------------------
 // fp32 codebook -> bf16 hi / lo terms [Hkv, M*K, D] and the largest row norm of every codebook.
@@ -71,78 +79,105 @@ struct AtParams {
     void *codes;
     int code_dtype;
     int64_t c_sb, c_sh, c_sl;
-    int Hkv, M, K;
+    int Hkv, M, K, ntiles;
     int64_t L;
     int32_t *status;
 };
 
-template <int D>
+template <int D, int NS>
 struct AtCfg {
     static constexpr int NH = D / 64;
-    static constexpr int kATile = NH * kHalfBytes;               // 128 keys x D bf16
-    static constexpr int kBHalf = kAtChunk * 64 * 2;              // 128 codewords x 64 bf16
-    static constexpr int kUnit = NH * kBHalf;                     // one term (hi or lo) of a chunk = one ring slot
-    static constexpr int kSlots = 3;
-    static constexpr int kAk = 0, kAqh = kATile, kAql = 2 * kATile, kB = 3 * kATile;
+    static constexpr int kATile = NH * kHalfBytes;     // 128 keys x D bf16 (one term of the residual)
+    static constexpr int kUnit = kHalfBytes;           // 128 codewords x 64 columns of one term: one ring slot
+    static constexpr int kSlots = 6;
+    static constexpr int kB = NS * 2 * kATile;         // per stream: Rh then Rl
     static constexpr int kTotal = kB + kSlots * kUnit + 1024;
+    static constexpr int kRegion = NS == 2 ? 256 : 512;  // score columns of a stream in tensor memory
+    static constexpr int kMaxChunks = kRegion / kAtChunk;
+    static constexpr int kMaxGroups = kRegion / 32;
+    static constexpr int kWarpMma = 4 * NS, kWarpTma = 4 * NS + 1;
+    static constexpr int kThreads = (4 * NS + 2) * 32;
 };
 
-// The defining score: one fp32 FMA chain over d of the residual r (shared memory, fp32) against
-// codeword row cc (global, fp32).
-template <int D>
-__device__ __forceinline__ float exact_chain(const float *__restrict__ r, const float *__restrict__ cc)
+// Largest (hi) and second largest (lo) of 32 values: pairs, then merges of (hi, lo) pairs.
+__device__ __forceinline__ void top2_32(const float (&v)[32], float &hi, float &lo)
 {
-    float acc = 0.f;
-#pragma unroll 8
-    for (int d = 0; d < D; d += 4) {
-        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cc + d));
-        const float4 r4 = *reinterpret_cast<const float4 *>(r + d);
-        acc = __fmaf_rn(r4.x, c4.x, acc);
-        acc = __fmaf_rn(r4.y, c4.y, acc);
-        acc = __fmaf_rn(r4.z, c4.z, acc);
-        acc = __fmaf_rn(r4.w, c4.w, acc);
+    float h[16], l[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        h[i] = fmaxf(v[2 * i], v[2 * i + 1]);
+        l[i] = fminf(v[2 * i], v[2 * i + 1]);
     }
-    return acc;
+#pragma unroll
+    for (int n = 8; n >= 1; n >>= 1)
+#pragma unroll
+        for (int i = 0; i < n; ++i) {
+            const float a = h[2 * i], b = h[2 * i + 1];
+            l[i] = fmax3(fminf(a, b), l[2 * i], l[2 * i + 1]);
+            h[i] = fmaxf(a, b);
+        }
+    hi = h[0];
+    lo = l[0];
 }
 
-template <int D>
-__global__ void __launch_bounds__(kAtThreads, 1)
+// A score with its low five mantissa bits replaced by 31 - i (i: index inside a group of 32 codes):
+// the maximum of such values carries the index of a maximal element; the values move by < 2^-18 |v|.
+__device__ __forceinline__ float tag_score(float v, int i)
+{
+    return __uint_as_float((__float_as_uint(v) & 0xffffffe0u) | static_cast<uint32_t>(31 - i));
+}
+
+// 32 score columns of this thread's key as floats (+ bias of their codes)
+__device__ __forceinline__ void load_scores(uint32_t taddr, const float *bm, int c0, float (&v)[32])
+{
+    uint32_t r[32];
+    tmem_ld32(taddr, r);
+    tc_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = __uint_as_float(r[i]);
+        if (bm) v[i] += __ldg(bm + c0 + i);
+    }
+}
+
+template <int D, int NS>
+__global__ void __launch_bounds__(AtCfg<D, NS>::kThreads, 1)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_hi,
                  const __grid_constant__ CUtensorMap tm_lo, AtParams p)
 {
-    using C = AtCfg<D>;
-    constexpr int NH = C::NH;
+    using C = AtCfg<D, NS>;
+    constexpr int NH = C::NH, SL = C::kSlots;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t bar_k, b_full[3], b_free[3], bar_c[kAtMaxK / kAtChunk], bar_q;
+    __shared__ __align__(8) uint64_t bar_k[NS], bar_q[NS], bar_c[NS][C::kMaxChunks], b_full[SL], b_free[SL];
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
-    __shared__ __align__(16) float s_res[4][D];  // per scan warp: exact fp32 residual of the key being re-scored
+    __shared__ uint16_t s_pairs[4 * NS][kAtPairCap];  // per scan warp: (owner lane << 9) | candidate code
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int u = blockIdx.y, b = u / p.Hkv, h = u % p.Hkv;
-    const int64_t j0 = static_cast<int64_t>(blockIdx.x) * kBlock;
     const int M = p.M, K = p.K, MK = M * K;
     const int chunks = K / kAtChunk;
-    const uint32_t tmem_cols = 512u;
-    // K <= 256: the score columns of consecutive codebooks alternate between two 256-column regions, so
-    // the key term of codebook m may be issued while the scan threads still read codebook m - 1
-    const bool two_regions = K <= 256;
+    const int tile0 = static_cast<int>(blockIdx.x) * NS;
+    const int n_act = min(NS, p.ntiles - tile0);       // streams with a tile
+    const int upj = chunks * 2 * NH;                   // ring units per (stream, codebook) job
 
     if (tid == 0) {
-        mbar_init(&bar_k, 1);
-        for (int i = 0; i < 3; ++i) {
+        for (int i = 0; i < NS; ++i) {
+            mbar_init(&bar_k[i], 1);
+            mbar_init(&bar_q[i], 128);
+            for (int c = 0; c < C::kMaxChunks; ++c) mbar_init(&bar_c[i][c], 1);
+        }
+        for (int i = 0; i < SL; ++i) {
             mbar_init(&b_full[i], 1);
             mbar_init(&b_free[i], 1);
         }
-        for (int i = 0; i < kAtMaxK / kAtChunk; ++i) mbar_init(&bar_c[i], 1);
-        mbar_init(&bar_q, 128);
         fence_mbar_init();
         s_err = 0;
     }
-    if (warp == 4) {
+    if (warp == C::kWarpMma) {
         __syncwarp();
-        tmem_alloc(&s_tmem, tmem_cols);
+        tmem_alloc(&s_tmem, 512u);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -150,93 +185,101 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     tc_fence_after();
     const uint32_t tmem = s_tmem;
 
-    if (warp == 4) {
-        // ============================================================ control: TMA loads + MMA issue
+    if (warp == C::kWarpTma) {
+        // ============================================================ TMA producer
         if (lane == 0) {
+            prefetch_tmap(&tm_k); prefetch_tmap(&tm_hi); prefetch_tmap(&tm_lo);
+            for (int s = 0; s < n_act; ++s) {
+                mbar_expect_tx(&bar_k[s], C::kATile);
+#pragma unroll
+                for (int hh = 0; hh < NH; ++hh)
+                    tma_load_4d(smem + s * 2 * C::kATile + hh * kHalfBytes, &tm_k, &bar_k[s], 64 * hh, (tile0 + s) * kBlock, h, b);
+            }
+            // Units in the order the MMA warp consumes them: jobs (codebook m, stream s) with s fastest;
+            // inside a job, per chunk: hi term columns 0-63, 64-127 (D = 128), then the lo term likewise.
+            const int total = n_act * M * upj;
             bool ok = true;
-            mbar_expect_tx(&bar_k, C::kATile);
-#pragma unroll
-            for (int hh = 0; hh < NH; ++hh)
-                tma_load_4d(smem + C::kAk + hh * kHalfBytes, &tm_k, &bar_k, 64 * hh, static_cast<int>(j0), h, b);
-            // The codebook streams through a 3-slot ring in UNITS: unit 2c is the hi term of chunk c
-            // (128 codewords), unit 2c+1 its lo term, chunks numbered through all M codebooks.
-            const int total = 2 * M * chunks;
-            auto issue_load = [&](int g) {
-                const int slot = g % C::kSlots;
-                if (g >= C::kSlots && !mbar_wait(&b_free[slot], ((g / C::kSlots) - 1) & 1)) {
+            for (int g = 0; g < total; ++g) {
+                const int slot = g % SL;
+                if (g >= SL && !mbar_wait(&b_free[slot], ((g / SL) - 1) & 1)) {
                     ok = false;
-                    return;
+                    break;
                 }
-                const int c = g >> 1;
-                const int row = h * MK + (c / chunks) * K + (c % chunks) * kAtChunk;  // row in [Hkv*M*K, D]
-                uint8_t *dst = smem + C::kB + slot * C::kUnit;
+                const int job = g / upj, t = g % upj;
+                const int m = job / n_act;
+                const int ch = t / (2 * NH), rem = t % (2 * NH), is_lo = rem / NH, hh = rem % NH;
+                const int row = h * MK + m * K + ch * kAtChunk;  // row in [Hkv*M*K, D]
                 mbar_expect_tx(&b_full[slot], C::kUnit);
-#pragma unroll
-                for (int hh = 0; hh < NH; ++hh) tma_load_3d(dst + hh * C::kBHalf, (g & 1) ? &tm_lo : &tm_hi, &b_full[slot], 64 * hh, row, 0);
-            };
-            constexpr uint32_t id_pos = idesc_bf16(128, kAtChunk, 0, 0, 0), id_neg = idesc_bf16(128, kAtChunk, 0, 0, 1);
+                tma_load_3d(smem + C::kB + slot * C::kUnit, is_lo ? &tm_lo : &tm_hi, &b_full[slot], 64 * hh, row, 0);
+            }
+            if (!ok) s_err = 1;
+        }
+    } else if (warp == C::kWarpMma) {
+        // ============================================================ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16(128, kAtChunk, 0, 0, 0);
             // descriptors differ only in their 16-byte-granular start address: build the bases once
-            const uint64_t d_k = smem_desc_sw128(smem_u32(smem + C::kAk), 16, 1024);
-            const uint64_t d_qh = smem_desc_sw128(smem_u32(smem + C::kAqh), 16, 1024);
-            const uint64_t d_ql = smem_desc_sw128(smem_u32(smem + C::kAql), 16, 1024);
+            const uint64_t d_a0 = smem_desc_sw128(smem_u32(smem), 16, 1024);
             const uint64_t d_b0 = smem_desc_sw128(smem_u32(smem + C::kB), 16, 1024);
-            issue_load(0);
-            if (total > 1) issue_load(1);
-            if (!mbar_wait(&bar_k, 0)) ok = false;
+            const int total = n_act * M * upj;
+            bool ok = true;
             for (int g = 0; g < total && ok; ++g) {
-                const int c = g >> 1, m = c / chunks, ch = c % chunks, slot = g % C::kSlots;
-                const bool is_lo = g & 1;
-                if (g + 2 < total) issue_load(g + 2);
-                if (!ok || !mbar_wait(&b_full[slot], (g / C::kSlots) & 1)) {
+                const int slot = g % SL;
+                const int job = g / upj, t = g % upj;
+                const int m = job / n_act, s = job % n_act;
+                const int ch = t / (2 * NH), rem = t % (2 * NH), is_lo = rem / NH, hh = rem % NH;
+                if (t == 0) {
+                    // the residual terms of (s, m): the key tile itself for m = 0, else written by the scan threads
+                    if (!(m == 0 ? mbar_wait(&bar_k[s], 0) : mbar_wait(&bar_q[s], (m - 1) & 1))) {
+                        ok = false;
+                        break;
+                    }
+                }
+                if (!mbar_wait(&b_full[slot], (g / SL) & 1)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint64_t d_b = d_b0 + static_cast<uint64_t>((slot * C::kUnit) >> 4);
-                const uint32_t dcol = tmem + (two_regions ? (m & 1) * 256 : 0) + ch * kAtChunk;
-                uint32_t acc = is_lo ? 1u : 0u;
-                if (m > 0 && !two_regions && ch == 0 && !is_lo && !mbar_wait(&bar_q, (m - 1) & 1)) {
-                    ok = false;  // one region only: it is free once the scan of codebook m - 1 is over
-                    break;
+                const uint64_t d_rh = d_a0 + static_cast<uint64_t>((s * 2 * C::kATile + hh * kHalfBytes) >> 4);
+                const uint64_t d_rl = d_rh + static_cast<uint64_t>(C::kATile >> 4);
+                const uint32_t dcol = tmem + s * C::kRegion + ch * kAtChunk;
+                uint32_t acc = rem == 0 ? 0u : 1u;
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    mma_ss(dcol, d_rh + static_cast<uint64_t>((k4 * 32) >> 4), d_b + static_cast<uint64_t>((k4 * 32) >> 4), idesc, acc);
+                    acc = 1;
                 }
-                auto term = [&](uint64_t a_desc, uint32_t idesc) {
+                if (!is_lo && m > 0) {
 #pragma unroll
-                    for (int hh = 0; hh < NH; ++hh)
-#pragma unroll
-                        for (int k4 = 0; k4 < 4; ++k4) {
-                            mma_ss(dcol, a_desc + static_cast<uint64_t>((hh * kHalfBytes + k4 * 32) >> 4),
-                                   d_b + static_cast<uint64_t>((hh * C::kBHalf + k4 * 32) >> 4), idesc, acc);
-                            acc = 1;
-                        }
-                };
-                term(d_k, id_pos);  // the key term needs nothing from the previous codebook's scan
-                if (m > 0) {
-                    // the q terms of codebook m exist once every scan thread has folded in its code of m - 1
-                    if (two_regions && ch == 0 && !is_lo && !mbar_wait(&bar_q, (m - 1) & 1)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    term(d_qh, id_neg);
-                    if (!is_lo) term(d_ql, id_neg);
+                    for (int k4 = 0; k4 < 4; ++k4)
+                        mma_ss(dcol, d_rl + static_cast<uint64_t>((k4 * 32) >> 4), d_b + static_cast<uint64_t>((k4 * 32) >> 4), idesc, 1u);
                 }
                 tc_commit(&b_free[slot]);
-                if (is_lo) tc_commit(&bar_c[ch]);  // this chunk's 128 score columns are complete
+                if (rem == 2 * NH - 1) tc_commit(&bar_c[s][ch]);  // this chunk's 128 score columns are complete
             }
             if (!ok) s_err = 1;
         }
-    } else {
+    } else if ((warp >> 2) < n_act) {
         // ============================================================ scan warps: one key per thread
-        const int row = tid;
+        // Loops are kept rolled on purpose: the warps of the two streams run different phases of this
+        // code at the same time, and it has to stay inside the instruction cache.
+        constexpr unsigned kAll = 0xffffffffu;
+        const int s = warp >> 2, wq = warp & 3;
+        const int row = wq * 32 + lane;
+        const int64_t j0 = static_cast<int64_t>(tile0 + s) * kBlock;
         const int64_t j = j0 + row;
         const bool valid = j < p.L;
-        const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-        const __nv_bfloat16 *krow = p.k + b * p.k_sb + h * p.k_sh + (valid ? j : 0) * p.k_sl;
+        const uint32_t tbase = tmem + (static_cast<uint32_t>(wq * 32) << 16) + s * C::kRegion;
+        const __nv_bfloat16 *kbase = p.k + b * p.k_sb + h * p.k_sh;
+        const __nv_bfloat16 *krow = kbase + (valid ? j : 0) * p.k_sl;
         const float *cbh = p.cb + static_cast<int64_t>(h) * MK * D;
-        float knorm = 0.f;
+        uint8_t *a_rh = smem + s * 2 * C::kATile, *a_rl = a_rh + C::kATile;
+        const int groups = K / 32;
+        float rbound;  // R: bound of the residual's norm
         {
             float ss = 0.f;
-#pragma unroll
+#pragma unroll 4
             for (int d = 0; d < D; d += 8) {
                 const uint4 raw = *reinterpret_cast<const uint4 *>(krow + d);
                 const __nv_bfloat162 *hp = reinterpret_cast<const __nv_bfloat162 *>(&raw);
@@ -246,168 +289,192 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     ss = fmaf(x, x, fmaf(y, y, ss));
                 }
             }
-            knorm = sqrtf(ss) * 1.0001f;
+            rbound = sqrtf(ss) * 1.0001f;
         }
-        float qbound = 0.f;
         bool ok = true;
         int prev[kAtMaxM];
 #pragma unroll
         for (int mm = 0; mm < kAtMaxM; ++mm) prev[mm] = 0;
         for (int m = 0; m < M && ok; ++m) {
             const float cm = p.cmax[h * M + m];
-            const float thr = 2.f * kAtEps * (knorm + qbound) * cm + 1e-30f;
+            const float thr0 = 2.f * kAtEps * rbound * cm + 1e-30f;
             const float *bm = p.bias ? p.bias + (static_cast<int64_t>(h) * M + m) * K : nullptr;
-            const uint32_t region = two_regions ? (m & 1) * 256 : 0;
-            // ---- scan, chunk by chunk as the tensor pipe finishes them: best (first maximum) and runner-up
+            // ---- scan, chunk by chunk as the tensor pipe finishes them: best and runner-up of the tagged
+            // scores (the tag of the best gives its index inside its group of 32).  gbits marks the groups
+            // whose maximum was within the threshold of the running best: a superset of the groups that
+            // can hold a candidate at the end.
             float best = -INFINITY, second = -INFINITY;
-            int bidx = 0;
-            for (int ch = 0; ch < chunks && ok; ++ch) {
-                if (!mbar_wait(&bar_c[ch], m & 1)) {
-                    ok = false;
-                    break;
+            int bgrp = 0;
+            uint32_t gbits = 0;
+#pragma unroll 1
+            for (int g = 0; g < groups && ok; ++g) {
+                if ((g & 3) == 0) {
+                    ok = __all_sync(kAll, mbar_wait(&bar_c[s][g >> 2], m & 1));
+                    tc_fence_after();
+                    if (!ok) break;
                 }
-                tc_fence_after();
+                float v[32];
+                load_scores(tbase + 32 * g, bm, 32 * g, v);
 #pragma unroll
-                for (int q4 = 0; q4 < kAtChunk / 32; ++q4) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem + lane_off + region + ch * kAtChunk + 32 * q4, r);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int c = ch * kAtChunk + 32 * q4 + i;
-                        float v = __uint_as_float(r[i]);
-                        if (bm) v += __ldg(bm + c);
-                        const bool gt = v > best;
-                        second = gt ? best : fmaxf(second, v);
-                        bidx = gt ? c : bidx;
-                        best = gt ? v : best;
-                    }
-                }
+                for (int i = 0; i < 32; ++i) v[i] = tag_score(v[i], i);
+                float hi, lo;
+                top2_32(v, hi, lo);
+                second = fmax3(second, fminf(best, hi), lo);
+                bgrp = hi > best ? g : bgrp;
+                best = fmaxf(best, hi);
+                // with a bias the fp32 additions s + bias round by up to 2^-24 |s + bias| each
+                const float thr_g = bm ? thr0 + fabsf(best) * 4.76837158203125e-7f : thr0;
+                gbits |= (hi >= best - thr_g ? 1u : 0u) << g;
             }
             if (!ok) break;
-            int code = bidx;
+            int code = bgrp * 32 + 31 - static_cast<int>(__float_as_uint(best) & 31u);  // first group holding the maximum
+            const float thr = bm ? thr0 + fabsf(best) * 4.76837158203125e-7f : thr0;
             const bool flagged = valid && !(best - second > thr);
-            unsigned fl = __ballot_sync(0xffffffffu, flagged);
-            if (fl) {
-                // candidate bit-mask of this thread's own row: codes within thr of the best
-                uint32_t mask[kAtMaxK / 32];
+            if (__ballot_sync(kAll, flagged)) {
+                // ---- exact settlement of the warp's doubtful keys: every (key, candidate code) pair gets a
+                // lane; pairs are collected in a list and re-scored whenever it is full, and at the end
+                const float cut = best - thr;
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                uint16_t *list = s_pairs[warp];
+                int n = 0;  // pairs in the list (same in all lanes)
+#pragma unroll 1
+                for (int g = 0; g <= groups; ++g) {
+                    const bool flush = g == groups;
+                    uint32_t bits = 0;  // this thread's candidates inside group g
+                    if (!flush) {
+                        const bool cg = flagged && ((gbits >> g) & 1u);
+                        if (!__ballot_sync(kAll, cg)) continue;
+                        float v[32];
+                        load_scores(tbase + 32 * g, bm, 32 * g, v);
 #pragma unroll
-                for (int w = 0; w < kAtMaxK / 32; ++w) {
-                    mask[w] = 0;
-                    if (w * 32 < K) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem + lane_off + region + w * 32, r);
-                        tc_wait_ld();
-                        uint32_t bits = 0;
+                        for (int i = 0; i < 32; ++i)
+                            if (v[i] >= cut) bits |= 1u << i;
+                        bits = cg ? bits : 0u;
+                    }
+                    for (;;) {
+                        const int cnt = __popc(bits);
+                        int incl = cnt;
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            float v = __uint_as_float(r[i]);
-                            if (bm) v += __ldg(bm + w * 32 + i);
-                            if (v >= best - thr) bits |= 1u << i;
+                        for (int off = 1; off < 32; off <<= 1) {
+                            const int t = __shfl_up_sync(kAll, incl, off);
+                            if (lane >= off) incl += t;
                         }
-                        mask[w] = bits;
+                        const int total = __shfl_sync(kAll, incl, 31);
+                        if (total == 0 && !(flush && n > 0)) break;
+                        int q = n + incl - cnt;
+                        while (bits != 0 && q < kAtPairCap) {
+                            const int bit = __ffs(bits) - 1;
+                            list[q++] = static_cast<uint16_t>((lane << 9) | (g * 32 + bit));
+                            bits &= bits - 1;
+                        }
+                        n = min(kAtPairCap, n + total);
+                        if (n < kAtPairCap && !flush) break;  // room left: collect from the next group first
+                        __syncwarp();
+                        const bool act = lane < n;
+                        int owner = lane, c = 0;
+                        if (act) {
+                            const int e = list[lane];
+                            owner = e >> 9;
+                            c = e & 511;
+                        }
+                        int pv[kAtMaxM];
+#pragma unroll
+                        for (int mm = 0; mm < kAtMaxM; ++mm) pv[mm] = (mm < m) ? __shfl_sync(kAll, prev[mm], owner) : 0;
+                        float sc = -INFINITY;
+                        if (act) {
+                            // the defining chain: r_m = ((k - C_0[c_0]) - C_1[c_1]) - ..., one FMA chain over d
+                            const __nv_bfloat16 *ks = kbase + (j0 + wq * 32 + owner) * p.k_sl;
+                            const float *cc = cbh + (static_cast<int64_t>(m) * K + c) * D;
+                            float acc = 0.f;
+#pragma unroll 8
+                            for (int d = 0; d < D; d += 4) {
+                                const uint2 raw = *reinterpret_cast<const uint2 *>(ks + d);
+                                const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
+                                const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
+                                float4 r4 = make_float4(__low2float(lo2), __high2float(lo2), __low2float(hi2), __high2float(hi2));
+#pragma unroll
+                                for (int mm = 0; mm < kAtMaxM; ++mm)
+                                    if (mm < m) {
+                                        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(mm) * K + pv[mm]) * D + d));
+                                        r4.x = __fsub_rn(r4.x, c4.x);
+                                        r4.y = __fsub_rn(r4.y, c4.y);
+                                        r4.z = __fsub_rn(r4.z, c4.z);
+                                        r4.w = __fsub_rn(r4.w, c4.w);
+                                    }
+                                const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cc + d));
+                                acc = __fmaf_rn(r4.x, c4.x, acc);
+                                acc = __fmaf_rn(r4.y, c4.y, acc);
+                                acc = __fmaf_rn(r4.z, c4.z, acc);
+                                acc = __fmaf_rn(r4.w, c4.w, acc);
+                            }
+                            sc = bm ? __fadd_rn(acc, __ldg(bm + c)) : acc;
+                        }
+                        __syncwarp();
+#pragma unroll 1
+                        for (int t = 0; t < n; ++t) {
+                            const int ot = __shfl_sync(kAll, owner, t), ct = __shfl_sync(kAll, c, t);
+                            const float st = __shfl_sync(kAll, sc, t);
+                            if (lane == ot && (st > bv || (st == bv && ct < bi))) {
+                                bv = st;
+                                bi = ct;
+                            }
+                        }
+                        n = 0;
                     }
                 }
-                while (fl) {
-                    const int src = __ffs(fl) - 1;
-                    fl &= fl - 1;
-                    const int64_t js = __shfl_sync(0xffffffffu, j, src);
-                    int pv[kAtMaxM];
-#pragma unroll
-                    for (int mm = 0; mm < kAtMaxM; ++mm) pv[mm] = __shfl_sync(0xffffffffu, prev[mm], src);
-                    const __nv_bfloat16 *ks = p.k + b * p.k_sb + h * p.k_sh + js * p.k_sl;
-                    // the warp forms the exact residual r_m = ((k - C_0[c_0]) - C_1[c_1]) - ... (4 columns per lane)
-                    __syncwarp();
-                    if (lane * 4 < D) {
-                        const uint2 raw = *reinterpret_cast<const uint2 *>(ks + lane * 4);
-                        const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
-                        const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
-                        float4 r4 = make_float4(__low2float(lo2), __high2float(lo2), __low2float(hi2), __high2float(hi2));
-#pragma unroll
-                        for (int mm = 0; mm < kAtMaxM; ++mm)
-                            if (mm < m) {
-                                const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(mm) * K + pv[mm]) * D + lane * 4));
-                                r4.x = __fsub_rn(r4.x, c4.x);
-                                r4.y = __fsub_rn(r4.y, c4.y);
-                                r4.z = __fsub_rn(r4.z, c4.z);
-                                r4.w = __fsub_rn(r4.w, c4.w);
-                            }
-                        *reinterpret_cast<float4 *>(&s_res[warp][lane * 4]) = r4;
-                    }
-                    __syncwarp();
-                    float bv = -INFINITY;
-                    int bi = 0x7fffffff;
-#pragma unroll
-                    for (int w = 0; w < kAtMaxK / 32; ++w) {
-                        const uint32_t word = __shfl_sync(0xffffffffu, mask[w], src);
-                        if ((word >> lane) & 1u) {
-                            const int c = w * 32 + lane;
-                            float s = exact_chain<D>(&s_res[warp][0], cbh + (static_cast<int64_t>(m) * K + c) * D);
-                            if (bm) s = __fadd_rn(s, __ldg(bm + c));
-                            if (s > bv || (s == bv && c < bi)) {
-                                bv = s;
-                                bi = c;
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int off = 16; off >= 1; off >>= 1) {
-                        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-                        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-                        if (ov > bv || (ov == bv && oi < bi)) {
-                            bv = ov;
-                            bi = oi;
-                        }
-                    }
-                    if (lane == src && bi != 0x7fffffff) code = bi;
-                }
+                if (flagged && bi != 0x7fffffff) code = bi;
             }
 #pragma unroll
             for (int mm = 0; mm < kAtMaxM; ++mm)
                 if (mm == m) prev[mm] = code;
             if (valid) store_code(p.codes, p.code_dtype, b * p.c_sb + h * p.c_sh + j * p.c_sl + m, code);
-            qbound += cm;
+            rbound += cm;
             if (m + 1 < M) {
-                // ---- q += C_m[code], re-split into bf16 hi / lo, written in the 128B-swizzled operand layout.
-                // The warp walks its 32 rows together: lane l owns columns 4l..4l+3 of every row, so the
-                // codeword rows are read with coalesced 16-byte loads.
-                {
-                    const int col = (lane * 4) % D, hh = col >> 6, ch8 = (col & 63) >> 3, sub8 = (col & 7) * 2;
+                // ---- residual -= C_m[code], re-split into bf16 hi / lo in the 128B-swizzled operand layout.
+                // Every thread updates its own key's row, 8 columns (one 16-byte chunk of each term) at a time.
+                const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D;
+                const uint32_t rbase = row * 128;
 #pragma unroll 8
-                    for (int rr = 0; rr < 32; ++rr) {
-                        const int r_row = warp * 32 + rr;
-                        const int r_code = __shfl_sync(0xffffffffu, code, rr);
-                        if (lane * 4 >= D) continue;  // D = 64: half of the lanes have no column
-                        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(m) * K + r_code) * D + col));
-                        const uint32_t off = hh * kHalfBytes + r_row * 128 + ((ch8 ^ (r_row & 7)) << 4) + sub8;
-                        uint2 *ph = reinterpret_cast<uint2 *>(smem + C::kAqh + off);
-                        uint2 *pl = reinterpret_cast<uint2 *>(smem + C::kAql + off);
-                        float q[4] = {0.f, 0.f, 0.f, 0.f};
-                        if (m > 0) {
-                            const uint2 vh = *ph, vl = *pl;
-                            const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&vh);
-                            const __nv_bfloat162 *l2 = reinterpret_cast<const __nv_bfloat162 *>(&vl);
-                            q[0] = __low2float(h2[0]) + __low2float(l2[0]);
-                            q[1] = __high2float(h2[0]) + __high2float(l2[0]);
-                            q[2] = __low2float(h2[1]) + __low2float(l2[1]);
-                            q[3] = __high2float(h2[1]) + __high2float(l2[1]);
-                        }
-                        q[0] += c4.x; q[1] += c4.y; q[2] += c4.z; q[3] += c4.w;
-                        uint32_t wh[2], wl[2];
+                for (int ck = 0; ck < D / 8; ++ck) {
+                    const float4 ca = __ldg(reinterpret_cast<const float4 *>(crow + 8 * ck));
+                    const float4 cb4 = __ldg(reinterpret_cast<const float4 *>(crow + 8 * ck + 4));
+                    const uint32_t off = (ck >> 3) * kHalfBytes + rbase + (((ck & 7) ^ (row & 7)) << 4);
+                    uint4 *ph = reinterpret_cast<uint4 *>(a_rh + off);
+                    uint4 *pl = reinterpret_cast<uint4 *>(a_rl + off);
+                    const uint4 vh = *ph;
+                    const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&vh);
+                    float x[8];
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const __nv_bfloat16 h0 = __float2bfloat16_rn(q[2 * e]), h1 = __float2bfloat16_rn(q[2 * e + 1]);
-                            __nv_bfloat162 hv = __halves2bfloat162(h0, h1);
-                            wh[e] = *reinterpret_cast<uint32_t *>(&hv);
-                            wl[e] = pack_bf16(q[2 * e] - __bfloat162float(h0), q[2 * e + 1] - __bfloat162float(h1));
-                        }
-                        *ph = make_uint2(wh[0], wh[1]);
-                        *pl = make_uint2(wl[0], wl[1]);
+                    for (int e = 0; e < 4; ++e) {
+                        x[2 * e] = __low2float(h2[e]);
+                        x[2 * e + 1] = __high2float(h2[e]);
                     }
+                    if (m > 0) {
+                        const uint4 vl = *pl;
+                        const __nv_bfloat162 *l2 = reinterpret_cast<const __nv_bfloat162 *>(&vl);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            x[2 * e] += __low2float(l2[e]);
+                            x[2 * e + 1] += __high2float(l2[e]);
+                        }
+                    }
+                    x[0] -= ca.x; x[1] -= ca.y; x[2] -= ca.z; x[3] -= ca.w;
+                    x[4] -= cb4.x; x[5] -= cb4.y; x[6] -= cb4.z; x[7] -= cb4.w;
+                    uint32_t wh[4], wl[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat16 h0 = __float2bfloat16_rn(x[2 * e]), h1 = __float2bfloat16_rn(x[2 * e + 1]);
+                        __nv_bfloat162 hv = __halves2bfloat162(h0, h1);
+                        wh[e] = *reinterpret_cast<uint32_t *>(&hv);
+                        wl[e] = pack_bf16(x[2 * e] - __bfloat162float(h0), x[2 * e + 1] - __bfloat162float(h1));
+                    }
+                    *ph = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                    *pl = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
                 fence_proxy_async_smem();
                 tc_fence_before();
-                mbar_arrive(&bar_q);
+                mbar_arrive(&bar_q[s]);
             }
         }
         if (!ok) s_err = 1;
@@ -416,20 +483,21 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     __syncthreads();
     if (s_err && tid == 0) {
         if (p.status) atomicExch(p.status, 3);
+#pragma unroll 1
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);  // let tile loads in flight land
     }
     __syncthreads();
-    if (warp == 4) {
+    if (warp == C::kWarpMma) {
         __syncwarp();
-        tmem_dealloc(tmem, tmem_cols);
+        tmem_dealloc(tmem, 512u);
     }
 }
 
-template <int D>
+template <int D, int NS>
 static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const VqTensorDesc *bias, VqTensorDesc *codes,
                             void *workspace, int32_t *status, cudaStream_t stream)
 {
-    using C = AtCfg<D>;
+    using C = AtCfg<D, NS>;
     const int64_t B = k->shape[0], Hkv = k->shape[1], L = k->shape[2];
     const int64_t M = cb->shape[1], K = cb->shape[2], MK = M * K;
     __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(workspace);
@@ -452,11 +520,12 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     p.c_sb = codes->stride[0]; p.c_sh = codes->stride[1]; p.c_sl = codes->stride[2];
     p.Hkv = static_cast<int>(Hkv); p.M = static_cast<int>(M); p.K = static_cast<int>(K);
     p.L = L;
+    p.ntiles = static_cast<int>((L + kBlock - 1) / kBlock);
     p.status = status;
-    auto kern = assign_tc_kernel<D>;
+    auto kern = assign_tc_kernel<D, NS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
-    dim3 grid(static_cast<unsigned>((L + kBlock - 1) / kBlock), static_cast<unsigned>(B * Hkv));
-    kern<<<grid, kAtThreads, C::kTotal, stream>>>(mk, mhi, mlo, p);
+    dim3 grid(static_cast<unsigned>((p.ntiles + NS - 1) / NS), static_cast<unsigned>(B * Hkv));
+    kern<<<grid, C::kThreads, C::kTotal, stream>>>(mk, mhi, mlo, p);
     return launch_status();
 }
 
@@ -505,6 +574,10 @@ extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc 
         workspace_bytes < vqattn_assign_workspace_bytes(B, Hkv, L, M, K, D))
         return VQ_EWORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return D == 64 ? launch_assign_tc<64>(k, codebooks, bias, codes, workspace, status_word, s)
-                   : launch_assign_tc<128>(k, codebooks, bias, codes, workspace, status_word, s);
+    // two key tiles per CTA share the 512 score columns of tensor memory when a codebook fits 256 of them
+    if (K <= 256)
+        return D == 64 ? launch_assign_tc<64, 2>(k, codebooks, bias, codes, workspace, status_word, s)
+                       : launch_assign_tc<128, 2>(k, codebooks, bias, codes, workspace, status_word, s);
+    return D == 64 ? launch_assign_tc<64, 1>(k, codebooks, bias, codes, workspace, status_word, s)
+                   : launch_assign_tc<128, 1>(k, codebooks, bias, codes, workspace, status_word, s);
 }

@@ -403,6 +403,7 @@ __global__ void __launch_bounds__(kBulkThreads, VQ_BULK_CTAS_PER_SM) decode_bulk
         if (tid == 0 && bp.status) atomicExch(bp.status, 2);
         // copies still in flight must land before the shared memory is released
         if (tid == 0)
+#pragma unroll 1
             for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
         __syncthreads();
     }

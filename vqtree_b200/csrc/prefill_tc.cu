@@ -273,6 +273,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_consta
         if (p.status) atomicExch(p.status, 1);
         // a bounded wait expired: give the tile loads still in flight time to land before the
         // shared memory is handed back (a few milliseconds, then leave regardless)
+#pragma unroll 1
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
     }
     tc_fence_before();

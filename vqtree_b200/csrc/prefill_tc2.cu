@@ -401,6 +401,7 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     if (s_err && tid == 0) {
         if (p.status) atomicExch(p.status, 1);
         // a bounded wait expired: give tile loads still in flight time to land before leaving
+#pragma unroll 1
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
     }
     __syncthreads();

@@ -39,12 +39,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+#ifndef VQ_SPIN_FREE
+#define VQ_SPIN_FREE 4096
+#endif
+#ifndef VQ_SPIN_NS
+#define VQ_SPIN_NS 128
+#endif
 // Bounded wait: ~2^21 polls with back-off (a fraction of a second), then failure.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
     for (uint32_t it = 0; it < (1u << 21); ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (it > 4096) __nanosleep(128);
+        if (it > VQ_SPIN_FREE) __nanosleep(VQ_SPIN_NS);
     }
     return false;
 }
