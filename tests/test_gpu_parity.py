@@ -92,6 +92,22 @@ def test_build_aggregates(api, D, M, K, dtype):
         np.testing.assert_array_equal(vs32.cpu().numpy(), vsum_w.reshape(B, Hkv, 5, M * K, D))
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_build_aggregates_skewed_codes(api, D):
+    """Every key of a block in one or two code rows (far more keys per row than the kernel stages at once)."""
+    B, Hkv, L, M, K = 1, 2, 640, 3, 128
+    g = torch.Generator().manual_seed(17)
+    codes = torch.randint(0, K, (B, Hkv, L, M), generator=g)
+    codes[:, 0, :, 0] = 5                                     # one row takes every key
+    codes[:, 0, :, 1] = torch.where(torch.arange(L) % 3 == 0, 8, 15)  # two rows of one warp
+    codes[:, 1, :128, 2] = 127
+    v = torch.randn(B, Hkv, L, D, generator=g).to(torch.bfloat16)
+    cnt_w, vsum_w = vo.build_aggregates(codes.numpy(), v.float().numpy(), K, NB=4)
+    cnt, vsum = api.build_aggregates(dev(codes.to(torch.uint8)), dev(v), K, nb=4)
+    np.testing.assert_array_equal(cnt.cpu().numpy().reshape(cnt_w.shape), cnt_w.astype(np.float32))
+    np.testing.assert_array_equal(vsum.float().cpu().numpy(), vo.round_bf16(vsum_w.reshape(B, Hkv, 4, M * K, D)))
+
+
 def test_gather_aggregates_from_reference_format(api, golden_dir):
     f = np.load(golden_dir / "fast_w128.npz")
     v_vq, vi = torch.from_numpy(f["v_vq"]), torch.from_numpy(f["vi"]).to(torch.int64)

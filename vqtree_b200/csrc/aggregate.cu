@@ -12,6 +12,11 @@
 
 namespace vq {
 
+// aggregate_reg.cu: bf16 kernel with the running sums in registers
+bool aggregates_reg_eligible(const VqTensorDesc *v, const VqTensorDesc *vsum, int K);
+int launch_aggregates_reg(const VqTensorDesc *codes, const VqTensorDesc *v, int K, VqTensorDesc *cnt, VqTensorDesc *vsum,
+                          cudaStream_t stream);
+
 constexpr int kAggThreads = 256;
 constexpr int kAggCols = 32;    // D-slice per CTA
 constexpr int kAggRows = 256;   // code rows per CTA
@@ -215,6 +220,8 @@ extern "C" int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensor
     if (v->stride[0] % 4 || v->stride[1] % 4 || v->stride[2] % 4 || reinterpret_cast<uintptr_t>(v->ptr) % 16) return VQ_EINVAL_STRIDE;
     if (reinterpret_cast<uintptr_t>(vsum->ptr) % 16) return VQ_EINVAL_STRIDE;
     if (B * Hkv > 65535) return VQ_EUNSUPPORTED;
+    if (NB > 0 && aggregates_reg_eligible(v, vsum, K))
+        return launch_aggregates_reg(codes, v, K, cnt, vsum, static_cast<cudaStream_t>(stream));
     int rows = static_cast<int>(K < kAggRows ? K : kAggRows);
     if (K % rows != 0) return VQ_EUNSUPPORTED;
     const int parts = static_cast<int>(K / rows);
