@@ -57,8 +57,11 @@ typedef struct VqTensorDesc {
 } VqTensorDesc;
 
 /* Which prefill kernel to run; AUTO picks the pipelined tensor-core kernel for bf16 and the fp32
- * kernel for f32.  TENSOR_SERIAL is the non-pipelined tensor-core kernel (same arithmetic). */
-typedef enum VqPrefillImpl { VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2, VQ_IMPL_TENSOR_SERIAL = 3 } VqPrefillImpl;
+ * kernel for f32.  TENSOR_SERIAL is the non-pipelined tensor-core kernel, TENSOR_TWOSTREAM the
+ * pipelined kernel with two softmax states merged at the end (same arithmetic up to rounding). */
+typedef enum VqPrefillImpl {
+    VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2, VQ_IMPL_TENSOR_SERIAL = 3, VQ_IMPL_TENSOR_TWOSTREAM = 4
+} VqPrefillImpl;
 
 int vqattn_version(void);
 const char *vqattn_status_string(int status);
@@ -108,8 +111,12 @@ int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensorDesc *v, in
  *   v_vq [B,H,L+1,D] f32|bf16 (sorted within-code prefix sums, ops/attn_vq.py:364-383)
  *   vi   [B,H,NBin,C] i32|i64 (row of v_vq per block and code, ops/attn_vq.py:384,412-413)
  *   ->   vsum [B,H,NB,C,D] (same dtype as v_vq), NB <= NBin
+ *   cnt  [B,H,NB,C] f32 dense, optional (NULL or ptr NULL): rows of codes without members
+ *        (cnt == 0) are written as zeros, which vqattn_prefill relies on (see below); the reference
+ *        masks such codes inside its kernel instead (ops/triton_fused_vq_attn.py:52-56).
  */
-int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensorDesc *vi, VqTensorDesc *vsum, void *stream);
+int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensorDesc *vi, const VqTensorDesc *cnt, VqTensorDesc *vsum,
+                             void *stream);
 
 /*
  * Fused prefill attention.  Replaces ops/triton_fused_vq_attn.py:190-251 vq_attn_forward, i.e. the
@@ -122,6 +129,8 @@ int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensorDesc *vi, V
  *       score q2_i.codebook[r] for every row r with cnt[r] > 0, numerator weight vsum[r],
  *       denominator weight cnt[r]                         (ops/triton_fused_vq_attn.py:38-68)
  * All of q1,q2,k1,k3,v,codebook,vsum,out share one dtype (f32 or bf16); math is fp32.
+ * vsum rows of codes with cnt == 0 must be zero (vqattn_build_aggregates and vqattn_gather_aggregates
+ * with cnt produce them so): the tensor-core kernel lets such codes take part with weight zero.
  *   q1,q2,out [B,Hq,L,D]; k1,k3,v [B,Hkv,L,D]; codebook [Hkv,MK,D]; cnt [B,Hkv,NB,MK] f32;
  *   vsum [B,Hkv,NB,MK,D]; lse2 NULL or [B,Hq,L] f32 (base-2 log-sum-exp of the scaled scores).
  * Constraints: D in {64,128}; window % 128 == 0; MK % 128 == 0; Hq % Hkv == 0;

@@ -117,6 +117,12 @@ def test_gather_aggregates_from_reference_format(api, golden_dir):
     for b in range(B):
         for h in range(H):
             np.testing.assert_array_equal(got[b, h], f["v_vq"][b, h][f["vi"][b, h]])
+    # with the counts: rows of codes without members come out as zeros
+    cnt = torch.from_numpy(f["k_vq_cnt"]).float()
+    assert (cnt == 0).any()
+    got0 = api.gather_aggregates(dev(v_vq), dev(vi), nb, dev(cnt)).cpu().numpy()
+    keep = (f["k_vq_cnt"] > 0)[..., None]
+    np.testing.assert_array_equal(got0, np.where(keep, got, 0.0))
 
 
 # ----------------------------------------------------------------------------- prefill
@@ -145,9 +151,9 @@ PREFILL_CASES = [
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,L,D,M,K,W,seed,rerope,dtype", PREFILL_CASES)
-@pytest.mark.parametrize("impl", ["simt", "tensor"])
+@pytest.mark.parametrize("impl", ["simt", "tensor", "tensor_twostream", "tensor_serial"])
 def test_prefill_matches_naive_oracle(api, impl, B, Hq, Hkv, L, D, M, K, W, seed, rerope, dtype):
-    if impl == "tensor" and dtype != torch.bfloat16:
+    if impl.startswith("tensor") and dtype != torch.bfloat16:
         pytest.skip("the tensor-core kernel computes in bf16")
     case = make_case(B, Hq, Hkv, L, D, M, K, W, seed, rerope, dtype)
     want, codes = oracle_prefill(case)

@@ -17,7 +17,7 @@ from . import native
 from .native import BLOCK, VqDecodeArgs, VqPrefillArgs, check, desc, lib, stream_ptr
 
 _IMPL = {"auto": native.IMPL_AUTO, "simt": native.IMPL_SIMT, "tensor": native.IMPL_TENSOR,
-         "tensor_serial": native.IMPL_TENSOR_SERIAL}
+         "tensor_serial": native.IMPL_TENSOR_SERIAL, "tensor_twostream": native.IMPL_TENSOR_TWOSTREAM}
 
 
 def _require_cuda(*ts):
@@ -106,9 +106,13 @@ def build_aggregates(codes: torch.Tensor, v: torch.Tensor, K: int, nb: Optional[
     return cnt, vsum
 
 
-def gather_aggregates(v_vq: torch.Tensor, vi: torch.Tensor, nb: int) -> torch.Tensor:
-    """Dense value sums from the reference's sorted-prefix format (v_vq [B,H,L+1,D], vi [B,H,NB,C])."""
-    dev = _require_cuda(v_vq, vi)
+def gather_aggregates(v_vq: torch.Tensor, vi: torch.Tensor, nb: int, cnt: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense value sums from the reference's sorted-prefix format (v_vq [B,H,L+1,D], vi [B,H,NB,C]).
+
+    cnt [B,H,nb,C] f32 (optional): rows of codes with cnt == 0 are written as zeros, as the prefill
+    kernels expect (the reference masks those codes inside its kernel).
+    """
+    dev = _require_cuda(v_vq, vi, cnt)
     B, H, _, D = v_vq.shape
     C = vi.shape[-1]
     if vi.dtype not in (torch.int32, torch.int64):
@@ -116,7 +120,8 @@ def gather_aggregates(v_vq: torch.Tensor, vi: torch.Tensor, nb: int) -> torch.Te
     vsum = torch.empty((B, H, nb, C, D), dtype=v_vq.dtype, device=dev)
     if nb > 0:
         with torch.cuda.device(dev):
-            check(lib.vqattn_gather_aggregates(desc(v_vq), desc(vi), desc(vsum), stream_ptr(dev)), "vqattn_gather_aggregates")
+            check(lib.vqattn_gather_aggregates(desc(v_vq), desc(vi), desc(cnt), desc(vsum), stream_ptr(dev)),
+                  "vqattn_gather_aggregates")
     return vsum
 
 

@@ -153,7 +153,8 @@ build_aggregates_kernel(const void *__restrict__ codes, int code_dtype, int64_t 
 template <typename T>
 __global__ void gather_aggregates_kernel(const T *__restrict__ v_vq, int64_t s_b, int64_t s_h, int64_t s_n,
                                          const void *__restrict__ vi, int vi_dtype, int64_t i_b, int64_t i_h, int64_t i_n,
-                                         T *__restrict__ vsum, int H, int NB, int C, int D, int64_t rows_in)
+                                         const float *__restrict__ cnt, T *__restrict__ vsum, int H, int NB, int C, int D,
+                                         int64_t rows_in)
 {
     // one warp per output row
     const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
@@ -165,7 +166,7 @@ __global__ void gather_aggregates_kernel(const T *__restrict__ v_vq, int64_t s_b
     const int64_t at = b * i_b + h * i_h + n * i_n + c;
     const int64_t src = vi_dtype == VQ_I64 ? static_cast<const int64_t *>(vi)[at] : static_cast<const int32_t *>(vi)[at];
     T *dst = vsum + ((static_cast<int64_t>(u) * NB + n) * C + c) * D;
-    const bool ok = src >= 0 && src < rows_in;
+    const bool ok = src >= 0 && src < rows_in && (cnt == nullptr || cnt[(static_cast<int64_t>(u) * NB + n) * C + c] > 0.f);
     const T *s = v_vq + b * s_b + h * s_h + (ok ? src : 0) * s_n;
     for (int d = lane; d < D; d += 32) dst[d] = ok ? s[d] : from_f32<T>(0.f);
 }
@@ -248,10 +249,12 @@ extern "C" int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensor
     return launch_status();
 }
 
-extern "C" int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensorDesc *vi, VqTensorDesc *vsum, void *stream)
+extern "C" int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensorDesc *vi, const VqTensorDesc *cnt,
+                                        VqTensorDesc *vsum, void *stream)
 {
     using namespace vq;
     int st;
+    if (cnt != nullptr && cnt->ptr == nullptr) cnt = nullptr;
     if ((st = check_basic(v_vq, 4)) != VQ_OK) return st;
     if ((st = check_basic(vi, 4)) != VQ_OK) return st;
     if ((st = check_basic(vsum, 5)) != VQ_OK) return st;
@@ -264,6 +267,13 @@ extern "C" int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensor
     if (vi->shape[0] != B || vi->shape[1] != H || vi->shape[2] < NB || vi->shape[3] != C) return VQ_EINVAL_SHAPE;
     if (vsum->shape[0] != B || vsum->shape[1] != H || vsum->shape[4] != D) return VQ_EINVAL_SHAPE;
     if (!is_dense(*vsum)) return VQ_EINVAL_STRIDE;
+    if (cnt != nullptr) {
+        if ((st = check_basic(cnt, 4)) != VQ_OK) return st;
+        if (cnt->dtype != VQ_F32) return VQ_EINVAL_DTYPE;
+        if (cnt->shape[0] != B || cnt->shape[1] != H || cnt->shape[2] != NB || cnt->shape[3] != C) return VQ_EINVAL_SHAPE;
+        if (!is_dense(*cnt) || cnt->device != vsum->device) return VQ_EINVAL_STRIDE;
+    }
+    const float *cntp = cnt ? static_cast<const float *>(cnt->ptr) : nullptr;
     if (B * H > 65535) return VQ_EUNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int warps = 8;
@@ -271,12 +281,12 @@ extern "C" int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensor
     if (v_vq->dtype == VQ_F32)
         gather_aggregates_kernel<float><<<grid, warps * 32, 0, s>>>(
             static_cast<const float *>(v_vq->ptr), v_vq->stride[0], v_vq->stride[1], v_vq->stride[2], vi->ptr, vi->dtype,
-            vi->stride[0], vi->stride[1], vi->stride[2], static_cast<float *>(vsum->ptr), static_cast<int>(H),
+            vi->stride[0], vi->stride[1], vi->stride[2], cntp, static_cast<float *>(vsum->ptr), static_cast<int>(H),
             static_cast<int>(NB), static_cast<int>(C), static_cast<int>(D), v_vq->shape[2]);
     else
         gather_aggregates_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
             static_cast<const __nv_bfloat16 *>(v_vq->ptr), v_vq->stride[0], v_vq->stride[1], v_vq->stride[2], vi->ptr,
-            vi->dtype, vi->stride[0], vi->stride[1], vi->stride[2], static_cast<__nv_bfloat16 *>(vsum->ptr),
+            vi->dtype, vi->stride[0], vi->stride[1], vi->stride[2], cntp, static_cast<__nv_bfloat16 *>(vsum->ptr),
             static_cast<int>(H), static_cast<int>(NB), static_cast<int>(C), static_cast<int>(D), v_vq->shape[2]);
     return launch_status();
 }

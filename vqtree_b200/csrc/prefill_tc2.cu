@@ -238,8 +238,12 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_bf16(128, 128, 0, 0);
             constexpr uint32_t idesc_pv = idesc_bf16(128, D, 0, 1);
-            const uint32_t q1_addr = smem_u32(smem + C::kQ1);
-            const uint32_t q2_addr = p.rerope ? smem_u32(smem + C::kQ2) : q1_addr;
+            // operand descriptors differ only in their 16-byte-granular start address: the bases are built
+            // once, every MMA adds a compile-time offset (the issuing thread is a serial resource)
+            const uint64_t d_q1 = smem_desc_sw128(smem_u32(smem + C::kQ1), 16, 1024);
+            const uint64_t d_q2 = p.rerope ? smem_desc_sw128(smem_u32(smem + C::kQ2), 16, 1024) : d_q1;
+            const uint64_t d_k0 = smem_desc_sw128(smem_u32(smem + C::kRing), 16, 1024);          // K tiles: K-major
+            const uint64_t d_v0 = smem_desc_sw128(smem_u32(smem + C::kRing), kHalfBytes, 1024);  // V tiles: MN-major
             bool ok = mbar_wait(&bar_q, 0);
             int q = 0;
             auto qk = [&](int it) {
@@ -251,15 +255,16 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
                 }
                 tc_fence_after();
                 const int kind = work.kind(it);
-                const uint32_t qa = (kind == kFar || kind == kBdA) ? q2_addr : q1_addr;
-                const uint32_t ka = smem_u32(smem + C::kRing + slot * C::kTile);
+                const uint64_t da = (kind == kFar || kind == kBdA) ? d_q2 : d_q1;
+                const uint64_t db = d_k0 + static_cast<uint64_t>((slot * C::kTile) >> 4);
                 const uint32_t sdst = tmem + (s ? C::kColS1 : C::kColS0);
 #pragma unroll
                 for (int h = 0; h < NH; ++h)
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)
-                        mma_ss(sdst, smem_desc_sw128(qa + h * kHalfBytes + k4 * 32, 16, 1024),
-                               smem_desc_sw128(ka + h * kHalfBytes + k4 * 32, 16, 1024), idesc_qk, (h | k4) ? 1u : 0u);
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const uint64_t off = static_cast<uint64_t>((h * kHalfBytes + k4 * 32) >> 4);
+                        mma_ss(sdst, da + off, db + off, idesc_qk, (h | k4) ? 1u : 0u);
+                    }
                 tc_commit(&kv_empty[slot]);  // K tile free once these MMAs have read it
                 tc_commit(&s_full[s]);       // S ready for the softmax warps of stream s
                 ++q;
@@ -272,14 +277,13 @@ prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
                     return;
                 }
                 tc_fence_after();
-                const uint32_t va = smem_u32(smem + C::kRing + slot * C::kTile);
+                const uint64_t dv = d_v0 + static_cast<uint64_t>((slot * C::kTile) >> 4);
                 const uint32_t odst = tmem + (s ? C::kColO1 : C::kColO0);
                 const uint32_t psrc = tmem + (s ? C::kColS1 : C::kColS0);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)
                     mma_ts(odst, psrc + (kk < 4 ? 8 * kk : 64 + 8 * (kk - 4)),  // keys 0-63 at columns 0.., keys 64-127 at columns 64..
-                           smem_desc_sw128(va + kk * 2048, kHalfBytes, 1024), idesc_pv,
-                           ((it >> 1) | kk) ? 1u : 0u);
+                           dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv, ((it >> 1) | kk) ? 1u : 0u);
                 tc_commit(&kv_empty[slot]);
                 if (it + 2 >= n) tc_commit(&o_done[s]);  // last product of this stream
                 ++q;

@@ -1,0 +1,429 @@
+// Fused VQ-attention prefill on the sm_100a tensor cores: one softmax state per query row, three
+// score buffers, the row maximum of the NEXT item found while the tensor pipe still works on it.
+//
+// One CTA owns one 128-row query tile of one (batch, query head) and walks its work items (far
+// codebook tiles, boundary block, interior blocks, causal diagonal - see TcWork) with ONE online
+// softmax (this replaces the reference's two kernels and their log-sum-exp merge,
+// ops/triton_fused_vq_attn.py:202-250).  Tensor memory holds three S/P buffers (128 columns each)
+// and the O accumulator.  Roles:
+//   warps 0-15  softmax: FOUR threads per query row, 32 key columns each (warp w: rows 32 (w & 3)..,
+//               columns 32 (w >> 2)..).  In iteration j a thread first reads S(j+1), publishes its
+//               partial row maximum and arrives on a barrier shared by the 128 threads of its 32 rows;
+//               then it picks up the maxima of S(j) published one iteration earlier (the barrier has
+//               long completed), and exponentiates S(j) into P(j) (packed bf16 over its own S columns).
+//               The exchange of maxima therefore never stalls the exponentials, and the warps of one SM
+//               sub-partition drift apart so that the special-function unit stays busy.  O is rescaled
+//               only when the maximum grew by more than 2^8 (rare), after the last product finished.
+//   warp 16     one thread issues every tcgen05.mma: S(j) = Q K(j)^T three items ahead (operands in
+//               shared memory), O += P(j) V(j) (P from tensor memory, V MN-major in shared memory);
+//   warp 17     one thread issues the TMA tile loads into a ring of four 32 KB slots in the order the
+//               tensor pipe consumes them (K0 K1 K2 V0 K3 V1 ...).
+// Hand-offs are mbarriers (tcgen05.commit arrives for the MMA side); every wait is bounded and a
+// failed wait raises the status word; all roles meet at one final barrier and TMEM is freed.
+#include "prefill_tc_common.cuh"
+
+namespace vq {
+
+using namespace ptx;
+
+constexpr int kT3Threads = 576;   // 16 softmax warps + MMA warp + TMA warp
+constexpr int kT3WarpMma = 16, kT3WarpTma = 17;
+constexpr int kT3Bufs = 3;        // S/P buffers
+constexpr float kT3Lazy = 8.f;    // log2 units: P stays below 2^8
+
+template <int D>
+struct T3Cfg {
+    static constexpr int NH = D / 64;
+    static constexpr int kTile = NH * kHalfBytes;             // 128 x D bf16
+    static constexpr int kSlots = 4;                           // ring of K / V tiles
+    static constexpr int kQ1 = 0, kQ2 = kTile, kRing = 2 * kTile;
+    static constexpr int kTotal = kRing + kSlots * kTile + 1024;  // + slack for 1024-byte alignment
+    static constexpr uint32_t kColS = 0, kColO = 128 * kT3Bufs, kCols = 512;
+    static constexpr int kOq = D / 4;                          // O columns rescaled / written by one thread
+};
+
+// One thread's 32 score columns of an item.  MODE 0: no mask; 1: columns [lo, hi) valid (relative to
+// this thread's first column); 2: far tile.  A far tile needs no mask: a code without members has a
+// zero value-sum row and weight 0 in the denominator, so its P contributes nothing; it can only raise
+// the reference maximum, which the softmax is invariant to (scores are far inside the exponent range).
+template <int MODE>
+__device__ __forceinline__ void t3_mask2(float &x0, float &x1, int c0, int lo, int hi)
+{
+    if (MODE == 1) {
+        x0 = (c0 >= lo && c0 < hi) ? x0 : -INFINITY;
+        x1 = (c0 + 1 >= lo && c0 + 1 < hi) ? x1 : -INFINITY;
+    }
+}
+
+template <int MODE>
+__device__ __forceinline__ float t3_max_pass(uint32_t s_addr, int lo, int hi)
+{
+    uint32_t r[32];
+    tmem_ld32(s_addr, r);
+    tc_wait_ld();
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        float a0 = __uint_as_float(r[2 * j]), a1 = __uint_as_float(r[2 * j + 1]);
+        t3_mask2<MODE>(a0, a1, 2 * j, lo, hi);
+        mx[j & 3] = fmax3(mx[j & 3], a0, a1);
+    }
+    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
+
+// P = exp2(S * scale - m) for the thread's 32 columns, packed bf16 written over its first 16 S columns;
+// returns the (count-weighted for MODE 2) sum of the 32 values.
+template <int MODE>
+__device__ __forceinline__ float t3_exp_pass(uint32_t s_addr, const float *cw, int lo, int hi,
+                                             float scale_log2, float neg_m)
+{
+    uint32_t r[32], pk[16];
+    tmem_ld32(s_addr, r);
+    tc_wait_ld();
+    float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int c0 = 2 * j;
+        float x0 = __uint_as_float(r[c0]), x1 = __uint_as_float(r[c0 + 1]);
+        float t0, t1;
+        t3_mask2<MODE>(x0, x1, c0, lo, hi);
+        ffma2(t0, t1, x0, x1, scale_log2, scale_log2, neg_m, neg_m);
+        const float p0 = ex2(t0), p1 = ex2(t1);
+        if (MODE == 2) ffma2(ls[2 * (j & 1)], ls[2 * (j & 1) + 1], p0, p1, cw[c0], cw[c0 + 1], ls[2 * (j & 1)], ls[2 * (j & 1) + 1]);
+        else fadd2(ls[2 * (j & 1)], ls[2 * (j & 1) + 1], ls[2 * (j & 1)], ls[2 * (j & 1) + 1], p0, p1);
+        pk[j] = pack_bf16(p0, p1);
+    }
+    tmem_st16(s_addr, pk);
+    return (ls[0] + ls[1]) + (ls[2] + ls[3]);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kT3Threads, 1)
+prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
+                   const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k3,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_cb,
+                   const __grid_constant__ CUtensorMap tm_vs, TcParams p)
+{
+    using C = T3Cfg<D>;
+    constexpr int NH = C::NH, NS = C::kSlots, NB3 = kT3Bufs;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t bar_q, kv_full[NS], kv_empty[NS], s_full[NB3], p_full[NB3], pv_done[NB3], maxbar[4][NB3], lbar[4];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_err;
+    __shared__ __align__(16) float s_cw[16][2][32];      // [softmax warp][item parity][column]: counts of a far tile
+    __shared__ __align__(16) float s_xch[NB3][kBlock][4]; // [item % 3][row][column quarter]: partial row maxima
+    __shared__ __align__(16) float s_l[kBlock][4];        // partial denominators at the end
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m = p.ntiles - 1 - static_cast<int>(blockIdx.x);  // heavy tiles first
+    const int bh = blockIdx.y;
+    const int b = bh / p.Hq, hq = bh % p.Hq;
+    const int hk = hq / (p.Hq / p.Hkv);
+    const int u = b * p.Hkv + hk;
+    const TcWork work(p, m);
+    const int n = work.n_items;
+
+    if (tid == 0) {
+        mbar_init(&bar_q, 1);
+        for (int i = 0; i < NS; ++i) {
+            mbar_init(&kv_full[i], 1);
+            mbar_init(&kv_empty[i], 1);
+        }
+        for (int i = 0; i < NB3; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 16);    // one arrival per softmax warp
+            mbar_init(&pv_done[i], 1);
+            for (int g = 0; g < 4; ++g) mbar_init(&maxbar[g][i], 4);
+        }
+        for (int g = 0; g < 4; ++g) mbar_init(&lbar[g], 4);
+        fence_mbar_init();
+        s_err = 0;
+    }
+    if (warp == kT3WarpTma) {
+        __syncwarp();
+        tmem_alloc(&s_tmem, C::kCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    if (warp == kT3WarpTma) {
+        // ================================================================== TMA producer
+        if (lane == 0) {
+            prefetch_tmap(&tm_q1); prefetch_tmap(&tm_k1); prefetch_tmap(&tm_v);
+            mbar_expect_tx(&bar_q, (p.rerope ? 2 : 1) * C::kTile);
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                tma_load_4d(smem + C::kQ1 + h * kHalfBytes, &tm_q1, &bar_q, 64 * h, m * kBlock, hq, b);
+                if (p.rerope) tma_load_4d(smem + C::kQ2 + h * kHalfBytes, &tm_q2, &bar_q, 64 * h, m * kBlock, hq, b);
+            }
+            bool ok = true;
+            int q = 0;  // position in the consumption sequence K0 K1 K2 V0 K3 V1 ...
+            auto load = [&](int it, bool is_v) {
+                if (!ok) return;
+                const int slot = q % NS;
+                if (q >= NS && !mbar_wait(&kv_empty[slot], ((q / NS) - 1) & 1)) {
+                    ok = false;
+                    return;
+                }
+                const int kind = work.kind(it), blk = work.block(it);
+                uint8_t *dst = smem + C::kRing + slot * C::kTile;
+                mbar_expect_tx(&kv_full[slot], C::kTile);
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    if (kind == kFar) {
+                        if (is_v) tma_load_3d(dst + h * kHalfBytes, &tm_vs, &kv_full[slot], 64 * h, blk * kBlock, u * p.NB + work.far_blk);
+                        else tma_load_3d(dst + h * kHalfBytes, &tm_cb, &kv_full[slot], 64 * h, blk * kBlock, hk);
+                    } else {
+                        const CUtensorMap *tm = is_v ? &tm_v : (kind == kBdA ? &tm_k3 : &tm_k1);
+                        tma_load_4d(dst + h * kHalfBytes, tm, &kv_full[slot], 64 * h, blk * kBlock, hk, b);
+                    }
+                }
+                ++q;
+            };
+            for (int j = 0; j < NB3 && j < n; ++j) load(j, false);
+            for (int j = 0; j < n; ++j) {
+                load(j, true);
+                if (j + NB3 < n) load(j + NB3, false);
+            }
+            if (!ok) s_err = 1;
+        }
+    } else if (warp == kT3WarpMma) {
+        // ================================================================== MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc_bf16(128, 128, 0, 0);
+            constexpr uint32_t idesc_pv = idesc_bf16(128, D, 0, 1);
+            // operand descriptors differ only in their 16-byte-granular start address
+            const uint64_t d_q1 = smem_desc_sw128(smem_u32(smem + C::kQ1), 16, 1024);
+            const uint64_t d_q2 = p.rerope ? smem_desc_sw128(smem_u32(smem + C::kQ2), 16, 1024) : d_q1;
+            const uint64_t d_k0 = smem_desc_sw128(smem_u32(smem + C::kRing), 16, 1024);          // K tiles: K-major
+            const uint64_t d_v0 = smem_desc_sw128(smem_u32(smem + C::kRing), kHalfBytes, 1024);  // V tiles: MN-major
+            bool ok = mbar_wait(&bar_q, 0);
+            int q = 0;
+            auto qk = [&](int it) {  // S(it) = Q K(it)^T into buffer it % 3 (free: the product of item it - 3 was issued before)
+                if (!ok) return;
+                const int slot = q % NS, buf = it % NB3;
+                if (!mbar_wait(&kv_full[slot], (q / NS) & 1)) {
+                    ok = false;
+                    return;
+                }
+                tc_fence_after();
+                const int kind = work.kind(it);
+                const uint64_t da = (kind == kFar || kind == kBdA) ? d_q2 : d_q1;
+                const uint64_t db = d_k0 + static_cast<uint64_t>((slot * C::kTile) >> 4);
+                const uint32_t sdst = tmem + C::kColS + 128 * buf;
+#pragma unroll
+                for (int h = 0; h < NH; ++h)
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const uint64_t off = static_cast<uint64_t>((h * kHalfBytes + k4 * 32) >> 4);
+                        mma_ss(sdst, da + off, db + off, idesc_qk, (h | k4) ? 1u : 0u);
+                    }
+                tc_commit(&kv_empty[slot]);
+                tc_commit(&s_full[buf]);
+                ++q;
+            };
+            auto pv = [&](int it) {  // O += P(it) V(it)
+                if (!ok) return;
+                const int slot = q % NS, buf = it % NB3;
+                if (!mbar_wait(&p_full[buf], (it / NB3) & 1) || !mbar_wait(&kv_full[slot], (q / NS) & 1)) {
+                    ok = false;
+                    return;
+                }
+                tc_fence_after();
+                const uint64_t dv = d_v0 + static_cast<uint64_t>((slot * C::kTile) >> 4);
+                const uint32_t odst = tmem + C::kColO, psrc = tmem + C::kColS + 128 * buf;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)  // keys 16 kk ..: written by column quarter kk / 2 at its columns 8 (kk & 1) ..
+                    mma_ts(odst, psrc + 32 * (kk >> 1) + 8 * (kk & 1), dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
+                           (it | kk) ? 1u : 0u);
+                tc_commit(&kv_empty[slot]);
+                tc_commit(&pv_done[buf]);
+                ++q;
+            };
+            for (int j = 0; j < NB3 && j < n; ++j) qk(j);
+            for (int j = 0; j < n; ++j) {
+                pv(j);
+                if (j + NB3 < n) qk(j + NB3);
+            }
+            if (!ok) s_err = 1;
+        }
+    } else {
+        // ================================================================== softmax
+        constexpr unsigned kAll = 0xffffffffu;
+        const int lq = warp & 3, cq = warp >> 2;         // lane quarter (32 query rows) and column quarter (32 keys)
+        const int row = lq * 32 + lane;                   // query row inside the tile (= TMEM lane)
+        const uint32_t lane_off = static_cast<uint32_t>(lq * 32) << 16;
+        const uint32_t s_base = tmem + lane_off + C::kColS + 32 * cq;  // + 128 * buffer
+        const uint32_t o_addr = tmem + lane_off + C::kColO + cq * C::kOq;
+        float row_m = -INFINITY, l_part = 0.f;            // row_m: the maximum P and O are currently scaled by
+        bool ok = true;
+        // Counts of a far tile: lane l of the warp fetches the count of the warp's column l one item
+        // ahead and the warp keeps them in its own shared-memory slot.
+        const float *cnt_base = p.cnt + (static_cast<int64_t>(u) * p.NB + work.far_blk) * p.MK + 32 * cq + lane;
+        float *cw_w = &s_cw[warp][0][0];
+        float cnt_reg = work.n_far > 0 ? __ldg(cnt_base) : 0.f;
+        auto publish_counts = [&](int it, float c) {
+            __syncwarp();
+            cw_w[(it & 1) * 32 + lane] = c;
+            __syncwarp();
+        };
+        // valid key columns of this row in item `it`, relative to this thread's first column: [lo, hi)
+        auto bounds = [&](int kind, int &lo, int &hi) {
+            lo = 0;
+            hi = 32;
+            if (kind == kDiag) hi = row + 1 - 32 * cq;
+            else if (kind == kBdA) hi = row - 32 * cq;
+            else if (kind == kBdB) lo = row - 32 * cq;
+        };
+        // partial row maximum of item `it`, published for the other three threads of the row
+        auto publish_max = [&](int it) {
+            if (it < work.n_far) publish_counts(it, cnt_reg);
+            cnt_reg = (it + 1 < work.n_far) ? __ldg(cnt_base + (it + 1) * kBlock) : 0.f;
+            const int buf = it % NB3;
+            if (!__all_sync(kAll, mbar_wait(&s_full[buf], (it / NB3) & 1))) return false;
+            tc_fence_after();
+            const int kind = work.kind(it);
+            int lo, hi;
+            bounds(kind, lo, hi);
+            const uint32_t sa = s_base + 128 * buf;
+            const float mx = (kind == kFar || kind == kFull) ? t3_max_pass<0>(sa, lo, hi) : t3_max_pass<1>(sa, lo, hi);
+            s_xch[buf][row][cq] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&maxbar[lq][buf]);  // one arrival per warp: its 32 stores are ordered before it
+            return true;
+        };
+        ok = publish_max(0);
+        for (int it = 0; it < n && ok; ++it) {
+            const int buf = it % NB3;
+            // ---- the next item's maximum first: by the time it is needed everybody has published it
+            if (it + 1 < n && !publish_max(it + 1)) {
+                ok = false;
+                break;
+            }
+            // ---- this item's row maximum
+            if (!__all_sync(kAll, mbar_wait(&maxbar[lq][buf], (it / NB3) & 1))) {
+                ok = false;
+                break;
+            }
+            const float4 m4 = *reinterpret_cast<const float4 *>(&s_xch[buf][row][0]);
+            const float m_tile = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w)) * p.scale_log2;
+            // lazy rescaling: keep the old reference maximum unless the new one is far above it
+            float m_use = row_m;
+            if (m_tile > row_m + kT3Lazy || row_m == -INFINITY) m_use = fmaxf(row_m, m_tile);
+            const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
+            const float alpha = (m_use == row_m) ? 1.f : ex2(row_m - m_safe);  // row_m = -inf -> 0
+            if (it > 0 && __any_sync(kAll, alpha != 1.f)) {
+                // O may be touched once the product of the previous item has finished
+                if (!__all_sync(kAll, mbar_wait(&pv_done[(it - 1) % NB3], ((it - 1) / NB3) & 1))) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if constexpr (C::kOq == 32) {
+                    uint32_t r[32];
+                    tmem_ld32(o_addr, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                    tmem_st32(o_addr, r);
+                } else {
+                    uint32_t r[16];
+                    tmem_ld16(o_addr, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                    tmem_st16(o_addr, r);
+                }
+            }
+            // ---- exponentials
+            const int kind = work.kind(it);
+            int lo, hi;
+            bounds(kind, lo, hi);
+            const float *cw = cw_w + (it & 1) * 32;
+            const uint32_t sa = s_base + 128 * buf;
+            float ls;
+            if (kind == kFar) ls = t3_exp_pass<2>(sa, cw, lo, hi, p.scale_log2, -m_safe);
+            else if (kind == kFull) ls = t3_exp_pass<0>(sa, cw, lo, hi, p.scale_log2, -m_safe);
+            else ls = t3_exp_pass<1>(sa, cw, lo, hi, p.scale_log2, -m_safe);
+            l_part = l_part * alpha + ls;
+            row_m = m_use;
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[buf]);
+        }
+        // ---- epilogue: O / l once the last product has finished
+        if (ok && !__all_sync(kAll, mbar_wait(&pv_done[(n - 1) % NB3], ((n - 1) / NB3) & 1))) ok = false;
+        tc_fence_after();
+        s_l[row][cq] = l_part;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&lbar[lq]);
+        if (ok && !__all_sync(kAll, mbar_wait(&lbar[lq], 0))) ok = false;
+        if (!ok) s_err = 1;
+        if (ok) {
+            const float4 l4 = *reinterpret_cast<const float4 *>(&s_l[row][0]);
+            const float den = (l4.x + l4.y) + (l4.z + l4.w);
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+            const int64_t grow = static_cast<int64_t>(m) * kBlock + row;
+            __nv_bfloat16 *o = p.out + b * p.o_sb + hq * p.o_sh + grow * p.o_sl + cq * C::kOq;
+            uint32_t r[C::kOq];
+            if constexpr (C::kOq == 32) tmem_ld32(o_addr, r);
+            else tmem_ld16(o_addr, r);
+            tc_wait_ld();
+            if (grow < p.L) {
+#pragma unroll
+                for (int j = 0; j < C::kOq / 8; ++j) {
+                    uint4 w;
+                    w.x = pack_bf16(__uint_as_float(r[8 * j]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
+                    w.y = pack_bf16(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
+                    w.z = pack_bf16(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
+                    w.w = pack_bf16(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(o + 8 * j) = w;
+                }
+                if (cq == 0 && p.lse2) p.lse2[static_cast<int64_t>(bh) * p.L + grow] = row_m + log2f(den);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (s_err && tid == 0) {
+        if (p.status) atomicExch(p.status, 1);
+        // a bounded wait expired: give tile loads still in flight time to land before leaving
+#pragma unroll 1
+        for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
+    }
+    __syncthreads();
+    if (warp == kT3WarpTma) {
+        __syncwarp();
+        tmem_dealloc(tmem, C::kCols);
+    }
+}
+
+template <int D>
+static int launch_tc3(const VqPrefillArgs *a, cudaStream_t stream)
+{
+    using C = T3Cfg<D>;
+    TcMaps m;
+    TcParams p;
+    const int st = tc_setup<D>(a, m, p);
+    if (st != VQ_OK) return st;
+    auto kern = prefill_tc3_kernel<D>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
+    dim3 grid(static_cast<unsigned>(p.ntiles), static_cast<unsigned>(a->q1.shape[0] * a->q1.shape[1]));
+    kern<<<grid, kT3Threads, C::kTotal, stream>>>(m.q1, m.q2, m.k1, m.k3, m.v, m.cb, m.vs, p);
+    return launch_status();
+}
+
+int launch_prefill_tensor3(const VqPrefillArgs *a, cudaStream_t stream)
+{
+    const int D = static_cast<int>(a->q1.shape[3]);
+    // 16-byte aligned rows for the output stores and the tensor maps
+    if (a->out.stride[2] % 8 || a->out.stride[1] % 8 || a->out.stride[0] % 8) return VQ_EINVAL_STRIDE;
+    return D == 64 ? launch_tc3<64>(a, stream) : launch_tc3<128>(a, stream);
+}
+
+}  // namespace vq

@@ -29,7 +29,7 @@ def vq_attn_forward(q1, q2, k1, k_vq, k_vq_cnt, k3, v, v_vq, vi, window_size, so
     cnt = vsum = cb = None
     if nb > 0:
         assert vi.shape[2] >= nb and k_vq_cnt.shape[2] >= nb
-        vsum = api.gather_aggregates(v_vq.to(q1.dtype), vi, nb)
         cnt = k_vq_cnt[:, :, :nb].float().contiguous()
+        vsum = api.gather_aggregates(v_vq.to(q1.dtype), vi, nb, cnt)
         cb = k_vq.to(q1.dtype).contiguous()
     return api.prefill_from_aggregates(q1, q2, k1, k3, v, cb, cnt, vsum, window_size, softmax_scale)

@@ -18,7 +18,7 @@ MAX_DIMS = 5
 BLOCK = 128
 
 VQ_F32, VQ_BF16, VQ_U8, VQ_U16, VQ_I32, VQ_I64 = range(6)
-IMPL_AUTO, IMPL_SIMT, IMPL_TENSOR, IMPL_TENSOR_SERIAL = 0, 1, 2, 3
+IMPL_AUTO, IMPL_SIMT, IMPL_TENSOR, IMPL_TENSOR_SERIAL, IMPL_TENSOR_TWOSTREAM = 0, 1, 2, 3, 4
 
 _DTYPES = {
     torch.float32: VQ_F32,
@@ -88,7 +88,7 @@ def _load() -> ctypes.CDLL:
                                            ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
     lib.vqattn_build_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc),
                                             P(VqTensorDesc), ctypes.c_void_p]
-    lib.vqattn_gather_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
+    lib.vqattn_gather_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
     lib.vqattn_prefill.argtypes = [P(VqPrefillArgs), ctypes.c_void_p]
     lib.vqattn_decode_workspace_bytes.restype = ctypes.c_size_t
     lib.vqattn_decode_workspace_bytes.argtypes = [ctypes.c_int64] * 4
