@@ -27,32 +27,29 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One poll: the hardware may suspend the thread for up to kWaitHintNs while the phase is incomplete
+// (it resumes as soon as the phase completes), so a waiting warp does not burn issue slots.
+constexpr uint32_t kWaitHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     return ok != 0;
 }
-#ifndef VQ_SPIN_FREE
-#define VQ_SPIN_FREE 4096
-#endif
-#ifndef VQ_SPIN_NS
-#define VQ_SPIN_NS 128
-#endif
-// Bounded wait: ~2^21 polls with back-off (a fraction of a second), then failure.
+// Bounded wait: polls for about two seconds of SM clock, then reports failure.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
-    for (uint32_t it = 0; it < (1u << 21); ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (it > VQ_SPIN_FREE) __nanosleep(VQ_SPIN_NS);
-    }
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > 4000000000LL) return false;
+    return true;
 }
 
 // ---------------------------------------------------------------- TMA tile loads
