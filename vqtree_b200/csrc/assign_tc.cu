@@ -30,7 +30,7 @@ namespace vq {
 
 using namespace ptx;
 
-constexpr int kAtChunk = 128;      // codewords per MMA chunk (one N = 128 instruction)
+constexpr int kAtMinChunk = 128;   // codewords per MMA chunk: 128, or 256 (one N = 256 instruction) when K allows
 constexpr int kAtMaxM = 8;
 constexpr int kAtMaxK = 512;
 constexpr float kAtEps = 1.220703125e-4f;  // 2^-13
@@ -84,16 +84,17 @@ struct AtParams {
     int32_t *status;
 };
 
-template <int D, int NS>
+template <int D, int NS, int CH>
 struct AtCfg {
     static constexpr int NH = D / 64;
     static constexpr int kATile = NH * kHalfBytes;     // 128 keys x D bf16 (one term of the residual)
-    static constexpr int kUnit = kHalfBytes;           // 128 codewords x 64 columns of one term: one ring slot
-    static constexpr int kSlots = 6;
+    static constexpr int kUnit = CH * 64 * 2;          // CH codewords x 64 columns of one term: one ring slot
+    static constexpr int kSlots = 96 * 1024 / kUnit;   // 96 KB of ring
     static constexpr int kB = NS * 2 * kATile;         // per stream: Rh then Rl
     static constexpr int kTotal = kB + kSlots * kUnit + 1024;
     static constexpr int kRegion = NS == 2 ? 256 : 512;  // score columns of a stream in tensor memory
-    static constexpr int kMaxChunks = kRegion / kAtChunk;
+    static constexpr int kMaxChunks = kRegion / CH;
+    static constexpr int kGroupsPerChunk = CH / 32;
     static constexpr int kMaxGroups = kRegion / 32;
     static constexpr int kWarpMma = 4 * NS, kWarpTma = 4 * NS + 1;
     static constexpr int kThreads = (4 * NS + 2) * 32;
@@ -140,12 +141,12 @@ __device__ __forceinline__ void load_scores(uint32_t taddr, const float *bm, int
     }
 }
 
-template <int D, int NS>
-__global__ void __launch_bounds__(AtCfg<D, NS>::kThreads, 1)
+template <int D, int NS, int CH>
+__global__ void __launch_bounds__(AtCfg<D, NS, CH>::kThreads, 1)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_hi,
                  const __grid_constant__ CUtensorMap tm_lo, AtParams p)
 {
-    using C = AtCfg<D, NS>;
+    using C = AtCfg<D, NS, CH>;
     constexpr int NH = C::NH, SL = C::kSlots;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -157,7 +158,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int u = blockIdx.y, b = u / p.Hkv, h = u % p.Hkv;
     const int M = p.M, K = p.K, MK = M * K;
-    const int chunks = K / kAtChunk;
+    const int chunks = K / CH;
     const int tile0 = static_cast<int>(blockIdx.x) * NS;
     const int n_act = min(NS, p.ntiles - tile0);       // streams with a tile
     const int upj = chunks * 2 * NH;                   // ring units per (stream, codebook) job
@@ -208,7 +209,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 const int job = g / upj, t = g % upj;
                 const int m = job / n_act;
                 const int ch = t / (2 * NH), rem = t % (2 * NH), is_lo = rem / NH, hh = rem % NH;
-                const int row = h * MK + m * K + ch * kAtChunk;  // row in [Hkv*M*K, D]
+                const int row = h * MK + m * K + ch * CH;  // row in [Hkv*M*K, D]
                 mbar_expect_tx(&b_full[slot], C::kUnit);
                 tma_load_3d(smem + C::kB + slot * C::kUnit, is_lo ? &tm_lo : &tm_hi, &b_full[slot], 64 * hh, row, 0);
             }
@@ -217,7 +218,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     } else if (warp == C::kWarpMma) {
         // ============================================================ MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = idesc_bf16(128, kAtChunk, 0, 0, 0);
+            constexpr uint32_t idesc = idesc_bf16(128, CH, 0, 0, 0);
             // descriptors differ only in their 16-byte-granular start address: build the bases once
             const uint64_t d_a0 = smem_desc_sw128(smem_u32(smem), 16, 1024);
             const uint64_t d_b0 = smem_desc_sw128(smem_u32(smem + C::kB), 16, 1024);
@@ -243,7 +244,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 const uint64_t d_b = d_b0 + static_cast<uint64_t>((slot * C::kUnit) >> 4);
                 const uint64_t d_rh = d_a0 + static_cast<uint64_t>((s * 2 * C::kATile + hh * kHalfBytes) >> 4);
                 const uint64_t d_rl = d_rh + static_cast<uint64_t>(C::kATile >> 4);
-                const uint32_t dcol = tmem + s * C::kRegion + ch * kAtChunk;
+                const uint32_t dcol = tmem + s * C::kRegion + ch * CH;
                 uint32_t acc = rem == 0 ? 0u : 1u;
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
@@ -308,8 +309,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             uint32_t gbits = 0;
 #pragma unroll 1
             for (int g = 0; g < groups && ok; ++g) {
-                if ((g & 3) == 0) {
-                    ok = __all_sync(kAll, mbar_wait(&bar_c[s][g >> 2], m & 1));
+                if (g % C::kGroupsPerChunk == 0) {
+                    ok = __all_sync(kAll, mbar_wait(&bar_c[s][g / C::kGroupsPerChunk], m & 1));
                     tc_fence_after();
                     if (!ok) break;
                 }
@@ -493,11 +494,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
 }
 
-template <int D, int NS>
+template <int D, int NS, int CH>
 static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const VqTensorDesc *bias, VqTensorDesc *codes,
                             void *workspace, int32_t *status, cudaStream_t stream)
 {
-    using C = AtCfg<D, NS>;
+    using C = AtCfg<D, NS, CH>;
     const int64_t B = k->shape[0], Hkv = k->shape[1], L = k->shape[2];
     const int64_t M = cb->shape[1], K = cb->shape[2], MK = M * K;
     __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(workspace);
@@ -509,7 +510,7 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     CUtensorMap mk, mhi, mlo;
     const uint64_t cd[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(Hkv * MK), 1};
     const uint64_t cs[3] = {1, static_cast<uint64_t>(D), static_cast<uint64_t>(Hkv * MK * D)};
-    if (!map_bhld(&mk, *k) || !make_map(&mhi, hi, 3, cd, cs) || !make_map(&mlo, lo, 3, cd, cs)) return VQ_ELAUNCH;
+    if (!map_bhld(&mk, *k) || !make_map(&mhi, hi, 3, cd, cs, CH) || !make_map(&mlo, lo, 3, cd, cs, CH)) return VQ_ELAUNCH;
     AtParams p{};
     p.k = static_cast<const __nv_bfloat16 *>(k->ptr);
     p.k_sb = k->stride[0]; p.k_sh = k->stride[1]; p.k_sl = k->stride[2];
@@ -522,7 +523,7 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     p.L = L;
     p.ntiles = static_cast<int>((L + kBlock - 1) / kBlock);
     p.status = status;
-    auto kern = assign_tc_kernel<D, NS>;
+    auto kern = assign_tc_kernel<D, NS, CH>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
     dim3 grid(static_cast<unsigned>((p.ntiles + NS - 1) / NS), static_cast<unsigned>(B * Hkv));
     kern<<<grid, C::kThreads, C::kTotal, stream>>>(mk, mhi, mlo, p);
@@ -550,7 +551,7 @@ extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc 
     const bool shapes_ok = k->ndim == 4 && codebooks->ndim == 4;
     const int64_t D = shapes_ok ? k->shape[3] : 0, M = shapes_ok ? codebooks->shape[1] : 0, K = shapes_ok ? codebooks->shape[2] : 0;
     const bool tensor_path = shapes_ok && k->dtype == VQ_BF16 && (D == 64 || D == 128) && M >= 1 && M <= kAtMaxM &&
-                             K % kAtChunk == 0 && K <= kAtMaxK && k->stride[0] % 8 == 0 && k->stride[1] % 8 == 0 &&
+                             K % kAtMinChunk == 0 && K <= kAtMaxK && k->stride[0] % 8 == 0 && k->stride[1] % 8 == 0 &&
                              k->stride[2] % 8 == 0 && k->shape[2] < (int64_t(1) << 31);
     if (!tensor_path) return vqattn_assign_codes(k, codebooks, bias, codes, stream);
     // same argument checks as the exact kernel's entry point
@@ -574,10 +575,17 @@ extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc 
         workspace_bytes < vqattn_assign_workspace_bytes(B, Hkv, L, M, K, D))
         return VQ_EWORKSPACE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // two key tiles per CTA share the 512 score columns of tensor memory when a codebook fits 256 of them
-    if (K <= 256)
-        return D == 64 ? launch_assign_tc<64, 2>(k, codebooks, bias, codes, workspace, status_word, s)
-                       : launch_assign_tc<128, 2>(k, codebooks, bias, codes, workspace, status_word, s);
-    return D == 64 ? launch_assign_tc<64, 1>(k, codebooks, bias, codes, workspace, status_word, s)
-                   : launch_assign_tc<128, 1>(k, codebooks, bias, codes, workspace, status_word, s);
+    // two key tiles per CTA share the 512 score columns of tensor memory when a codebook fits 256 of them;
+    // N = 256 instructions when K is a multiple of 256
+    if (K == 128)
+        return D == 64 ? launch_assign_tc<64, 2, 128>(k, codebooks, bias, codes, workspace, status_word, s)
+                       : launch_assign_tc<128, 2, 128>(k, codebooks, bias, codes, workspace, status_word, s);
+    if (K == 256)
+        return D == 64 ? launch_assign_tc<64, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s)
+                       : launch_assign_tc<128, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s);
+    if (K == 512)
+        return D == 64 ? launch_assign_tc<64, 1, 256>(k, codebooks, bias, codes, workspace, status_word, s)
+                       : launch_assign_tc<128, 1, 256>(k, codebooks, bias, codes, workspace, status_word, s);
+    return D == 64 ? launch_assign_tc<64, 1, 128>(k, codebooks, bias, codes, workspace, status_word, s)   // K = 384
+                   : launch_assign_tc<128, 1, 128>(k, codebooks, bias, codes, workspace, status_word, s);
 }
