@@ -69,98 +69,109 @@ build_aggregates_reg_kernel(const void *__restrict__ codes, int code_dtype, int6
     auto add_row = [&](int r, const uint2 raw) {
         float x[CPL];
         unpack(raw, x);
-#pragma unroll
-        for (int rr = 0; rr < kArRows; ++rr)
-            if (r == rr) {
-#pragma unroll
-                for (int c = 0; c < CPL; ++c) acc[rr][c] = __fadd_rn(acc[rr][c], x[c]);
-            }
-        if (lane == r) my_cnt += 1.f;
-    };
-    // this warp's keys in a block with codes c[]: bit k of (lo, hi) set when key k's code is one of its rows
-    auto my_keys = [&](const int (&c)[4], uint64_t &lo, uint64_t &hi) {
-        uint32_t w[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) w[t] = __ballot_sync(kAll, static_cast<unsigned>(c[t] - row0) < static_cast<unsigned>(kArRows));
-        lo = w[0] | (static_cast<uint64_t>(w[1]) << 32);
-        hi = w[2] | (static_cast<uint64_t>(w[3]) << 32);
-    };
-    auto pop = [&](uint64_t &lo, uint64_t &hi) {  // lowest key of a non-empty mask
-        int key;
-        if (lo != 0) {
-            key = __ffsll(static_cast<long long>(lo)) - 1;
-            lo &= lo - 1;
-        } else {
-            key = 64 + __ffsll(static_cast<long long>(hi)) - 1;
-            hi &= hi - 1;
+        // r is the same in all lanes: one taken branch instead of eight predicated copies of the adds
+#define VQ_AR_ADD(rr)                                                                  \
+    case rr:                                                                           \
+        _Pragma("unroll") for (int c = 0; c < CPL; ++c) acc[rr][c] = __fadd_rn(acc[rr][c], x[c]); \
+        break;
+        switch (r) {
+            VQ_AR_ADD(0) VQ_AR_ADD(1) VQ_AR_ADD(2) VQ_AR_ADD(3) VQ_AR_ADD(4) VQ_AR_ADD(5) VQ_AR_ADD(6) VQ_AR_ADD(7)
+        default: break;
         }
-        return key;
+#undef VQ_AR_ADD
+        if (lane == r) my_cnt += 1.f;
     };
     // Value rows travel through a per-warp staging area in shared memory: the rows of a block's first
     // kArSlots keys are copied there asynchronously one block ahead (cp.async holds no register; every
-    // lane copies and later reads only its own CPL columns, so no synchronisation is needed).
+    // lane copies and later reads only its own CPL columns), together with the code row of each.
     __shared__ __align__(16) uint8_t s_stage[kArWarps][2][kArSlots][D * 2];
+    __shared__ int s_row[kArWarps][2][kArSlots];
     uint8_t *stage = &s_stage[threadIdx.x >> 5][0][0][0] + CPL * 2 * lane;
-    auto stage_rows = [&](int n, int buf, uint64_t lo, uint64_t hi) {
-#pragma unroll 1
-        for (int slot = 0; slot < kArSlots && (lo | hi) != 0; ++slot) {
-            const int key = pop(lo, hi);
-            const __nv_bfloat16 *src = vbase + (static_cast<int64_t>(n) * kBlock + key) * v_sl;
-            const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(stage + (buf * kArSlots + slot) * (D * 2)));
-            if constexpr (CPL == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-            else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+    int *rows = &s_row[threadIdx.x >> 5][0][0];
+    auto copy_row = [&](const __nv_bfloat16 *src, int buf, int slot) {
+        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(stage + (buf * kArSlots + slot) * (D * 2)));
+        if constexpr (CPL == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+        else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+    };
+    // Stage the keys of block n whose codes (c) fall into this warp's rows; returns how many were staged,
+    // rest[] keeps the keys beyond the slots (bit k of rest[t]: key 32 t + k).
+    auto stage_block = [&](int n, const int (&c)[4], int buf, uint32_t (&rest)[4]) {
+        const __nv_bfloat16 *vb = vbase + static_cast<int64_t>(n) * kBlock * v_sl;
+        int slot = 0;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int lc = c[t] - row0;
+            uint32_t w = __ballot_sync(kAll, static_cast<unsigned>(lc) < static_cast<unsigned>(kArRows));
+            while (w != 0 && slot < kArSlots) {
+                const int bit = __ffs(w) - 1;
+                w &= w - 1;
+                const int r = __shfl_sync(kAll, lc, bit);
+                copy_row(vb + static_cast<int64_t>(32 * t + bit) * v_sl, buf, slot);
+                if (lane == 0) rows[buf * kArSlots + slot] = r;
+                ++slot;
+            }
+            rest[t] = w;
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        return slot;
+    };
+    auto read_row = [&](int buf, int slot) {
+        const uint8_t *sp = stage + (buf * kArSlots + slot) * (D * 2);
+        uint2 raw = make_uint2(0u, 0u);
+        if constexpr (CPL == 4) raw = *reinterpret_cast<const uint2 *>(sp);
+        else raw.x = *reinterpret_cast<const uint32_t *>(sp);
+        return raw;
     };
 
     // Software pipeline over the blocks: codes are loaded two blocks ahead, value rows one block ahead.
     int c_nxt[4] = {0, 0, 0, 0}, c_nn[4] = {0, 0, 0, 0};
-    uint64_t lo = 0, hi = 0;       // keys of the current block
-    uint32_t p01 = 0, p23 = 0;     // its codes, 16 bits each: key k in lane k & 31, field k >> 5
+    uint32_t rest[4] = {0, 0, 0, 0};  // keys of the current block beyond the staged ones
+    int staged = 0;                    // staged keys of the current block
     if (NB > 0) {
         int c0[4];
         load_codes(0, c0);
         if (NB > 1) load_codes(1, c_nxt);
-        my_keys(c0, lo, hi);
-        stage_rows(0, 0, lo, hi);
-        p01 = (c0[0] & 0xffff) | (c0[1] << 16);
-        p23 = (c0[2] & 0xffff) | (c0[3] << 16);
+        staged = stage_block(0, c0, 0, rest);
     }
     for (int n = 0; n < NB; ++n) {
         const int buf = n & 1;
         if (n + 2 < NB) load_codes(n + 2, c_nn);
-        uint64_t nlo = 0, nhi = 0;
-        if (n + 1 < NB) my_keys(c_nxt, nlo, nhi);
-        stage_rows(n + 1, buf ^ 1, nlo, nhi);
+        uint32_t rest_n[4] = {0, 0, 0, 0};
+        int staged_n = 0;
+        if (n + 1 < NB) staged_n = stage_block(n + 1, c_nxt, buf ^ 1, rest_n);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");  // this block's rows have landed
+        __syncwarp();                                          // ... and lane 0's row numbers are visible
         // ---- this block's keys, in position order
-        int slot = 0;
-        while ((lo | hi) != 0) {
-            if (slot == kArSlots) {
-                // More keys than staging slots (skewed codes): every lane has read its columns of the
-                // slots, so the next keys of this block are staged into them and waited for at once.
-                uint64_t tlo = lo, thi = hi;
 #pragma unroll 1
-                for (int s2 = 0; s2 < kArSlots && (tlo | thi) != 0; ++s2) {
-                    const int key = pop(tlo, thi);
-                    const __nv_bfloat16 *src = vbase + (static_cast<int64_t>(n) * kBlock + key) * v_sl;
-                    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(stage + (buf * kArSlots + s2) * (D * 2)));
-                    if constexpr (CPL == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-                    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+        for (int slot = 0; slot < staged; ++slot) add_row(rows[buf * kArSlots + slot], read_row(buf, slot));
+        if ((rest[0] | rest[1] | rest[2] | rest[3]) != 0) {
+            // More keys than staging slots (skewed codes): staged into the same slots in chunks and waited
+            // for at once; their code rows are read again from global memory.
+            const __nv_bfloat16 *vb = vbase + static_cast<int64_t>(n) * kBlock * v_sl;
+#pragma unroll 1
+            for (int t = 0; t < 4; ++t) {
+                uint32_t w = rest[t];
+                while (w != 0) {
+                    __syncwarp();
+                    int cnt = 0;
+                    uint32_t w2 = w;
+                    while (w2 != 0 && cnt < kArSlots) {
+                        const int bit = __ffs(w2) - 1;
+                        w2 &= w2 - 1;
+                        copy_row(vb + static_cast<int64_t>(32 * t + bit) * v_sl, buf, cnt);
+                        ++cnt;
+                    }
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    for (int i = 0; i < cnt; ++i) {
+                        const int bit = __ffs(w) - 1;
+                        w &= w - 1;
+                        const int64_t j = static_cast<int64_t>(n) * kBlock + 32 * t + bit;
+                        add_row(load_code(codes, code_dtype, cbase + j * c_sl) - row0, read_row(buf, i));
+                    }
                 }
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                slot = 0;
             }
-            const int key = pop(lo, hi);
-            const uint32_t c01 = __shfl_sync(kAll, p01, key & 31), c23 = __shfl_sync(kAll, p23, key & 31);
-            const int r = static_cast<int>(((key & 64 ? c23 : c01) >> (key & 32 ? 16 : 0)) & 0xffffu) - row0;
-            const uint8_t *sp = stage + (buf * kArSlots + slot) * (D * 2);
-            uint2 raw = make_uint2(0u, 0u);
-            if constexpr (CPL == 4) raw = *reinterpret_cast<const uint2 *>(sp);
-            else raw.x = *reinterpret_cast<const uint32_t *>(sp);
-            add_row(r, raw);
-            ++slot;
         }
         // ---- snapshot of the eight rows
         const int64_t out_row0 = (static_cast<int64_t>(u) * NB + n) * MK + base;
@@ -174,12 +185,12 @@ build_aggregates_reg_kernel(const void *__restrict__ codes, int code_dtype, int6
         }
         if (lane < kArRows) __stcs(cnt + out_row0 + lane, my_cnt);
         // ---- rotate the pipeline
-        lo = nlo;
-        hi = nhi;
-        p01 = (c_nxt[0] & 0xffff) | (c_nxt[1] << 16);
-        p23 = (c_nxt[2] & 0xffff) | (c_nxt[3] << 16);
+        staged = staged_n;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) c_nxt[t] = c_nn[t];
+        for (int t = 0; t < 4; ++t) {
+            rest[t] = rest_n[t];
+            c_nxt[t] = c_nn[t];
+        }
     }
 }
 
