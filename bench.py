@@ -48,10 +48,10 @@ def contraction_flops(B, Hq, L, D, W, M, K, **_):
     return 4.0 * D * B * Hq * (local + far)
 
 
-def decode_bytes(B, Hq, Hkv, D, W, M, K, **_):
-    """HBM bytes one decode step must move (bf16 window K/V, bf16 value sums, f32 counts, q/out, f32 codebooks)."""
+def decode_bytes(B, Hq, Hkv, D, W, M, K, cb_bytes=4, **_):
+    """HBM bytes one decode step must move (bf16 window K/V, bf16 value sums, f32 counts, q/out, codebooks once per head)."""
     per_unit = 2 * W * D * 2 + M * K * D * 2 + M * K * 4 + (Hq // Hkv) * D * 2 * 2
-    return B * Hkv * per_unit + Hkv * M * K * D * 4
+    return B * Hkv * per_unit + Hkv * M * K * D * cb_bytes
 
 
 def attention_bytes(w):
@@ -180,6 +180,8 @@ def main():
     ap.add_argument("--attn-impl", default="auto", choices=["auto", "simt", "tensor"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--decode-codebook", default="bf16", choices=["bf16", "f32"],
+                    help="dtype of the codebook the decode kernel scores with (bf16: the copy the prefill uses too)")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -338,6 +340,8 @@ def main():
                              v=rn(d["B"], d["Hkv"], d["W"], d["D"]).bfloat16(), cnt=cntd, vsum=vsumd))
             del codes
         cbd = rn(d["Hkv"], MK, d["D"]) * d["D"] ** -0.25
+        if args.decode_codebook == "bf16":
+            cbd = cbd.bfloat16()  # the activation-dtype copy the prefill scores with too
         ws = api.decode_workspace(d["B"], d["Hq"], d["Hkv"], d["D"], dev)
         outd = torch.empty(d["B"], d["Hq"], d["D"], dtype=torch.bfloat16, device=dev)
         run = lambda bf: api.vq_attention_decode(bf["q"], bf["q"], bf["k"], bf["k"], bf["v"], cbd, bf["cnt"], bf["vsum"],
@@ -357,10 +361,10 @@ def main():
             t = torch.tensor([us], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             us = float(t.item())
-        by = decode_bytes(**d)
+        by = decode_bytes(**d, cb_bytes=2 if args.decode_codebook == "bf16" else 4)
         decode = dict(tok_s=world * d["B"] / (us * 1e-6), us_per_step=us, bytes_per_step=by, achieved_gbs=by / (us * 1e-6) / 1e9,
                       frac_hbm=by / (us * 1e-6) / 1e9 / peaks["hbm"], peak_gbs=peaks["hbm"], peak_source=peaks["source"],
-                      config=f"B{d['B']} H{d['Hq']} D{d['D']} ctx{d['ctx']} W{d['W']} M{d['M']}xK{d['K']} bf16, f32 codebooks")
+                      config=f"B{d['B']} H{d['Hq']} D{d['D']} ctx{d['ctx']} W{d['W']} M{d['M']}xK{d['K']} bf16, {args.decode_codebook} codebooks")
         del bufs
 
     if rank != 0:

@@ -200,6 +200,9 @@ def test_prefill_lse_and_local_only(api, golden_dir):
     (2, 8, 2, 128, 2, 128, 128, torch.bfloat16, False),   # GQA group of 4
     (1, 6, 2, 64, 1, 128, 128, torch.float32, True),      # group of 3 -> one head per CTA
     (3, 2, 1, 64, 2, 256, 128, torch.bfloat16, True),
+    (2, 4, 4, 128, 2, 128, 256, torch.bfloat16, False),   # tensor-core decode kernel, one query head per kv head
+    (1, 16, 2, 128, 1, 256, 256, torch.bfloat16, False),  # tensor-core decode kernel, group of 8
+    (1, 3, 1, 128, 3, 128, 128, torch.bfloat16, False),   # tensor-core decode kernel, group of 3
 ])
 def test_decode_matches_oracle_and_prefill_row(api, B, Hq, Hkv, D, M, K, W, dtype, cb_f32):
     L = 1024

@@ -19,6 +19,10 @@
 
 namespace vq {
 
+// decode_tc.cu: tensor-core kernel (bf16, D = 128, bf16 codebook, dense rows, <= 16 query heads per kv head)
+bool decode_tc_eligible(const VqDecodeArgs *a);
+int launch_decode_tc(const VqDecodeArgs *a, const DecodeParams &p, cudaStream_t s);
+
 int launch_decode_bulk(const DecodeParams &p, int64_t units, int D, int GH, bool cb32, void *workspace, size_t workspace_bytes,
                        int32_t *status, cudaStream_t s);
 size_t decode_bulk_workspace_bytes(int64_t units_times_groups, int64_t heads_per_group, int64_t D);
@@ -301,6 +305,10 @@ extern "C" int vqattn_decode(const VqDecodeArgs *a, void *stream)
     const bool dense_rows = a->k1_win.stride[2] == D && a->k3_win.stride[2] == D && a->v_win.stride[2] == D &&
                             a->q1.stride[1] == D && a->q2.stride[1] == D && a->q1.stride[0] % 8 == 0 && a->q2.stride[0] % 8 == 0 &&
                             reinterpret_cast<uintptr_t>(a->q1.ptr) % 16 == 0 && reinterpret_cast<uintptr_t>(a->q2.ptr) % 16 == 0;
+    if (dt == VQ_BF16 && dense_rows && decode_tc_eligible(a)) {
+        const int r = launch_decode_tc(a, p, s);
+        if (r != VQ_EWORKSPACE) return r;  // too small a workspace for it: the SIMT kernel below
+    }
     if (dt == VQ_BF16 && dense_rows)
         return launch_decode_bulk(p, B * Hkv, static_cast<int>(D), GH, far && cb32, a->workspace, a->workspace_bytes,
                                   a->status_word, s);
