@@ -99,6 +99,8 @@ __global__ void __launch_bounds__(kBulkThreads, VQ_BULK_CTAS_PER_SM) decode_bulk
     const int64_t T = static_cast<int64_t>(bp.units) * TU;
     const int NC = bp.num_ctas, c = blockIdx.x;
     const int64_t g0 = static_cast<int64_t>(c) * T / NC, g1 = static_cast<int64_t>(c + 1) * T / NC;
+    // (unit, tile) of the first tile; the loops step them (a 64-bit division per tile would cost more than the tile's arithmetic)
+    const int ue_first = static_cast<int>(g0 / TU), tt_first = static_cast<int>(g0 % TU);
 
     if (tid == 0) {
         for (int s = 0; s < kBulkStages; ++s) {
@@ -114,13 +116,17 @@ __global__ void __launch_bounds__(kBulkThreads, VQ_BULK_CTAS_PER_SM) decode_bulk
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             bool ok = true;
+            int ue = ue_first, tt = tt_first - 1;
             for (int64_t g = g0; g < g1; ++g) {
                 const int t = static_cast<int>(g - g0), sidx = t % kBulkStages;
+                if (++tt == TU) {
+                    tt = 0;
+                    ++ue;
+                }
                 if (t >= kBulkStages && !mbar_wait(&empty[sidx], ((t / kBulkStages) - 1) & 1)) {
                     ok = false;
                     break;
                 }
-                const int ue = static_cast<int>(g / TU), tt = static_cast<int>(g % TU);
                 const int u = ue / HG, hg = ue % HG;
                 const int b = u / p.Hkv, hk = u % p.Hkv;
                 uint8_t *dst = ring + sidx * ST::kBytes;
@@ -188,6 +194,29 @@ __global__ void __launch_bounds__(kBulkThreads, VQ_BULK_CTAS_PER_SM) decode_bulk
             consumer_barrier();
             const int first_c = owner_of(static_cast<int64_t>(ue) * TU, T, NC);
             const int last_c = owner_of(static_cast<int64_t>(ue + 1) * TU - 1, T, NC);
+            if (first_c == last_c) {
+                // the whole unit was processed by this CTA: merge the warps and write the output row directly
+                const int u = ue / HG, hg = ue % HG;
+                const int b = u / p.Hkv, hk = u % p.Hkv;
+                const int hq0 = hk * p.G + hg * GH;
+                for (int i = tid; i < GH * D; i += kDecThreads) {
+                    const int g = i / D, d = i % D;
+                    float M = -INFINITY;
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) M = fmaxf(M, s_red[(w * GH + g) * (D + 2) + D]);
+                    float num = 0.f, den = 0.f;
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) {
+                        const float mw = s_red[(w * GH + g) * (D + 2) + D];
+                        const float a = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+                        num += a * s_red[(w * GH + g) * (D + 2) + d];
+                        den += a * s_red[(w * GH + g) * (D + 2) + D + 1];
+                    }
+                    static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hq0 + g) * p.o_sh + d] = __float2bfloat16_rn(num / den);
+                }
+                consumer_barrier();  // s_red is reused by the next segment
+                return;
+            }
             float *part = bp.partial + static_cast<int64_t>(c + ue) * GH * (D + 2);
             for (int i = tid; i < GH * (D + 1); i += kDecThreads) {
                 const int g = i / (D + 1), d = i % (D + 1);
@@ -239,9 +268,13 @@ __global__ void __launch_bounds__(kBulkThreads, VQ_BULK_CTAS_PER_SM) decode_bulk
             consumer_barrier();  // s_red and s_last are reused by the next segment
         };
 
+        int ue = ue_first, tt = tt_first - 1;
         for (int64_t g = g0; g < g1; ++g) {
             const int t = static_cast<int>(g - g0), sidx = t % kBulkStages;
-            const int ue = static_cast<int>(g / TU), tt = static_cast<int>(g % TU);
+            if (++tt == TU) {
+                tt = 0;
+                ++ue;
+            }
             if (ue != cur_ue) {
                 if (cur_ue >= 0) flush(cur_ue);
                 st.init();

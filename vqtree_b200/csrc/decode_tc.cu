@@ -38,7 +38,7 @@ constexpr int kDtOffCnt = kDtOffP + 2 * kDtQBytes;      // 3 x 128 counts
 constexpr int kDtSmem = kDtOffCnt + kDtStages * kDtRows * 4 + 1024;
 constexpr float kDtLazy = 8.f;
 #ifndef VQ_DT_MIN_GROUP
-#define VQ_DT_MIN_GROUP 2
+#define VQ_DT_MIN_GROUP 1
 #endif
 
 struct DtParams {
@@ -118,8 +118,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
     const int NC = bp.num_ctas, c = blockIdx.x;
     const int64_t g0 = static_cast<int64_t>(c) * T / NC, g1 = static_cast<int64_t>(c + 1) * T / NC;
     const int n_items = static_cast<int>(g1 - g0);
+    // (unit, tile) of the first item; the roles step them item by item (no 64-bit divisions in the loops)
+    const int ue0 = static_cast<int>(g0 / TU), tt0 = static_cast<int>(g0 % TU);
 
-    if (tid == 0) {
+    // The producer lane initialises the barriers itself and starts the first tile loads at once; the
+    // other roles see the barriers after the CTA-wide barrier below (TMEM is allocated meanwhile).
+    if (tid == 5 * 32) {
         for (int i = 0; i < NS; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
@@ -135,7 +139,58 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
         fence_mbar_init();
         s_err = 0;
     }
-    if (warp == 5) {
+    float *cnt_s = reinterpret_cast<float *>(smem + kDtOffCnt);
+    // producer state (lane 0 of warp 5): position in the CTA's item list
+    int pr_t = 0, pr_ue = ue0, pr_tt = tt0 - 1, pr_cur = -1, pr_seg = -1;
+    bool pr_ok = true;
+    auto produce = [&](int upto) {  // issue the loads of items [pr_t, upto)
+        for (; pr_t < upto && pr_ok; ++pr_t) {
+            const int t = pr_t, st = t % NS;
+            if (++pr_tt == TU) {
+                pr_tt = 0;
+                ++pr_ue;
+            }
+            const int ue = pr_ue, tt = pr_tt;
+            const int b = ue / p.Hkv, hk = ue % p.Hkv;
+            if (t >= NS && !mbar_wait(&empty[st], ((t / NS) - 1) & 1)) {
+                pr_ok = false;
+                break;
+            }
+            if (ue != pr_cur) {
+                pr_cur = ue;
+                ++pr_seg;
+                const int slot = pr_seg & 1;
+                if (pr_seg >= 2 && !mbar_wait(&q_free[slot], ((pr_seg >> 1) - 1) & 1)) {
+                    pr_ok = false;
+                    break;
+                }
+                uint8_t *qd = smem + kDtOffQ + slot * 2 * kDtQBytes;
+                mbar_expect_tx(&q_full[slot], 2 * kDtQBytes);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    tma_load_3d(qd + h * (kDtN * 128), &tm_q1, &q_full[slot], 64 * h, hk * G, b);
+                    tma_load_3d(qd + kDtQBytes + h * (kDtN * 128), &tm_q2, &q_full[slot], 64 * h, hk * G, b);
+                }
+            }
+            const DtItem it = dt_item(bp, tt);
+            uint8_t *dst = smem + st * kDtStageBytes;
+            mbar_expect_tx(&full[st], kDtStageBytes + (it.kind == 2 ? kDtRows * 4 : 0));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (it.kind == 2) {
+                    tma_load_3d(dst + h * kHalfBytes, &tm_cb, &full[st], 64 * h, it.row0, hk);
+                    tma_load_4d(dst + kDtTile + h * kHalfBytes, &tm_vs, &full[st], 64 * h, it.row0, hk, b);
+                } else {
+                    tma_load_4d(dst + h * kHalfBytes, it.kind == 0 ? &tm_k1 : &tm_k3, &full[st], 64 * h, it.row0, hk, b);
+                    tma_load_4d(dst + kDtTile + h * kHalfBytes, &tm_v, &full[st], 64 * h, it.row0, hk, b);
+                }
+            }
+            if (it.kind == 2)
+                dt_bulk_copy(cnt_s + st * kDtRows, p.cnt + static_cast<int64_t>(ue) * p.MK + it.row0, kDtRows * 4, &full[st]);
+        }
+    };
+    if (tid == 5 * 32) produce(min(n_items, NS));   // the ring is empty: no wait inside
+    if (warp == 4) {
         __syncwarp();
         tmem_alloc(&s_tmem, 64);
         tmem_relinquish();
@@ -144,56 +199,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;  // columns: S^T buffers at 0 and 16, O^T at 32
-    float *cnt_s = reinterpret_cast<float *>(smem + kDtOffCnt);
 
     if (warp == 5) {
-        // ================================================================== producer
+        // ================================================================== producer (the first loads were issued above)
         if (lane == 0) {
-            prefetch_tmap(&tm_k1); prefetch_tmap(&tm_v); prefetch_tmap(&tm_q1);
-            bool ok = true;
-            int cur_ue = -1, seg = -1;
-            for (int t = 0; t < n_items && ok; ++t) {
-                const int64_t g = g0 + t;
-                const int st = t % NS;
-                const int ue = static_cast<int>(g / TU), tt = static_cast<int>(g % TU);
-                const int b = ue / p.Hkv, hk = ue % p.Hkv;
-                if (t >= NS && !mbar_wait(&empty[st], ((t / NS) - 1) & 1)) {
-                    ok = false;
-                    break;
-                }
-                if (ue != cur_ue) {
-                    cur_ue = ue;
-                    ++seg;
-                    const int slot = seg & 1;
-                    if (seg >= 2 && !mbar_wait(&q_free[slot], ((seg >> 1) - 1) & 1)) {
-                        ok = false;
-                        break;
-                    }
-                    uint8_t *qd = smem + kDtOffQ + slot * 2 * kDtQBytes;
-                    mbar_expect_tx(&q_full[slot], 2 * kDtQBytes);
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        tma_load_3d(qd + h * (kDtN * 128), &tm_q1, &q_full[slot], 64 * h, hk * G, b);
-                        tma_load_3d(qd + kDtQBytes + h * (kDtN * 128), &tm_q2, &q_full[slot], 64 * h, hk * G, b);
-                    }
-                }
-                const DtItem it = dt_item(bp, tt);
-                uint8_t *dst = smem + st * kDtStageBytes;
-                mbar_expect_tx(&full[st], kDtStageBytes + (it.kind == 2 ? kDtRows * 4 : 0));
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (it.kind == 2) {
-                        tma_load_3d(dst + h * kHalfBytes, &tm_cb, &full[st], 64 * h, it.row0, hk);
-                        tma_load_4d(dst + kDtTile + h * kHalfBytes, &tm_vs, &full[st], 64 * h, it.row0, hk, b);
-                    } else {
-                        tma_load_4d(dst + h * kHalfBytes, it.kind == 0 ? &tm_k1 : &tm_k3, &full[st], 64 * h, it.row0, hk, b);
-                        tma_load_4d(dst + kDtTile + h * kHalfBytes, &tm_v, &full[st], 64 * h, it.row0, hk, b);
-                    }
-                }
-                if (it.kind == 2)
-                    dt_bulk_copy(cnt_s + st * kDtRows, p.cnt + static_cast<int64_t>(ue) * p.MK + it.row0, kDtRows * 4, &full[st]);
-            }
-            if (!ok) s_err = 1;
+            produce(n_items);
+            if (!pr_ok) s_err = 1;
         }
     } else if (warp == 4) {
         // ================================================================== MMA issuer
@@ -205,14 +216,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             const uint64_t d_q = smem_desc_sw128(smem_u32(smem + kDtOffQ), 16, 1024);
             const uint64_t d_p = smem_desc_sw128(smem_u32(smem + kDtOffP), 16, 1024);
             bool ok = true;
-            int ue1 = -1, seg = -1;          // unit / segment of the last issued score MMA
+            int seg = -1;                    // unit segment of the last issued score MMA
+            int tt_s = tt0 - 1, tt_p = tt0 - 1;  // tile inside its unit of the last score / product item
             auto scores = [&](int t) {
                 if (!ok) return;
-                const int64_t g = g0 + t;
                 const int st = t % NS, sb = t & 1;
-                const int ue = static_cast<int>(g / TU), tt = static_cast<int>(g % TU);
-                if (ue != ue1) {
-                    ue1 = ue;
+                if (++tt_s == TU) tt_s = 0;
+                const int tt = tt_s;
+                if (t == 0 || tt == 0) {         // first item of a unit segment
                     ++seg;
                     if (!mbar_wait(&q_full[seg & 1], (seg >> 1) & 1)) {
                         ok = false;
@@ -235,14 +246,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                                db + static_cast<uint64_t>((h * (kDtN * 128) + k4 * 32) >> 4), idesc_s, (h | k4) ? 1u : 0u);
                 tc_commit(&s_ready[sb]);
                 // the query rows of a unit are free after its last score MMA in this CTA
-                const bool last_of_seg = (t + 1 == n_items) || static_cast<int>((g + 1) / TU) != ue;
+                const bool last_of_seg = (t + 1 == n_items) || tt + 1 == TU;
                 if (last_of_seg) tc_commit(&q_free[seg & 1]);
             };
             auto product = [&](int t) {
                 if (!ok) return;
-                const int64_t g = g0 + t;
                 const int st = t % NS, sb = t & 1;
-                const bool first_of_seg = (t == 0) || static_cast<int>((g - 1) / TU) != static_cast<int>(g / TU);
+                if (++tt_p == TU) tt_p = 0;
+                const bool first_of_seg = (t == 0) || tt_p == 0;
                 if (!mbar_wait(&p_ready[sb], (t >> 1) & 1)) {
                     ok = false;
                     return;
@@ -299,18 +310,32 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             tc_wait_ld();
             // denominators: sum of the 128 threads' partial sums
 #pragma unroll
-            for (int g = 0; g < kDtN; ++g) {
-                float v = l_part[g];
+            for (int g = 0; g < kDtN; ++g)
+                if (g < G) {
+                    float v = l_part[g];
 #pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(kAll, v, off);
-                if (lane == 0) s_wl[warp][g] = v;
-            }
+                    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(kAll, v, off);
+                    if (lane == 0) s_wl[warp][g] = v;
+                }
             if (!sync4()) {
                 ok = false;
                 return;
             }
             const int first_c = static_cast<int>(((static_cast<int64_t>(ue) * TU + 1) * NC - 1) / T);
             const int last_c = static_cast<int>(((static_cast<int64_t>(ue + 1) * TU) * NC - 1) / T);
+            if (first_c == last_c) {
+                // the whole unit was processed by this CTA: normalise and write the output row directly
+                const int b = ue / p.Hkv, hk = ue % p.Hkv;
+#pragma unroll
+                for (int g = 0; g < kDtN; ++g)
+                    if (g < G) {
+                        const float den = (s_wl[0][g] + s_wl[1][g]) + (s_wl[2][g] + s_wl[3][g]);
+                        static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hk * G + g) * p.o_sh + tid] =
+                            __float2bfloat16_rn(__uint_as_float(o[g]) / den);
+                    }
+                if (!sync4()) ok = false;  // s_wl is reused by the next unit
+                return;
+            }
             float *part = bp.partial + static_cast<int64_t>(c + ue) * G * (D + 2);
 #pragma unroll
             for (int g = 0; g < kDtN; ++g)
@@ -356,10 +381,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             if (!sync4()) ok = false;  // s_wl and s_last are reused by the next unit
         };
 
+        int ue = ue0, tt = tt0 - 1;
         for (int t = 0; t < n_items && ok; ++t) {
-            const int64_t g = g0 + t;
             const int st = t % NS, sb = t & 1;
-            const int ue = static_cast<int>(g / TU), tt = static_cast<int>(g % TU);
+            if (++tt == TU) {
+                tt = 0;
+                ++ue;
+            }
             const bool first_of_seg = ue != cur_ue;
             if (first_of_seg) {
                 if (cur_ue >= 0) flush(cur_ue, last_t);
@@ -471,7 +499,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
     }
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 4) {
         __syncwarp();
         tmem_dealloc(tmem, 64);
     }
@@ -487,8 +515,7 @@ static int dt_sm_count()
     return n;
 }
 
-// bf16, D = 128, dense rows, 2 to 16 query heads per kv head (with one head per kv head the SIMT
-// stream is the faster kernel), bf16 codebook, M*K a multiple of 128.
+// bf16, D = 128, dense rows, 1 to 16 query heads per kv head, bf16 codebook, M*K a multiple of 128.
 bool decode_tc_eligible(const VqDecodeArgs *a)
 {
     const bool far = a->use_far != 0;
