@@ -161,7 +161,6 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int chunks = K / CH;
     const int tile0 = static_cast<int>(blockIdx.x) * NS;
     const int n_act = min(NS, p.ntiles - tile0);       // streams with a tile
-    const int upj = chunks * 2 * NH;                   // ring units per (stream, codebook) job
 
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) {
@@ -198,21 +197,23 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             }
             // Units in the order the MMA warp consumes them: jobs (codebook m, stream s) with s fastest;
             // inside a job, per chunk: hi term columns 0-63, 64-127 (D = 128), then the lo term likewise.
-            const int total = n_act * M * upj;
+            // (nested counters instead of divisions of a flat index: this thread's instructions are serial)
             bool ok = true;
-            for (int g = 0; g < total; ++g) {
-                const int slot = g % SL;
-                if (g >= SL && !mbar_wait(&b_free[slot], ((g / SL) - 1) & 1)) {
-                    ok = false;
-                    break;
-                }
-                const int job = g / upj, t = g % upj;
-                const int m = job / n_act;
-                const int ch = t / (2 * NH), rem = t % (2 * NH), is_lo = rem / NH, hh = rem % NH;
-                const int row = h * MK + m * K + ch * CH;  // row in [Hkv*M*K, D]
-                mbar_expect_tx(&b_full[slot], C::kUnit);
-                tma_load_3d(smem + C::kB + slot * C::kUnit, is_lo ? &tm_lo : &tm_hi, &b_full[slot], 64 * hh, row, 0);
-            }
+            int g = 0;
+            for (int m = 0; m < M && ok; ++m)
+                for (int s = 0; s < n_act && ok; ++s)
+                    for (int ch = 0; ch < chunks && ok; ++ch)
+#pragma unroll
+                        for (int rem = 0; rem < 2 * NH; ++rem, ++g) {
+                            const int slot = g % SL, is_lo = rem / NH, hh = rem % NH;
+                            if (g >= SL && !mbar_wait(&b_free[slot], ((g / SL) - 1) & 1)) {
+                                ok = false;
+                                break;
+                            }
+                            const int row = h * MK + m * K + ch * CH;  // row in [Hkv*M*K, D]
+                            mbar_expect_tx(&b_full[slot], C::kUnit);
+                            tma_load_3d(smem + C::kB + slot * C::kUnit, is_lo ? &tm_lo : &tm_hi, &b_full[slot], 64 * hh, row, 0);
+                        }
             if (!ok) s_err = 1;
         }
     } else if (warp == C::kWarpMma) {
@@ -222,43 +223,42 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             // descriptors differ only in their 16-byte-granular start address: build the bases once
             const uint64_t d_a0 = smem_desc_sw128(smem_u32(smem), 16, 1024);
             const uint64_t d_b0 = smem_desc_sw128(smem_u32(smem + C::kB), 16, 1024);
-            const int total = n_act * M * upj;
             bool ok = true;
-            for (int g = 0; g < total && ok; ++g) {
-                const int slot = g % SL;
-                const int job = g / upj, t = g % upj;
-                const int m = job / n_act, s = job % n_act;
-                const int ch = t / (2 * NH), rem = t % (2 * NH), is_lo = rem / NH, hh = rem % NH;
-                if (t == 0) {
+            int g = 0;
+            for (int m = 0; m < M && ok; ++m)
+                for (int s = 0; s < n_act && ok; ++s) {
                     // the residual terms of (s, m): the key tile itself for m = 0, else written by the scan threads
                     if (!(m == 0 ? mbar_wait(&bar_k[s], 0) : mbar_wait(&bar_q[s], (m - 1) & 1))) {
                         ok = false;
                         break;
                     }
-                }
-                if (!mbar_wait(&b_full[slot], (g / SL) & 1)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint64_t d_b = d_b0 + static_cast<uint64_t>((slot * C::kUnit) >> 4);
-                const uint64_t d_rh = d_a0 + static_cast<uint64_t>((s * 2 * C::kATile + hh * kHalfBytes) >> 4);
-                const uint64_t d_rl = d_rh + static_cast<uint64_t>(C::kATile >> 4);
-                const uint32_t dcol = tmem + s * C::kRegion + ch * CH;
-                uint32_t acc = rem == 0 ? 0u : 1u;
+                    for (int ch = 0; ch < chunks && ok; ++ch) {
+                        const uint32_t dcol = tmem + s * C::kRegion + ch * CH;
 #pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4) {
-                    mma_ss(dcol, d_rh + static_cast<uint64_t>((k4 * 32) >> 4), d_b + static_cast<uint64_t>((k4 * 32) >> 4), idesc, acc);
-                    acc = 1;
-                }
-                if (!is_lo && m > 0) {
+                        for (int rem = 0; rem < 2 * NH; ++rem, ++g) {
+                            const int slot = g % SL, is_lo = rem / NH, hh = rem % NH;
+                            if (!mbar_wait(&b_full[slot], (g / SL) & 1)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+                            const uint64_t d_b = d_b0 + static_cast<uint64_t>((slot * C::kUnit) >> 4);
+                            const uint64_t d_rh = d_a0 + static_cast<uint64_t>((s * 2 * C::kATile + hh * kHalfBytes) >> 4);
+                            const uint64_t d_rl = d_rh + static_cast<uint64_t>(C::kATile >> 4);
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)
-                        mma_ss(dcol, d_rl + static_cast<uint64_t>((k4 * 32) >> 4), d_b + static_cast<uint64_t>((k4 * 32) >> 4), idesc, 1u);
+                            for (int k4 = 0; k4 < 4; ++k4)
+                                mma_ss(dcol, d_rh + static_cast<uint64_t>((k4 * 32) >> 4), d_b + static_cast<uint64_t>((k4 * 32) >> 4), idesc,
+                                       (rem | k4) ? 1u : 0u);
+                            if (!is_lo && m > 0) {
+#pragma unroll
+                                for (int k4 = 0; k4 < 4; ++k4)
+                                    mma_ss(dcol, d_rl + static_cast<uint64_t>((k4 * 32) >> 4), d_b + static_cast<uint64_t>((k4 * 32) >> 4), idesc, 1u);
+                            }
+                            tc_commit(&b_free[slot]);
+                            if (rem == 2 * NH - 1) tc_commit(&bar_c[s][ch]);  // this chunk's score columns are complete
+                        }
+                    }
                 }
-                tc_commit(&b_free[slot]);
-                if (rem == 2 * NH - 1) tc_commit(&bar_c[s][ch]);  // this chunk's 128 score columns are complete
-            }
             if (!ok) s_err = 1;
         }
     } else if ((warp >> 2) < n_act) {
