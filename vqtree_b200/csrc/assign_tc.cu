@@ -9,13 +9,16 @@
 //      residual is carried as two bf16 terms as well, rho_m = Rh + Rl (rho_0 = k exactly, Rl = 0);
 //      after the code of codebook m is known, t = (Rh + Rl) - C_m[code] in fp32 is re-split.  The
 //      tensor cores form  s~ = Rh.Ch + Rl.Ch + Rh.Cl  with fp32 accumulation.
-//   2. Error of s~ against the defining chain, in units of |r| |C| (|r| <= R = |k| + sum of the
-//      largest codeword norms of the codebooks before m):  split of C and dropped Rl.Cl: 2 * 2^-18;
+//   2. Error of s~ against the defining chain, in units of |r| |C| (|r|: the norm of the residual,
+//      bounded from the residual itself, which the thread has in hand when it re-splits it; a priori
+//      |r| <= |k| + sum of the largest codeword norms of the codebooks before m):
+//      split of C and dropped Rl.Cl: 2 * 2^-18;
 //      re-splits of the residual: m * (2^-18 + 3 * 2^-24);  the fp32 chain itself: D * 2^-24 <= 2^-17;
-//      tensor-core accumulation of 3 D exact products, each addition truncated to fp32:
-//      3 D * 2^-23 <= 12.1 * 2^-18;  index tag in the low five mantissa bits (see tag_score): 2^-18.
-//      For M <= 8 that is below 25 * 2^-18; eps = 2^-13 = 32 * 2^-18.
-//      A key whose best approximate score leads the runner-up by more than thr = 2 eps R max|C_m|
+//      tensor-core accumulation of 3 D (codebook 0: 2 D) exact products, each addition truncated to fp32:
+//      3 D * 2^-23 <= 12 * 2^-18;  index tag in the low five mantissa bits (see tag_score): 2^-18.
+//      Sum for D = 128: 13 units of 2^-18 for codebook 0, 17 + 1.05 m for codebook m; the kernel uses
+//      eps_m = (4 + D/64 + (2 or 3) D/32 + 1.1 m) 2^-18, one unit above that.
+//      A key whose best approximate score leads the runner-up by more than thr = 2 eps |r| max|C_m|
 //      has a unique arg-max: that code is final.
 //   3. The other keys (a few per cent for random data) are settled exactly on the spot: every
 //      (key, candidate code within thr of the best) pair of a warp gets a lane, which runs the
@@ -33,7 +36,6 @@ using namespace ptx;
 constexpr int kAtMinChunk = 128;   // codewords per MMA chunk: 128, or 256 (one N = 256 instruction) when K allows
 constexpr int kAtMaxM = 8;
 constexpr int kAtMaxK = 512;
-constexpr float kAtEps = 1.220703125e-4f;  // 2^-13
 constexpr int kAtPairCap = 32;     // (key, candidate) pairs re-scored per pass of a warp
 
 // ------------------------------------------------------------------------------------------------
@@ -277,7 +279,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         const float *cbh = p.cb + static_cast<int64_t>(h) * MK * D;
         uint8_t *a_rh = smem + s * 2 * C::kATile, *a_rl = a_rh + C::kATile;
         const int groups = K / 32;
-        float rbound;  // R: bound of the residual's norm
+        float rbound;  // |k| + sum of the largest codeword norms so far: a priori bound of the residual's norm
+        float rnow;    // bound of the current residual's norm from the residual itself (tighter)
         {
             float ss = 0.f;
 #pragma unroll 4
@@ -291,6 +294,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 }
             }
             rbound = sqrtf(ss) * 1.0001f;
+            rnow = rbound;
         }
         bool ok = true;
         int prev[kAtMaxM];
@@ -298,7 +302,9 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         for (int mm = 0; mm < kAtMaxM; ++mm) prev[mm] = 0;
         for (int m = 0; m < M && ok; ++m) {
             const float cm = p.cmax[h * M + m];
-            const float thr0 = 2.f * kAtEps * rbound * cm + 1e-30f;
+            // eps of this codebook in units of 2^-18: the terms listed at the top of the file plus one unit of slack
+            const float eps_m = (4.f + D / 64 + (m > 0 ? 3 : 2) * (D / 32) + 1.1f * m) * 3.814697265625e-6f;
+            const float thr0 = 2.f * eps_m * rnow * cm + 1e-30f;
             const float *bm = p.bias ? p.bias + (static_cast<int64_t>(h) * M + m) * K : nullptr;
             // ---- scan, chunk by chunk as the tensor pipe finishes them: best and runner-up of the tagged
             // scores (the tag of the best gives its index inside its group of 32).  gbits marks the groups
@@ -436,6 +442,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 // Every thread updates its own key's row, 8 columns (one 16-byte chunk of each term) at a time.
                 const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D;
                 const uint32_t rbase = row * 128;
+                float ss = 0.f;  // squared norm of the new residual
 #pragma unroll 8
                 for (int ck = 0; ck < D / 8; ++ck) {
                     const float4 ca = __ldg(reinterpret_cast<const float4 *>(crow + 8 * ck));
@@ -462,6 +469,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     }
                     x[0] -= ca.x; x[1] -= ca.y; x[2] -= ca.z; x[3] -= ca.w;
                     x[4] -= cb4.x; x[5] -= cb4.y; x[6] -= cb4.z; x[7] -= cb4.w;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
                     uint32_t wh[4], wl[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -473,6 +482,9 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     *ph = make_uint4(wh[0], wh[1], wh[2], wh[3]);
                     *pl = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
+                // The operand of the next scores is this residual (norm sqrt(ss) up to rounding); the exact chain's
+                // residual differs from it by at most (m + 1) (2^-18 + 3 * 2^-24) times the a priori bound.
+                rnow = sqrtf(ss) * 1.001f + static_cast<float>(m + 1) * 7.7e-6f * rbound;
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(&bar_q[s]);
