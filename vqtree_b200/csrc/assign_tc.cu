@@ -37,6 +37,7 @@ constexpr int kAtMinChunk = 128;   // codewords per MMA chunk: 128, or 256 (one 
 constexpr int kAtMaxM = 8;
 constexpr int kAtMaxK = 512;
 constexpr int kAtPairCap = 32;     // (key, candidate) pairs re-scored per pass of a warp
+constexpr int kAtLanesPerPair = 8;  // ... eight lanes per pair when there are at most four
 
 // ------------------------------------------------------------------------------------------------
 // fp32 codebook -> bf16 hi / lo terms [Hkv, M*K, D] and the largest row norm of every codebook.
@@ -378,10 +379,15 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                         n = min(kAtPairCap, n + total);
                         if (n < kAtPairCap && !flush) break;  // room left: collect from the next group first
                         __syncwarp();
-                        const bool act = lane < n;
+                        // A few pairs (the usual case): eight lanes per pair, each loads one eighth of the rows (all
+                        // loads in flight at once) and the FMA chain walks from lane to lane in d order.  Many pairs:
+                        // one lane per pair.
+                        const bool few = n <= 32 / kAtLanesPerPair;
+                        const int slot = few ? lane / kAtLanesPerPair : lane;   // pair of this lane
+                        const bool act = slot < n;
                         int owner = lane, c = 0;
                         if (act) {
-                            const int e = list[lane];
+                            const int e = list[slot];
                             owner = e >> 9;
                             c = e & 511;
                         }
@@ -389,26 +395,59 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
                         for (int mm = 0; mm < kAtMaxM; ++mm) pv[mm] = (mm < m) ? __shfl_sync(kAll, prev[mm], owner) : 0;
                         float sc = -INFINITY;
-                        if (act) {
-                            // the defining chain: r_m = ((k - C_0[c_0]) - C_1[c_1]) - ..., one FMA chain over d
-                            const __nv_bfloat16 *ks = kbase + (j0 + wq * 32 + owner) * p.k_sl;
-                            const float *cc = cbh + (static_cast<int64_t>(m) * K + c) * D;
+                        // the defining chain: r_m = ((k - C_0[c_0]) - C_1[c_1]) - ..., one FMA chain over d
+                        const __nv_bfloat16 *ks = kbase + (j0 + wq * 32 + owner) * p.k_sl;
+                        const float *cc = cbh + (static_cast<int64_t>(m) * K + c) * D;
+                        auto residual4 = [&](int d) {
+                            const uint2 raw = *reinterpret_cast<const uint2 *>(ks + d);
+                            const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
+                            const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
+                            float4 r4 = make_float4(__low2float(lo2), __high2float(lo2), __low2float(hi2), __high2float(hi2));
+#pragma unroll
+                            for (int mm = 0; mm < kAtMaxM; ++mm)
+                                if (mm < m) {
+                                    const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(mm) * K + pv[mm]) * D + d));
+                                    r4.x = __fsub_rn(r4.x, c4.x);
+                                    r4.y = __fsub_rn(r4.y, c4.y);
+                                    r4.z = __fsub_rn(r4.z, c4.z);
+                                    r4.w = __fsub_rn(r4.w, c4.w);
+                                }
+                            return r4;
+                        };
+                        if (few) {
+                            constexpr int SEG = D / kAtLanesPerPair, STEPS = SEG / 4;  // columns / float4 steps of a lane
+                            const int q = lane % kAtLanesPerPair;
+                            float4 r4[STEPS], c4[STEPS];
+                            if (act) {
+#pragma unroll
+                                for (int st = 0; st < STEPS; ++st) {
+                                    r4[st] = residual4(SEG * q + 4 * st);
+                                    c4[st] = __ldg(reinterpret_cast<const float4 *>(cc + SEG * q + 4 * st));
+                                }
+                            } else {
+#pragma unroll
+                                for (int st = 0; st < STEPS; ++st) r4[st] = c4[st] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                            float acc = 0.f;
+#pragma unroll 1
+                            for (int seg = 0; seg < kAtLanesPerPair; ++seg) {
+                                if (q == seg) {
+#pragma unroll
+                                    for (int st = 0; st < STEPS; ++st) {
+                                        acc = __fmaf_rn(r4[st].x, c4[st].x, acc);
+                                        acc = __fmaf_rn(r4[st].y, c4[st].y, acc);
+                                        acc = __fmaf_rn(r4[st].z, c4[st].z, acc);
+                                        acc = __fmaf_rn(r4[st].w, c4[st].w, acc);
+                                    }
+                                }
+                                acc = __shfl_sync(kAll, acc, (lane & ~(kAtLanesPerPair - 1)) | seg);
+                            }
+                            if (act) sc = bm ? __fadd_rn(acc, __ldg(bm + c)) : acc;
+                        } else if (act) {
                             float acc = 0.f;
 #pragma unroll 8
                             for (int d = 0; d < D; d += 4) {
-                                const uint2 raw = *reinterpret_cast<const uint2 *>(ks + d);
-                                const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
-                                const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
-                                float4 r4 = make_float4(__low2float(lo2), __high2float(lo2), __low2float(hi2), __high2float(hi2));
-#pragma unroll
-                                for (int mm = 0; mm < kAtMaxM; ++mm)
-                                    if (mm < m) {
-                                        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(mm) * K + pv[mm]) * D + d));
-                                        r4.x = __fsub_rn(r4.x, c4.x);
-                                        r4.y = __fsub_rn(r4.y, c4.y);
-                                        r4.z = __fsub_rn(r4.z, c4.z);
-                                        r4.w = __fsub_rn(r4.w, c4.w);
-                                    }
+                                const float4 r4 = residual4(d);
                                 const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cc + d));
                                 acc = __fmaf_rn(r4.x, c4.x, acc);
                                 acc = __fmaf_rn(r4.y, c4.y, acc);
@@ -418,10 +457,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                             sc = bm ? __fadd_rn(acc, __ldg(bm + c)) : acc;
                         }
                         __syncwarp();
+                        const int stride = few ? kAtLanesPerPair : 1;
 #pragma unroll 1
                         for (int t = 0; t < n; ++t) {
-                            const int ot = __shfl_sync(kAll, owner, t), ct = __shfl_sync(kAll, c, t);
-                            const float st = __shfl_sync(kAll, sc, t);
+                            const int ot = __shfl_sync(kAll, owner, t * stride), ct = __shfl_sync(kAll, c, t * stride);
+                            const float st = __shfl_sync(kAll, sc, t * stride);
                             if (lane == ot && (st > bv || (st == bv && ct < bi))) {
                                 bv = st;
                                 bi = ct;
