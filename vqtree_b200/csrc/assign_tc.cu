@@ -483,7 +483,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D;
                 const uint32_t rbase = row * 128;
                 float ss = 0.f;  // squared norm of the new residual
-#pragma unroll 8
+#pragma unroll 16
                 for (int ck = 0; ck < D / 8; ++ck) {
                     const float4 ca = __ldg(reinterpret_cast<const float4 *>(crow + 8 * ck));
                     const float4 cb4 = __ldg(reinterpret_cast<const float4 *>(crow + 8 * ck + 4));
