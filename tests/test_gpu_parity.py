@@ -286,6 +286,9 @@ def test_errors_are_reported_not_crashed(api):
     (1, 2, 1024, 128, 8, 256),     # config 5 codebooks
     (1, 3, 515, 64, 2, 128),       # D = 64
     (1, 1, 128, 128, 1, 64),       # single chunk
+    (1, 2, 900, 128, 3, 384),      # three 128-codeword chunks, one key tile per CTA
+    (2, 1, 640, 64, 2, 512),       # D = 64 with 9-bit codes
+    (1, 2, 385, 128, 2, 128),      # odd number of key tiles: the last CTA has one
 ])
 def test_assign_tensor_path_is_bit_exact(api, B, Hkv, L, D, M, K):
     g = torch.Generator().manual_seed(77 + L + K + M)
