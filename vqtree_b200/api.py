@@ -285,25 +285,36 @@ def vq_attention_prefill_host(q1, q2, k1, k3, v, codebooks, window: int, scale: 
         parts = [(b, h0, min(Hkv, h0 + hc)) for b in range(B) for h0 in range(0, Hkv, hc)]
         s_in.wait_stream(cur)
         s_out.wait_stream(cur)
+        # copy order k, v, q: the kernels of a chunk need them in that order (codes from k, aggregates from v,
+        # attention from q), so each stage waits only for what it reads
+        Hkv_, M_, K_, _ = dcb.shape
+        nb = far_blocks(L, window)
         arrived = []
         with torch.cuda.stream(s_in):
             for b, h0, h1 in parts:
                 g0, g1 = h0 * group, h1 * group
-                dq1[b, g0:g1].copy_(hq1[b, g0:g1], non_blocking=True)
-                if not same_q:
-                    dq2[b, g0:g1].copy_(hq2[b, g0:g1], non_blocking=True)
-                dk1[b, h0:h1].copy_(hk1[b, h0:h1], non_blocking=True)
-                if not same_k:
-                    dk3[b, h0:h1].copy_(hk3[b, h0:h1], non_blocking=True)
-                dv[b, h0:h1].copy_(hv[b, h0:h1], non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record(s_in)
-                arrived.append(ev)
-        for (b, h0, h1), ev in zip(parts, arrived):
+                evs = []
+                for dst, src, lo, hi, skip in ((dk1, hk1, h0, h1, False), (dk3, hk3, h0, h1, same_k), (dv, hv, h0, h1, False),
+                                                (dq1, hq1, g0, g1, False), (dq2, hq2, g0, g1, same_q)):
+                    if not skip:
+                        dst[b, lo:hi].copy_(src[b, lo:hi], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(s_in)
+                    evs.append(ev)
+                arrived.append(evs)
+        for (b, h0, h1), evs in zip(parts, arrived):
             g0, g1 = h0 * group, h1 * group
-            cur.wait_event(ev)
-            vq_attention_prefill(dq1[b:b + 1, g0:g1], dq2[b:b + 1, g0:g1], dk1[b:b + 1, h0:h1], dk3[b:b + 1, h0:h1],
-                                 dv[b:b + 1, h0:h1], dcb[h0:h1], window, scale, impl=impl, out=dout[b:b + 1, g0:g1])
+            sl_q, sl_k = (slice(b, b + 1), slice(g0, g1)), (slice(b, b + 1), slice(h0, h1))
+            cnt = vsum = cb_act = None
+            if nb > 0:
+                cur.wait_event(evs[1])   # k1, k3
+                codes = assign_codes(dk3[sl_k], dcb[h0:h1])
+                cur.wait_event(evs[2])   # v
+                cnt, vsum = build_aggregates(codes, dv[sl_k], K_, nb)
+                cb_act = dcb[h0:h1].reshape(h1 - h0, M_ * K_, D).to(q1.dtype)
+            cur.wait_event(evs[4])       # q1, q2 (and everything before them)
+            prefill_from_aggregates(dq1[sl_q], dq2[sl_q], dk1[sl_k], dk3[sl_k], dv[sl_k], cb_act, cnt, vsum, window, scale,
+                                    impl, out=dout[sl_q])
             done = torch.cuda.Event()
             done.record(cur)
             s_out.wait_event(done)
