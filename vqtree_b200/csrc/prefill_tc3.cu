@@ -26,20 +26,26 @@ namespace vq {
 
 using namespace ptx;
 
-constexpr int kT3Threads = 576;   // 16 softmax warps + MMA warp + TMA warp
-constexpr int kT3WarpMma = 16, kT3WarpTma = 17;
+#ifndef VQ_T3_TPR
+#define VQ_T3_TPR 4
+#endif
 constexpr int kT3Bufs = 3;        // S/P buffers
 constexpr float kT3Lazy = 8.f;    // log2 units: P stays below 2^8
 
-template <int D>
+template <int D, int TPR>   // TPR: softmax threads per query row (4 or 2)
 struct T3Cfg {
+    static constexpr int kWarps = 4 * TPR;                     // softmax warps
+    static constexpr int kWarpMma = kWarps, kWarpTma = kWarps + 1;
+    static constexpr int kThreads = (kWarps + 2) * 32;
+    static constexpr int kCpt = 128 / TPR;                     // key columns of a work item per softmax thread
+    static constexpr int kChunks = kCpt / 32;
     static constexpr int NH = D / 64;
     static constexpr int kTile = NH * kHalfBytes;             // 128 x D bf16
     static constexpr int kSlots = 4;                           // ring of K / V tiles
     static constexpr int kQ1 = 0, kQ2 = kTile, kRing = 2 * kTile;
     static constexpr int kTotal = kRing + kSlots * kTile + 1024;  // + slack for 1024-byte alignment
     static constexpr uint32_t kColS = 0, kColO = 128 * kT3Bufs, kCols = 512;
-    static constexpr int kOq = D / 4;                          // O columns rescaled / written by one thread
+    static constexpr int kOq = D / TPR;                        // O columns rescaled / written by one thread
 };
 
 // One thread's 32 score columns of an item.  MODE 0: no mask; 1: columns [lo, hi) valid (relative to
@@ -71,10 +77,10 @@ __device__ __forceinline__ float t3_max_pass(uint32_t s_addr, int lo, int hi)
     return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
-// P = exp2(S * scale - m) for the thread's 32 columns, packed bf16 written over its first 16 S columns;
+// P = exp2(S * scale - m) for 32 of the thread's columns, packed bf16 written to 16 columns at p_addr;
 // returns the (count-weighted for MODE 2) sum of the 32 values.
 template <int MODE>
-__device__ __forceinline__ float t3_exp_pass(uint32_t s_addr, const float *cw, int lo, int hi,
+__device__ __forceinline__ float t3_exp_pass(uint32_t s_addr, uint32_t p_addr, const float *cw, int lo, int hi,
                                              float scale_log2, float neg_m)
 {
     uint32_t r[32], pk[16];
@@ -93,25 +99,25 @@ __device__ __forceinline__ float t3_exp_pass(uint32_t s_addr, const float *cw, i
         else fadd2(ls[2 * (j & 1)], ls[2 * (j & 1) + 1], ls[2 * (j & 1)], ls[2 * (j & 1) + 1], p0, p1);
         pk[j] = pack_bf16(p0, p1);
     }
-    tmem_st16(s_addr, pk);
+    tmem_st16(p_addr, pk);
     return (ls[0] + ls[1]) + (ls[2] + ls[3]);
 }
 
-template <int D>
-__global__ void __launch_bounds__(kT3Threads, 1)
+template <int D, int TPR>
+__global__ void __launch_bounds__(T3Cfg<D, TPR>::kThreads, 1)
 prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                    const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k3,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_cb,
                    const __grid_constant__ CUtensorMap tm_vs, TcParams p)
 {
-    using C = T3Cfg<D>;
+    using C = T3Cfg<D, TPR>;
     constexpr int NH = C::NH, NS = C::kSlots, NB3 = kT3Bufs;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(8) uint64_t bar_q, kv_full[NS], kv_empty[NS], s_full[NB3], p_full[NB3], pv_done[NB3], maxbar[4][NB3], lbar[4];
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
-    __shared__ __align__(16) float s_cw[16][2][32];      // [softmax warp][item parity][column]: counts of a far tile
+    __shared__ __align__(16) float s_cw[C::kWarps][2][C::kCpt];  // [softmax warp][item parity][column]: counts of a far tile
     __shared__ __align__(16) float s_xch[NB3][kBlock][4]; // [item % 3][row][column quarter]: partial row maxima
     __shared__ __align__(16) float s_l[kBlock][4];        // partial denominators at the end
 
@@ -132,15 +138,15 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         }
         for (int i = 0; i < NB3; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 16);    // one arrival per softmax warp
+            mbar_init(&p_full[i], C::kWarps);  // one arrival per softmax warp
             mbar_init(&pv_done[i], 1);
-            for (int g = 0; g < 4; ++g) mbar_init(&maxbar[g][i], 4);
+            for (int g = 0; g < 4; ++g) mbar_init(&maxbar[g][i], TPR);
         }
-        for (int g = 0; g < 4; ++g) mbar_init(&lbar[g], 4);
+        for (int g = 0; g < 4; ++g) mbar_init(&lbar[g], TPR);
         fence_mbar_init();
         s_err = 0;
     }
-    if (warp == kT3WarpTma) {
+    if (warp == C::kWarpTma) {
         __syncwarp();
         tmem_alloc(&s_tmem, C::kCols);
         tmem_relinquish();
@@ -150,7 +156,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     tc_fence_after();
     const uint32_t tmem = s_tmem;
 
-    if (warp == kT3WarpTma) {
+    if (warp == C::kWarpTma) {
         // ================================================================== TMA producer
         if (lane == 0) {
             prefetch_tmap(&tm_q1); prefetch_tmap(&tm_k1); prefetch_tmap(&tm_v);
@@ -191,7 +197,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             }
             if (!ok) s_err = 1;
         }
-    } else if (warp == kT3WarpMma) {
+    } else if (warp == C::kWarpMma) {
         // ================================================================== MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_bf16(128, 128, 0, 0);
@@ -237,8 +243,8 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
                 const uint64_t dv = d_v0 + static_cast<uint64_t>((slot * C::kTile) >> 4);
                 const uint32_t odst = tmem + C::kColO, psrc = tmem + C::kColS + 128 * buf;
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)  // keys 16 kk ..: written by column quarter kk / 2 at its columns 8 (kk & 1) ..
-                    mma_ts(odst, psrc + 32 * (kk >> 1) + 8 * (kk & 1), dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
+                for (int kk = 0; kk < 8; ++kk)  // keys 16 kk ..: written by the thread that owns them, packed over its own S columns
+                    mma_ts(odst, psrc + C::kCpt * ((16 * kk) / C::kCpt) + ((16 * kk) % C::kCpt) / 2, dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
                            (it | kk) ? 1u : 0u);
                 tc_commit(&kv_empty[slot]);
                 tc_commit(&pv_done[buf]);
@@ -254,35 +260,39 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     } else {
         // ================================================================== softmax
         constexpr unsigned kAll = 0xffffffffu;
-        const int lq = warp & 3, cq = warp >> 2;         // lane quarter (32 query rows) and column quarter (32 keys)
+        const int lq = warp & 3, cq = warp >> 2;         // lane quarter (32 query rows) and column part (kCpt keys)
         const int row = lq * 32 + lane;                   // query row inside the tile (= TMEM lane)
         const uint32_t lane_off = static_cast<uint32_t>(lq * 32) << 16;
-        const uint32_t s_base = tmem + lane_off + C::kColS + 32 * cq;  // + 128 * buffer
+        const uint32_t s_base = tmem + lane_off + C::kColS + C::kCpt * cq;  // + 128 * buffer
         const uint32_t o_addr = tmem + lane_off + C::kColO + cq * C::kOq;
         float row_m = -INFINITY, l_part = 0.f;            // row_m: the maximum P and O are currently scaled by
         bool ok = true;
         // Counts of a far tile: lane l of the warp fetches the count of the warp's column l one item
         // ahead and the warp keeps them in its own shared-memory slot.
-        const float *cnt_base = p.cnt + (static_cast<int64_t>(u) * p.NB + work.far_blk) * p.MK + 32 * cq + lane;
+        const float *cnt_base = p.cnt + (static_cast<int64_t>(u) * p.NB + work.far_blk) * p.MK + C::kCpt * cq + lane;
         float *cw_w = &s_cw[warp][0][0];
-        float cnt_reg = work.n_far > 0 ? __ldg(cnt_base) : 0.f;
-        auto publish_counts = [&](int it, float c) {
+        float cnt_reg[C::kChunks];
+#pragma unroll
+        for (int i = 0; i < C::kChunks; ++i) cnt_reg[i] = work.n_far > 0 ? __ldg(cnt_base + 32 * i) : 0.f;
+        auto publish_counts = [&](int it) {
             __syncwarp();
-            cw_w[(it & 1) * 32 + lane] = c;
+#pragma unroll
+            for (int i = 0; i < C::kChunks; ++i) cw_w[(it & 1) * C::kCpt + 32 * i + lane] = cnt_reg[i];
             __syncwarp();
         };
         // valid key columns of this row in item `it`, relative to this thread's first column: [lo, hi)
         auto bounds = [&](int kind, int &lo, int &hi) {
             lo = 0;
-            hi = 32;
-            if (kind == kDiag) hi = row + 1 - 32 * cq;
-            else if (kind == kBdA) hi = row - 32 * cq;
-            else if (kind == kBdB) lo = row - 32 * cq;
+            hi = C::kCpt;
+            if (kind == kDiag) hi = row + 1 - C::kCpt * cq;
+            else if (kind == kBdA) hi = row - C::kCpt * cq;
+            else if (kind == kBdB) lo = row - C::kCpt * cq;
         };
         // partial row maximum of item `it`, published for the other three threads of the row
         auto publish_max = [&](int it) {
-            if (it < work.n_far) publish_counts(it, cnt_reg);
-            cnt_reg = (it + 1 < work.n_far) ? __ldg(cnt_base + (it + 1) * kBlock) : 0.f;
+            if (it < work.n_far) publish_counts(it);
+#pragma unroll
+            for (int i = 0; i < C::kChunks; ++i) cnt_reg[i] = (it + 1 < work.n_far) ? __ldg(cnt_base + (it + 1) * kBlock + 32 * i) : 0.f;
             const int buf = it % NB3;
             if (!__all_sync(kAll, mbar_wait(&s_full[buf], (it / NB3) & 1))) return false;
             tc_fence_after();
@@ -290,7 +300,11 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             int lo, hi;
             bounds(kind, lo, hi);
             const uint32_t sa = s_base + 128 * buf;
-            const float mx = (kind == kFar || kind == kFull) ? t3_max_pass<0>(sa, lo, hi) : t3_max_pass<1>(sa, lo, hi);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < C::kChunks; ++c)
+                mx = fmaxf(mx, (kind == kFar || kind == kFull) ? t3_max_pass<0>(sa + 32 * c, lo - 32 * c, hi - 32 * c)
+                                                              : t3_max_pass<1>(sa + 32 * c, lo - 32 * c, hi - 32 * c));
             s_xch[buf][row][cq] = mx;
             __syncwarp();
             if (lane == 0) mbar_arrive(&maxbar[lq][buf]);  // one arrival per warp: its 32 stores are ordered before it
@@ -309,8 +323,10 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
                 ok = false;
                 break;
             }
-            const float4 m4 = *reinterpret_cast<const float4 *>(&s_xch[buf][row][0]);
-            const float m_tile = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w)) * p.scale_log2;
+            float m_all = s_xch[buf][row][0];
+#pragma unroll
+            for (int i = 1; i < TPR; ++i) m_all = fmaxf(m_all, s_xch[buf][row][i]);
+            const float m_tile = m_all * p.scale_log2;
             // lazy rescaling: keep the old reference maximum unless the new one is far above it
             float m_use = row_m;
             if (m_tile > row_m + kT3Lazy || row_m == -INFINITY) m_use = fmaxf(row_m, m_tile);
@@ -323,13 +339,16 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
                     break;
                 }
                 tc_fence_after();
-                if constexpr (C::kOq == 32) {
-                    uint32_t r[32];
-                    tmem_ld32(o_addr, r);
-                    tc_wait_ld();
+                if constexpr (C::kOq >= 32) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-                    tmem_st32(o_addr, r);
+                    for (int c = 0; c < C::kOq / 32; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(o_addr + 32 * c, r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                        tmem_st32(o_addr + 32 * c, r);
+                    }
                 } else {
                     uint32_t r[16];
                     tmem_ld16(o_addr, r);
@@ -343,12 +362,16 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             const int kind = work.kind(it);
             int lo, hi;
             bounds(kind, lo, hi);
-            const float *cw = cw_w + (it & 1) * 32;
+            const float *cw = cw_w + (it & 1) * C::kCpt;
             const uint32_t sa = s_base + 128 * buf;
-            float ls;
-            if (kind == kFar) ls = t3_exp_pass<2>(sa, cw, lo, hi, p.scale_log2, -m_safe);
-            else if (kind == kFull) ls = t3_exp_pass<0>(sa, cw, lo, hi, p.scale_log2, -m_safe);
-            else ls = t3_exp_pass<1>(sa, cw, lo, hi, p.scale_log2, -m_safe);
+            float ls = 0.f;
+            // chunk c reads columns [32c, 32c+32) of the thread's part and writes P over [16c, 16c+16): never ahead of a read
+#pragma unroll
+            for (int c = 0; c < C::kChunks; ++c) {
+                if (kind == kFar) ls += t3_exp_pass<2>(sa + 32 * c, sa + 16 * c, cw + 32 * c, lo - 32 * c, hi - 32 * c, p.scale_log2, -m_safe);
+                else if (kind == kFull) ls += t3_exp_pass<0>(sa + 32 * c, sa + 16 * c, cw + 32 * c, lo - 32 * c, hi - 32 * c, p.scale_log2, -m_safe);
+                else ls += t3_exp_pass<1>(sa + 32 * c, sa + 16 * c, cw + 32 * c, lo - 32 * c, hi - 32 * c, p.scale_log2, -m_safe);
+            }
             l_part = l_part * alpha + ls;
             row_m = m_use;
             tc_wait_st();
@@ -365,14 +388,19 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         if (ok && !__all_sync(kAll, mbar_wait(&lbar[lq], 0))) ok = false;
         if (!ok) s_err = 1;
         if (ok) {
-            const float4 l4 = *reinterpret_cast<const float4 *>(&s_l[row][0]);
-            const float den = (l4.x + l4.y) + (l4.z + l4.w);
+            float den = s_l[row][0];
+#pragma unroll
+            for (int i = 1; i < TPR; ++i) den += s_l[row][i];
             const float inv = den > 0.f ? 1.f / den : 0.f;
             const int64_t grow = static_cast<int64_t>(m) * kBlock + row;
             __nv_bfloat16 *o = p.out + b * p.o_sb + hq * p.o_sh + grow * p.o_sl + cq * C::kOq;
             uint32_t r[C::kOq];
-            if constexpr (C::kOq == 32) tmem_ld32(o_addr, r);
-            else tmem_ld16(o_addr, r);
+            if constexpr (C::kOq >= 32) {
+#pragma unroll
+                for (int c = 0; c < C::kOq / 32; ++c) tmem_ld32(o_addr + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+            } else {
+                tmem_ld16(o_addr, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
+            }
             tc_wait_ld();
             if (grow < p.L) {
 #pragma unroll
@@ -397,7 +425,7 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
     }
     __syncthreads();
-    if (warp == kT3WarpTma) {
+    if (warp == C::kWarpTma) {
         __syncwarp();
         tmem_dealloc(tmem, C::kCols);
     }
@@ -406,15 +434,16 @@ prefill_tc3_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
 template <int D>
 static int launch_tc3(const VqPrefillArgs *a, cudaStream_t stream)
 {
-    using C = T3Cfg<D>;
+    constexpr int TPR = VQ_T3_TPR;
+    using C = T3Cfg<D, TPR>;
     TcMaps m;
     TcParams p;
     const int st = tc_setup<D>(a, m, p);
     if (st != VQ_OK) return st;
-    auto kern = prefill_tc3_kernel<D>;
+    auto kern = prefill_tc3_kernel<D, TPR>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
     dim3 grid(static_cast<unsigned>(p.ntiles), static_cast<unsigned>(a->q1.shape[0] * a->q1.shape[1]));
-    kern<<<grid, kT3Threads, C::kTotal, stream>>>(m.q1, m.q2, m.k1, m.k3, m.v, m.cb, m.vs, p);
+    kern<<<grid, C::kThreads, C::kTotal, stream>>>(m.q1, m.q2, m.k1, m.k3, m.v, m.cb, m.vs, p);
     return launch_status();
 }
 
