@@ -62,3 +62,39 @@ def test_long_prefilling_entry_point(golden_dir):
     want = torch.from_numpy(gd["out"]).transpose(1, 2).reshape(B, L, H * D)
     np.testing.assert_allclose(out.cpu().numpy(), want.numpy(), atol=1e-4, rtol=0)
     assert cache.get_seq_length(0) == L
+
+
+@pytest.mark.parametrize("dtype,L0,T,hq,hkv", [(torch.bfloat16, 600, 330, 8, 2), (torch.float32, 300, 140, 2, 2),
+                                               (torch.bfloat16, 100, 40, 4, 4)])
+def test_cache_prefill_then_decode_steps(dtype, L0, T, hq, hkv):
+    """Prefill L0 tokens into the cache, then generate T more one at a time (the boundary moves at least
+    twice in the long cases); every generated row must match the naive per-query attention over the whole sequence."""
+    from oracle import vq_oracle as vo
+    from vqtree_b200 import api
+    from vqtree_b200.attn_vq import (AttentionMode, VectorQuantizedReRoPECache, decode_step,
+                                     long_prefilling_sort_based_linear, rope_cos_sin, rotate_half)
+    B, D, M, K, W = 1, 128, 2, 128, 256
+    L = L0 + T
+    g = torch.Generator(device="cpu").manual_seed(77)
+    q = torch.randn(B, hq, L, D, generator=g).cuda().to(dtype)
+    k = torch.randn(B, hkv, L, D, generator=g).cuda().to(dtype)
+    v = torch.randn(B, hkv, L, D, generator=g).cuda().to(dtype)
+    cb = (torch.randn(hkv, M, K, D, generator=g) * 0.7).to(dtype).float().cuda()
+    cache = VectorQuantizedReRoPECache(W, cb, False, attention_mode=AttentionMode.SORT_BASED_LINEAR)
+    pos = torch.arange(L, device="cuda")[None].expand(B, -1)
+    got = [long_prefilling_sort_based_linear(q[:, :, :L0], k[:, :, :L0], v[:, :, :L0], pos[:, :L0], cache)]
+    assert cache.get_seq_length(0) == L0
+    for i in range(L0, L):
+        got.append(decode_step(q[:, :, i:i + 1], k[:, :, i:i + 1], v[:, :, i:i + 1], pos[:, i:i + 1], cache))
+    assert cache.get_seq_length(0) == L and cache.seen_tokens == L
+    got = torch.cat(got, dim=1).float().cpu().numpy()
+
+    cos, sin = rope_cos_sin(max(L, W + 2), D, q.device)
+    rot = lambda x, c, s: (x.float() * c + rotate_half(x.float()) * s).to(dtype).float().cpu().numpy()
+    q1, k1 = rot(q, cos[pos].unsqueeze(1), sin[pos].unsqueeze(1)), rot(k, cos[pos].unsqueeze(1), sin[pos].unsqueeze(1))
+    q2 = rot(q, cos[W + 1], sin[W + 1])
+    codes = api.assign_codes(k.contiguous(), cb).cpu().numpy()
+    want = vo.attn_naive(q1, q2, k1, k.float().cpu().numpy(), v.float().cpu().numpy(), cb.cpu().numpy(), codes, W)
+    want = want.transpose(0, 2, 1, 3).reshape(B, L, hq * D)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    np.testing.assert_allclose(got, want, atol=tol, rtol=0)

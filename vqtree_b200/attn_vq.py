@@ -84,3 +84,78 @@ def long_prefilling_sort_based_linear(query_states, key_states, value_states, po
     if layer_idx == 0:
         past_key_value.seen_tokens += q_len
     return out.transpose(1, 2).contiguous().flatten(2)
+
+
+def _decode_state(cache: VectorQuantizedReRoPECache, layer_idx: int):
+    """Turns the state a prefill left (all keys) into the decode form: a window of the newest keys from the
+    boundary on, and the aggregates (counts, fp32 value sums + their activation-dtype copy) of everything older."""
+    st = cache.layers[layer_idx]
+    if "win_k1" in st:
+        return st
+    W = cache.window_length
+    n = st["n"]
+    k1, k3, v, codes = st["k1"], st["k3"], st["v"], st["codes"]
+    B, Hkv, _, D = k3.shape
+    _, M, K, _ = cache.codebook.shape
+    dev, dt = k3.device, k3.dtype
+    bd = max(0, (n - W) // BLOCK_SIZE * BLOCK_SIZE)   # boundary of the NEXT query (position n)
+    nwin = W + 2 * BLOCK_SIZE                          # rows [bd, i] never exceed W + 128; one block of slack
+    win = lambda t: torch.zeros(B, Hkv, nwin, D, dtype=dt, device=dev)
+    st.update(win_k1=win(k1), win_k3=win(k3), win_v=win(v), bd=bd,
+              cnt=torch.zeros(B, Hkv, M * K, dtype=torch.float32, device=dev),
+              vsum32=torch.zeros(B, Hkv, M * K, D, dtype=torch.float32, device=dev),
+              vsum=torch.zeros(B, Hkv, M * K, D, dtype=dt, device=dev) if dt != torch.float32 else None,
+              cb_act=cache.codebook.reshape(Hkv, M * K, D).to(dt).contiguous())
+    for name, src in (("win_k1", k1), ("win_k3", k3), ("win_v", v)):
+        st[name][:, :, : n - bd] = src[:, :, bd:n]
+    if bd > 0:
+        if codes is None:
+            codes = api.assign_codes(k3.contiguous(), cache.codebook.float().contiguous())
+        api.cache_advance(codes[:, :, :bd].contiguous(), v[:, :, :bd].contiguous(), K, st["cnt"], st["vsum32"], st["vsum"])
+    for name in ("k1", "k3", "v", "codes"):
+        st.pop(name)
+    return st
+
+
+def decode_step(query_states, key_states, value_states, position_ids, past_key_value: VectorQuantizedReRoPECache,
+                layer_idx: int = 0, rope_base: float = 10000.0):
+    """One generated token (seqlen_q == 1): stands in for the reference's unfinished cache update
+    (ops/attn_vq.py:128-165) and the decode kernel its README names.
+
+    query_states [B,Hq,1,D], key/value_states [B,Hkv,1,D] (un-rotated), position_ids [B,1] (all equal to the number
+    of tokens seen).  The new key joins the window; when the boundary moves (every 128 tokens) the 128 oldest
+    window keys are quantised and folded into the aggregates.  Returns [B, 1, Hq*D].
+    """
+    st = _decode_state(past_key_value, layer_idx)
+    W = past_key_value.window_length
+    i = st["n"]                                        # position of the new token
+    assert int(position_ids.reshape(-1)[0]) == i, "decode_step expects the next position"
+    bsz, hq, _, d = query_states.shape
+    _, M, K, _ = past_key_value.codebook.shape
+    dt = query_states.dtype
+    cos, sin = rope_cos_sin(max(i + 1, W + 2), d, query_states.device, rope_base)
+    rot = lambda x, p: (x.float() * cos[p] + rotate_half(x.float()) * sin[p]).to(dt)
+    q1, q2 = rot(query_states[:, :, 0], i), rot(query_states[:, :, 0], W + 1)
+    bd = max(0, (i - W) // BLOCK_SIZE * BLOCK_SIZE)
+    if bd > st["bd"]:
+        # the boundary moved by one block: its keys leave the window for the aggregates
+        assert bd == st["bd"] + BLOCK_SIZE
+        old_k3 = st["win_k3"][:, :, :BLOCK_SIZE].contiguous()
+        codes = api.assign_codes(old_k3, past_key_value.codebook.float().contiguous())
+        api.cache_advance(codes, st["win_v"][:, :, :BLOCK_SIZE].contiguous(), K, st["cnt"], st["vsum32"], st["vsum"])
+        for name in ("win_k1", "win_k3", "win_v"):
+            st[name] = torch.roll(st[name], -BLOCK_SIZE, dims=2)
+        st["bd"] = bd
+    r = i - bd                                         # window row of the new key
+    st["win_k1"][:, :, r] = rot(key_states[:, :, 0], i)
+    st["win_k3"][:, :, r] = key_states[:, :, 0]
+    st["win_v"][:, :, r] = value_states[:, :, 0]
+    far = bd > 0
+    vs = st["vsum"] if st["vsum"] is not None else st["vsum32"]
+    out = api.vq_attention_decode(q1.contiguous(), q2.contiguous(), st["win_k1"], st["win_k3"], st["win_v"],
+                                  st["cb_act"] if far else None, st["cnt"] if far else None, vs if far else None,
+                                  n_valid=r + 1, n_bd=max(0, i - W) - bd, scale=1.0 / math.sqrt(d))
+    st["n"] = i + 1
+    if layer_idx == 0:
+        past_key_value.seen_tokens += 1
+    return out.reshape(bsz, 1, hq * d)
