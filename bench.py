@@ -382,7 +382,7 @@ def main():
         warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None,
         dtype="bf16", data="synthetic", config=cfg,
         stages_ms=dict(assign_codes=stage_ms[0], build_aggregates=stage_ms[1], fused_attention=stage_ms[2]),
-        roofline=dict(kernel="prefill_tc3_kernel (fused attention)", bound="tensor", achieved=attn_tflops, peak=peaks["tensor"],
+        roofline=dict(kernel="prefill_tc4_kernel (fused attention)", bound="tensor", achieved=attn_tflops, peak=peaks["tensor"],
                       unit="TFLOP/s", frac=attn_tflops / peaks["tensor"], peak_source=f"{peaks['source']} (burst bf16 matmul)",
                       traffic=attention_bytes(w) * 0.992, traffic_unit="bytes per launch",
                       traffic_note="algorithmic bytes x 0.992, the DRAM read+write / algorithmic ratio ncu measured on the c2 "

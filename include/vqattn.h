@@ -57,10 +57,12 @@ typedef struct VqTensorDesc {
 } VqTensorDesc;
 
 /* Which prefill kernel to run; AUTO picks the pipelined tensor-core kernel for bf16 and the fp32
- * kernel for f32.  TENSOR_SERIAL is the non-pipelined tensor-core kernel, TENSOR_TWOSTREAM the
- * pipelined kernel with two softmax states merged at the end (same arithmetic up to rounding). */
+ * kernel for f32.  Earlier tensor-core designs stay selectable: TENSOR_FOURWAY (four softmax threads
+ * per query row), TENSOR_TWOSTREAM (two softmax states merged at the end), TENSOR_SERIAL (not
+ * pipelined); all compute the same arithmetic up to rounding. */
 typedef enum VqPrefillImpl {
-    VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2, VQ_IMPL_TENSOR_SERIAL = 3, VQ_IMPL_TENSOR_TWOSTREAM = 4
+    VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2, VQ_IMPL_TENSOR_SERIAL = 3, VQ_IMPL_TENSOR_TWOSTREAM = 4,
+    VQ_IMPL_TENSOR_FOURWAY = 5
 } VqPrefillImpl;
 
 int vqattn_version(void);

@@ -17,7 +17,8 @@ from . import native
 from .native import BLOCK, VqDecodeArgs, VqPrefillArgs, check, desc, lib, stream_ptr
 
 _IMPL = {"auto": native.IMPL_AUTO, "simt": native.IMPL_SIMT, "tensor": native.IMPL_TENSOR,
-         "tensor_serial": native.IMPL_TENSOR_SERIAL, "tensor_twostream": native.IMPL_TENSOR_TWOSTREAM}
+         "tensor_serial": native.IMPL_TENSOR_SERIAL, "tensor_twostream": native.IMPL_TENSOR_TWOSTREAM,
+         "tensor_fourway": native.IMPL_TENSOR_FOURWAY}
 
 
 def _require_cuda(*ts):
