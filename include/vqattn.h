@@ -62,7 +62,7 @@ typedef struct VqTensorDesc {
  * pipelined); all compute the same arithmetic up to rounding. */
 typedef enum VqPrefillImpl {
     VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2, VQ_IMPL_TENSOR_SERIAL = 3, VQ_IMPL_TENSOR_TWOSTREAM = 4,
-    VQ_IMPL_TENSOR_FOURWAY = 5
+    VQ_IMPL_TENSOR_FOURWAY = 5, VQ_IMPL_TENSOR_PAIR = 6
 } VqPrefillImpl;
 
 int vqattn_version(void);

@@ -151,7 +151,7 @@ PREFILL_CASES = [
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,L,D,M,K,W,seed,rerope,dtype", PREFILL_CASES)
-@pytest.mark.parametrize("impl", ["simt", "tensor", "tensor_fourway", "tensor_twostream", "tensor_serial"])
+@pytest.mark.parametrize("impl", ["simt", "tensor", "tensor_fourway", "tensor_pair", "tensor_twostream", "tensor_serial"])
 def test_prefill_matches_naive_oracle(api, impl, B, Hq, Hkv, L, D, M, K, W, seed, rerope, dtype):
     if impl.startswith("tensor") and dtype != torch.bfloat16:
         pytest.skip("the tensor-core kernel computes in bf16")

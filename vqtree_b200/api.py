@@ -18,7 +18,7 @@ from .native import BLOCK, VqDecodeArgs, VqPrefillArgs, check, desc, lib, stream
 
 _IMPL = {"auto": native.IMPL_AUTO, "simt": native.IMPL_SIMT, "tensor": native.IMPL_TENSOR,
          "tensor_serial": native.IMPL_TENSOR_SERIAL, "tensor_twostream": native.IMPL_TENSOR_TWOSTREAM,
-         "tensor_fourway": native.IMPL_TENSOR_FOURWAY}
+         "tensor_fourway": native.IMPL_TENSOR_FOURWAY, "tensor_pair": native.IMPL_TENSOR_PAIR}
 
 
 def _require_cuda(*ts):

@@ -7,6 +7,7 @@ int launch_prefill_tensor(const VqPrefillArgs *a, cudaStream_t stream);
 int launch_prefill_tensor_serial(const VqPrefillArgs *a, cudaStream_t stream);
 int launch_prefill_tensor3(const VqPrefillArgs *a, cudaStream_t stream);
 int launch_prefill_tensor4(const VqPrefillArgs *a, cudaStream_t stream);
+int launch_prefill_pair(const VqPrefillArgs *a, cudaStream_t stream);
 }  // namespace vq
 
 extern "C" int vqattn_version(void) { return VQATTN_VERSION; }
@@ -94,10 +95,12 @@ extern "C" int vqattn_prefill(const VqPrefillArgs *a, void *stream)
     int impl = a->impl;
     if (impl == VQ_IMPL_AUTO) impl = (dt == VQ_BF16) ? VQ_IMPL_TENSOR : VQ_IMPL_SIMT;
     if (impl == VQ_IMPL_SIMT) return launch_prefill_simt(a, s);
-    if (impl == VQ_IMPL_TENSOR || impl == VQ_IMPL_TENSOR_SERIAL || impl == VQ_IMPL_TENSOR_TWOSTREAM || impl == VQ_IMPL_TENSOR_FOURWAY) {
+    if (impl == VQ_IMPL_TENSOR || impl == VQ_IMPL_TENSOR_SERIAL || impl == VQ_IMPL_TENSOR_TWOSTREAM || impl == VQ_IMPL_TENSOR_FOURWAY ||
+        impl == VQ_IMPL_TENSOR_PAIR) {
         if (dt != VQ_BF16) return VQ_EINVAL_DTYPE;
         if (impl == VQ_IMPL_TENSOR) return launch_prefill_tensor4(a, s);
         if (impl == VQ_IMPL_TENSOR_FOURWAY) return launch_prefill_tensor3(a, s);
+        if (impl == VQ_IMPL_TENSOR_PAIR) return launch_prefill_pair(a, s);
         return impl == VQ_IMPL_TENSOR_TWOSTREAM ? launch_prefill_tensor(a, s) : launch_prefill_tensor_serial(a, s);
     }
     return VQ_EINVAL_ARG;

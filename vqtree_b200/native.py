@@ -18,7 +18,7 @@ MAX_DIMS = 5
 BLOCK = 128
 
 VQ_F32, VQ_BF16, VQ_U8, VQ_U16, VQ_I32, VQ_I64 = range(6)
-IMPL_AUTO, IMPL_SIMT, IMPL_TENSOR, IMPL_TENSOR_SERIAL, IMPL_TENSOR_TWOSTREAM, IMPL_TENSOR_FOURWAY = 0, 1, 2, 3, 4, 5
+IMPL_AUTO, IMPL_SIMT, IMPL_TENSOR, IMPL_TENSOR_SERIAL, IMPL_TENSOR_TWOSTREAM, IMPL_TENSOR_FOURWAY, IMPL_TENSOR_PAIR = 0, 1, 2, 3, 4, 5, 6
 
 _DTYPES = {
     torch.float32: VQ_F32,
