@@ -199,6 +199,21 @@ size_t vqattn_decode_static_capacity(void);
 int vqattn_decode_static(const VqDecodeArgs *args, void *stream);
 
 /*
+ * Rotary position embedding of x [B,H,L,D] (f32|bf16) in the HF Llama half-split convention the
+ * reference applies before its kernels (ops/attn_vq.py:55-64,296-299: x*cos + rotate_half(x)*sin):
+ *   out_pos   (optional) [B,H,L,D]: every row rotated to its own position, positions[b*L + l]
+ *             (int64, device) or l when positions is NULL          (ops/attn_vq.py:402-404)
+ *   out_const (optional) [B,H,L,D]: every row rotated to const_pos, the ReRoPE query at
+ *             window + 1                                             (ops/attn_vq.py:405-407)
+ * cos_tab, sin_tab: device fp32 tables [n_pos, D/2] (angle = pos * base^(-2i/D)).  Products and sum
+ * are rounded separately in fp32, then once to the output dtype.  A position outside [0, n_pos)
+ * sets *status_word to 2 (status_word may be NULL) and uses the nearest table row.
+ * Constraints: D % 16 == 0 (bf16) or D % 8 == 0 (f32); 16-byte aligned rows.
+ */
+int vqattn_rope(const VqTensorDesc *x, const int64_t *positions, const float *cos_tab, const float *sin_tab, int64_t n_pos,
+                int64_t const_pos, VqTensorDesc *out_pos, VqTensorDesc *out_const, int32_t *status_word, void *stream);
+
+/*
  * Cache advance: folds `n_new` (a multiple of 128 is not required) keys that cross the boundary
  * into the running aggregates of a decode cache.  Stands in for the unfinished
  * ops/attn_vq.py:128-165 VectorQuantizedReRoPECache.update.

@@ -345,3 +345,40 @@ def test_prefill_host_pipeline_equals_device_path(api, B, Hq, Hkv, rerope, chunk
     got2 = api.vq_attention_prefill_host(case["q1"], case["q2"] if rerope else case["q1"], case["k1"],
                                          case["k3"] if rerope else case["k1"], case["v"], cb, case["W"], out=got)
     assert got2 is got and torch.equal(got2, want.cpu())
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float32, 64), (torch.bfloat16, 64)])
+def test_rope_matches_elementwise_expression_and_oracle(dtype, D):
+    """RoPE kernel against the element-wise expression the reference uses (ops/attn_vq.py:55-64,296-299,402-407):
+    bit-exact against the same fp32 arithmetic in PyTorch, and within rounding of the oracle's float64 tables."""
+    from oracle import vq_oracle as vo
+    from vqtree_b200 import api
+    from vqtree_b200.attn_vq import rope_cos_sin, rotate_half
+    B, H, L, W = 2, 3, 333, 128
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn(B, H, L, D, generator=g).cuda().to(dtype)
+    pos = torch.stack([torch.arange(L), torch.arange(L).flip(0)]).cuda()
+    cos, sin = rope_cos_sin(L, D, x.device)
+    ref = lambda c, s: (x.float() * c + rotate_half(x.float()) * s).to(dtype)
+    got_pos, got_const = api.rope(x, pos, const_pos=W + 1)
+    assert torch.equal(got_pos, ref(cos[pos].unsqueeze(1), sin[pos].unsqueeze(1)))
+    assert torch.equal(got_const, ref(cos[W + 1], sin[W + 1]))
+    plain, none = api.rope(x)                       # positions 0..L-1, no constant-position output
+    assert none is None and torch.equal(plain[0], got_pos[0])
+    only_const = api.rope(x[:, :, 5:9], const_pos=7, want_pos=False)   # a strided view, constant position only
+    assert only_const[0] is None and torch.equal(only_const[1], ref(cos[7], sin[7])[:, :, 5:9])
+    oc, osn = vo.rope_tables(L, D)
+    want = vo.apply_rope(x.float().cpu().numpy(), oc, osn, pos.cpu().numpy()[:, None, :])
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    np.testing.assert_allclose(got_pos.float().cpu().numpy(), want, atol=tol, rtol=0)
+    api.check_status()
+
+
+def test_rope_reports_positions_outside_the_tables():
+    from vqtree_b200 import api, native
+    x = torch.randn(1, 1, 16, 64, device="cuda")
+    pos = torch.arange(16, device="cuda")[None] + 10**6   # far beyond any table built so far (tables are cached and only grow)
+    api.rope(x, pos, n_pos=32)
+    with pytest.raises(native.VqError):
+        api.check_status()
+    api.check_status()   # the word was cleared

@@ -107,6 +107,47 @@ def build_aggregates(codes: torch.Tensor, v: torch.Tensor, K: int, nb: Optional[
     return cnt, vsum
 
 
+_ROPE_TABLES = {}
+
+
+def rope_tables(n_pos: int, dim: int, device, base: float = 10000.0):
+    """fp32 cos / sin tables [n_pos, dim/2] (angle = pos * base^(-2i/dim), evaluated in float64), cached per device."""
+    dev = torch.device(device)
+    key = (dev.index or 0, dim, float(base))
+    have = _ROPE_TABLES.get(key)
+    if have is None or have[0].shape[0] < n_pos:
+        n = max(n_pos, 2 * have[0].shape[0] if have is not None else 0)
+        inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float64, device=dev) / dim))
+        ang = torch.outer(torch.arange(n, dtype=torch.float64, device=dev), inv)
+        have = _ROPE_TABLES[key] = (ang.cos().float().contiguous(), ang.sin().float().contiguous())
+    return have
+
+
+def rope(x: torch.Tensor, positions: Optional[torch.Tensor] = None, const_pos: Optional[int] = None,
+         want_pos: bool = True, base: float = 10000.0, n_pos: Optional[int] = None):
+    """RoPE of x [B,H,L,D] (ops/attn_vq.py:296-299,402-407): returns (x rotated to its positions or None,
+    x rotated to ``const_pos`` or None), both from one pass.  positions: int64 [B,L] (None: 0..L-1);
+    n_pos: an upper bound of the positions + 1 (None: read from ``positions``, which synchronises)."""
+    dev = _require_cuda(x, positions)
+    B, H, L, D = x.shape
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if n_pos is None:
+        n_pos = L if positions is None else int(positions.max().item()) + 1
+    if const_pos is not None:
+        n_pos = max(n_pos, const_pos + 1)
+    cos, sin = rope_tables(n_pos, D, dev, base)
+    if positions is not None:
+        positions = positions.to(torch.int64).expand(B, L).contiguous()
+    out_pos = torch.empty((B, H, L, D), dtype=x.dtype, device=dev) if want_pos else None
+    out_const = torch.empty((B, H, L, D), dtype=x.dtype, device=dev) if const_pos is not None else None
+    with torch.cuda.device(dev):
+        check(lib.vqattn_rope(desc(x), positions.data_ptr() if positions is not None else None, cos.data_ptr(), sin.data_ptr(),
+                              cos.shape[0], const_pos if const_pos is not None else 0, desc(out_pos), desc(out_const),
+                              device_status_word(dev).data_ptr(), stream_ptr(dev)), "vqattn_rope")
+    return out_pos, out_const
+
+
 def gather_aggregates(v_vq: torch.Tensor, vi: torch.Tensor, nb: int, cnt: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Dense value sums from the reference's sorted-prefix format (v_vq [B,H,L+1,D], vi [B,H,NB,C]).
 

@@ -71,12 +71,9 @@ def long_prefilling_sort_based_linear(query_states, key_states, value_states, po
     """
     bsz, hq, q_len, d = query_states.shape
     W = past_key_value.window_length
-    cos, sin = rope_cos_sin(max(q_len, W + 2), d, query_states.device, rope_base)
-    c, s = cos[position_ids].unsqueeze(1), sin[position_ids].unsqueeze(1)
-    dt = query_states.dtype
-    q1 = (query_states.float() * c + rotate_half(query_states.float()) * s).to(dt)
-    k1 = (key_states.float() * c + rotate_half(key_states.float()) * s).to(dt)
-    q2 = (query_states.float() * cos[W + 1] + rotate_half(query_states.float()) * sin[W + 1]).to(dt)  # :405-407
+    n_pos = max(q_len, W + 2)
+    q1, q2 = api.rope(query_states, position_ids, const_pos=W + 1, base=rope_base, n_pos=n_pos)  # :402-407
+    k1, _ = api.rope(key_states, position_ids, base=rope_base, n_pos=n_pos)
     cb = past_key_value.codebook.float().contiguous()
     out, st = api.vq_attention_prefill(q1, q2, k1, key_states.contiguous(), value_states.contiguous(), cb, W,
                                        scale=1.0 / math.sqrt(d), return_state=True)
@@ -132,10 +129,10 @@ def decode_step(query_states, key_states, value_states, position_ids, past_key_v
     assert int(position_ids.reshape(-1)[0]) == i, "decode_step expects the next position"
     bsz, hq, _, d = query_states.shape
     _, M, K, _ = past_key_value.codebook.shape
-    dt = query_states.dtype
-    cos, sin = rope_cos_sin(max(i + 1, W + 2), d, query_states.device, rope_base)
-    rot = lambda x, p: (x.float() * cos[p] + rotate_half(x.float()) * sin[p]).to(dt)
-    q1, q2 = rot(query_states[:, :, 0], i), rot(query_states[:, :, 0], W + 1)
+    n_pos = max(i + 1, W + 2)
+    q1, q2 = api.rope(query_states, position_ids, const_pos=W + 1, base=rope_base, n_pos=n_pos)
+    k1_new, _ = api.rope(key_states, position_ids, base=rope_base, n_pos=n_pos)
+    q1, q2 = q1[:, :, 0], q2[:, :, 0]
     bd = max(0, (i - W) // BLOCK_SIZE * BLOCK_SIZE)
     if bd > st["bd"]:
         # the boundary moved by one block: its keys leave the window for the aggregates
@@ -147,7 +144,7 @@ def decode_step(query_states, key_states, value_states, position_ids, past_key_v
             st[name] = torch.roll(st[name], -BLOCK_SIZE, dims=2)
         st["bd"] = bd
     r = i - bd                                         # window row of the new key
-    st["win_k1"][:, :, r] = rot(key_states[:, :, 0], i)
+    st["win_k1"][:, :, r] = k1_new[:, :, 0]
     st["win_k3"][:, :, r] = key_states[:, :, 0]
     st["win_v"][:, :, r] = value_states[:, :, 0]
     far = bd > 0

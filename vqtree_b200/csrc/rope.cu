@@ -1,0 +1,148 @@
+// Rotary position embedding of a [B,H,L,D] tensor in the HF Llama half-split convention
+// (ops/attn_vq.py:55-64,296-299: x*cos + rotate_half(x)*sin with rotate_half(x) = cat(-x2, x1)),
+// to each row's own position and / or to one constant position (the ReRoPE query of
+// ops/attn_vq.py:402-407), both from one read of x.  HBM-bound: one thread moves 16 bytes of the
+// first half of a row and the matching 16 bytes of the second half; cos / sin come from fp32 tables
+// [n_pos, D/2] that stay in L2 (every head reads the same rows).  Products and the sum are rounded
+// separately (no fused multiply-add), which is what the element-wise PyTorch expression computes.
+#include "vq_common.cuh"
+
+namespace vq {
+
+template <typename T> struct RopeVec;
+template <> struct RopeVec<float> {
+    static constexpr int kN = 4;
+    __device__ static void load(const float *p, float (&f)[4])
+    {
+        const float4 v = *reinterpret_cast<const float4 *>(p);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+    __device__ static void store(float *p, const float (&f)[4]) { *reinterpret_cast<float4 *>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct RopeVec<__nv_bfloat16> {
+    static constexpr int kN = 8;
+    __device__ static void load(const __nv_bfloat16 *p, float (&f)[8])
+    {
+        const uint4 v = *reinterpret_cast<const uint4 *>(p);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ static void store(__nv_bfloat16 *p, const float (&f)[8])
+    {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// out = x * cos + rotate_half(x) * sin for the kN elements at d (first half) and d + D/2 (second half)
+template <int N>
+__device__ __forceinline__ void rope_rotate(const float (&x1)[N], const float (&x2)[N], const float *c, const float *s, float (&o1)[N], float (&o2)[N])
+{
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const float ci = __ldg(c + i), si = __ldg(s + i);
+        o1[i] = __fadd_rn(__fmul_rn(x1[i], ci), __fmul_rn(-x2[i], si));
+        o2[i] = __fadd_rn(__fmul_rn(x2[i], ci), __fmul_rn(x1[i], si));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rope_kernel(const T *__restrict__ x, int64_t x_sb, int64_t x_sh, int64_t x_sl,
+                                                   const int64_t *__restrict__ positions, const float *__restrict__ cos_tab,
+                                                   const float *__restrict__ sin_tab, int64_t n_pos, int64_t const_pos,
+                                                   T *__restrict__ out_pos, int64_t p_sb, int64_t p_sh, int64_t p_sl,
+                                                   T *__restrict__ out_const, int64_t c_sb, int64_t c_sh, int64_t c_sl, int H,
+                                                   int64_t L, int D, int64_t rows, int *__restrict__ status)
+{
+    constexpr int N = RopeVec<T>::kN;
+    const int half = D / 2, tpr = half / N;          // threads per row
+    const int64_t total = rows * tpr;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / tpr;
+        const int d = static_cast<int>(i % tpr) * N;
+        const int64_t l = r % L, bh = r / L;
+        const int h = static_cast<int>(bh % H);
+        const int64_t b = bh / H;
+        float x1[N], x2[N], o1[N], o2[N];
+        const T *xp = x + b * x_sb + h * x_sh + l * x_sl + d;
+        RopeVec<T>::load(xp, x1);
+        RopeVec<T>::load(xp + half, x2);
+        if (out_pos != nullptr) {
+            int64_t pos = positions ? positions[b * L + l] : l;
+            if (pos < 0 || pos >= n_pos) {               // outside the tables: report, rotate to the nearest row
+                if (status) atomicExch(status, 2);
+                pos = pos < 0 ? 0 : n_pos - 1;
+            }
+            rope_rotate<N>(x1, x2, cos_tab + pos * half + d, sin_tab + pos * half + d, o1, o2);
+            T *op = out_pos + b * p_sb + h * p_sh + l * p_sl + d;
+            RopeVec<T>::store(op, o1);
+            RopeVec<T>::store(op + half, o2);
+        }
+        if (out_const != nullptr) {
+            rope_rotate<N>(x1, x2, cos_tab + const_pos * half + d, sin_tab + const_pos * half + d, o1, o2);
+            T *op = out_const + b * c_sb + h * c_sh + l * c_sl + d;
+            RopeVec<T>::store(op, o1);
+            RopeVec<T>::store(op + half, o2);
+        }
+    }
+}
+
+}  // namespace vq
+
+extern "C" int vqattn_rope(const VqTensorDesc *x, const int64_t *positions, const float *cos_tab, const float *sin_tab,
+                           int64_t n_pos, int64_t const_pos, VqTensorDesc *out_pos, VqTensorDesc *out_const,
+                           int32_t *status_word, void *stream)
+{
+    using namespace vq;
+    int st;
+    if (out_pos != nullptr && out_pos->ptr == nullptr) out_pos = nullptr;
+    if (out_const != nullptr && out_const->ptr == nullptr) out_const = nullptr;
+    if ((st = check_basic(x, 4)) != VQ_OK) return st;
+    if (cos_tab == nullptr || sin_tab == nullptr || n_pos <= 0 || (out_pos == nullptr && out_const == nullptr)) return VQ_EINVAL_ARG;
+    if (out_const != nullptr && (const_pos < 0 || const_pos >= n_pos)) return VQ_EINVAL_ARG;
+    if (!is_act_dtype(x->dtype)) return VQ_EINVAL_DTYPE;
+    const int64_t B = x->shape[0], H = x->shape[1], L = x->shape[2], D = x->shape[3];
+    const int vec = x->dtype == VQ_F32 ? 4 : 8;
+    if (D % (2 * vec) != 0) return VQ_EINVAL_SHAPE;
+    const VqTensorDesc *ts[3] = {x, out_pos, out_const};
+    if ((st = check_device(ts, 3)) != VQ_OK) return st;
+    for (int i = 0; i < 3; ++i) {
+        const VqTensorDesc *t = ts[i];
+        if (t == nullptr) continue;
+        if (i > 0) {
+            if ((st = check_basic(t, 4)) != VQ_OK) return st;
+            if (t->dtype != x->dtype) return VQ_EINVAL_DTYPE;
+            if (t->shape[0] != B || t->shape[1] != H || t->shape[2] != L || t->shape[3] != D) return VQ_EINVAL_SHAPE;
+        }
+        // 16-byte vectors: aligned base and row strides
+        if (reinterpret_cast<uintptr_t>(t->ptr) % 16 || t->stride[0] % vec || t->stride[1] % vec || t->stride[2] % vec) return VQ_EINVAL_STRIDE;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t rows = B * H * L, total = rows * (D / 2 / vec);
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return VQ_EDEVICE;
+    const int64_t want = (total + 255) / 256;
+    const unsigned grid = static_cast<unsigned>(want < static_cast<int64_t>(sms) * 16 ? want : static_cast<int64_t>(sms) * 16);
+#define VQ_ROPE_LAUNCH(T)                                                                                                   \
+    rope_kernel<T><<<grid, 256, 0, s>>>(static_cast<const T *>(x->ptr), x->stride[0], x->stride[1], x->stride[2], positions,  \
+                                        cos_tab, sin_tab, n_pos, const_pos, out_pos ? static_cast<T *>(out_pos->ptr) : nullptr, \
+                                        out_pos ? out_pos->stride[0] : 0, out_pos ? out_pos->stride[1] : 0,                   \
+                                        out_pos ? out_pos->stride[2] : 0, out_const ? static_cast<T *>(out_const->ptr) : nullptr, \
+                                        out_const ? out_const->stride[0] : 0, out_const ? out_const->stride[1] : 0,           \
+                                        out_const ? out_const->stride[2] : 0, static_cast<int>(H), L, static_cast<int>(D), rows, \
+                                        status_word)
+    if (x->dtype == VQ_F32) VQ_ROPE_LAUNCH(float);
+    else VQ_ROPE_LAUNCH(__nv_bfloat16);
+#undef VQ_ROPE_LAUNCH
+    return launch_status();
+}

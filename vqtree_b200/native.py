@@ -33,7 +33,7 @@ EXPORTS = (
     "vqattn_version", "vqattn_status_string", "vqattn_assign_codes", "vqattn_build_aggregates",
     "vqattn_gather_aggregates", "vqattn_prefill", "vqattn_decode_workspace_bytes", "vqattn_decode",
     "vqattn_cache_advance", "vqattn_decode_static_capacity", "vqattn_decode_static",
-    "vqattn_assign_workspace_bytes", "vqattn_assign_codes_ws",
+    "vqattn_assign_workspace_bytes", "vqattn_assign_codes_ws", "vqattn_rope",
 )
 
 
@@ -97,6 +97,8 @@ def _load() -> ctypes.CDLL:
     lib.vqattn_decode_static_capacity.restype = ctypes.c_size_t
     lib.vqattn_cache_advance.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc),
                                          P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
+    lib.vqattn_rope.argtypes = [P(VqTensorDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p, ctypes.c_void_p]
     for name in EXPORTS:
         if name not in ("vqattn_status_string", "vqattn_decode_workspace_bytes", "vqattn_decode_static_capacity",
                         "vqattn_assign_workspace_bytes"):
