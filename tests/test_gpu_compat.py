@@ -64,16 +64,16 @@ def test_long_prefilling_entry_point(golden_dir):
     assert cache.get_seq_length(0) == L
 
 
-@pytest.mark.parametrize("dtype,L0,T,hq,hkv", [(torch.bfloat16, 600, 330, 8, 2), (torch.float32, 300, 140, 2, 2),
-                                               (torch.bfloat16, 100, 40, 4, 4)])
-def test_cache_prefill_then_decode_steps(dtype, L0, T, hq, hkv):
+@pytest.mark.parametrize("dtype,L0,T,hq,hkv,D", [(torch.bfloat16, 600, 330, 8, 2, 128), (torch.float32, 300, 140, 2, 2, 128),
+                                                 (torch.bfloat16, 100, 40, 4, 4, 128), (torch.bfloat16, 400, 150, 4, 2, 64)])
+def test_cache_prefill_then_decode_steps(dtype, L0, T, hq, hkv, D):
     """Prefill L0 tokens into the cache, then generate T more one at a time (the boundary moves at least
     twice in the long cases); every generated row must match the naive per-query attention over the whole sequence."""
     from oracle import vq_oracle as vo
     from vqtree_b200 import api
     from vqtree_b200.attn_vq import (AttentionMode, VectorQuantizedReRoPECache, decode_step,
                                      long_prefilling_sort_based_linear, rope_cos_sin, rotate_half)
-    B, D, M, K, W = 1, 128, 2, 128, 256
+    B, M, K, W = 1, 2, 128, 256
     L = L0 + T
     g = torch.Generator(device="cpu").manual_seed(77)
     q = torch.randn(B, hq, L, D, generator=g).cuda().to(dtype)
