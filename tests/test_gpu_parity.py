@@ -147,6 +147,9 @@ PREFILL_CASES = [
     (1, 4, 4, 1024, 128, 4, 256, 256, 1, False, torch.bfloat16),  # config 2 shape, scaled down
     (2, 4, 2, 1024, 128, 4, 512, 128, 3, True, torch.bfloat16),   # config 4 shape, scaled down, GQA
     (1, 2, 2, 717, 64, 2, 128, 128, 4, True, torch.bfloat16),     # ragged, D = 64
+    (1, 2, 2, 128, 128, 1, 128, 128, 11, True, torch.bfloat16),   # a single query tile
+    (1, 2, 1, 300, 128, 2, 128, 128, 12, True, torch.bfloat16),   # three tiles (odd: the last pair has one), ragged, GQA
+    (1, 2, 2, 1664, 128, 2, 128, 256, 13, False, torch.bfloat16), # thirteen tiles, far part from tile 3 on
 ]
 
 
