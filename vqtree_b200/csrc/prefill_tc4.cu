@@ -121,11 +121,14 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     __shared__ float s_lend[NB3][kBlock], s_mend[NB3][kBlock];  // partial denominators and the references they are scaled to
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m = p.ntiles - 1 - static_cast<int>(blockIdx.x);  // heavy tiles first
-    const int bh = blockIdx.y;
-    const int b = bh / p.Hq, hq = bh % p.Hq;
-    const int hk = hq / (p.Hq / p.Hkv);
-    const int u = b * p.Hkv + hk;
+    // grid.x = (query tile, query head inside its kv-head group), grid.y = (batch, kv head): the query heads
+    // that share a kv head run next to each other, so their K / V / value-sum tiles meet in L2
+    const int G = p.Hq / p.Hkv;
+    const int m = p.ntiles - 1 - static_cast<int>(blockIdx.x) / G;  // heavy tiles first
+    const int u = blockIdx.y;
+    const int b = u / p.Hkv, hk = u % p.Hkv;
+    const int hq = hk * G + static_cast<int>(blockIdx.x) % G;
+    const int bh = b * p.Hq + hq;
     const TcWork work(p, m);
     const int n = work.n_items;
 
@@ -425,7 +428,7 @@ static int launch_tc4(const VqPrefillArgs *a, cudaStream_t stream)
     if (st != VQ_OK) return st;
     auto kern = prefill_tc4_kernel<D>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
-    dim3 grid(static_cast<unsigned>(p.ntiles), static_cast<unsigned>(a->q1.shape[0] * a->q1.shape[1]));
+    dim3 grid(static_cast<unsigned>(p.ntiles * (p.Hq / p.Hkv)), static_cast<unsigned>(a->q1.shape[0] * p.Hkv));
     kern<<<grid, C::kThreads, C::kTotal, stream>>>(m.q1, m.q2, m.k1, m.k3, m.v, m.cb, m.vs, p);
     return launch_status();
 }
