@@ -62,6 +62,23 @@ def attention_bytes(w):
     return act + B * Hkv * nb * M * K * (D * 2 + 4) + Hkv * M * K * D * 2
 
 
+def stage_rooflines(w, stage_ms, peaks):
+    """The two kernels in front of the attention, against the roofs that bound them (informational)."""
+    B, Hkv, L, D, M, K, W = w["B"], w["Hkv"], w["L"], w["D"], w["M"], w["K"], w["W"]
+    nb = max(0, (L + 127) // 128 - W // 128 - 1)                       # per-block snapshots the attention reads
+    score_flops = 2.0 * B * Hkv * L * M * K * D                          # the fp32 chain that defines the codes
+    agg_bytes = B * Hkv * (nb * M * K * (D * 2 + 4) + L * (D * 2 + M))   # snapshots written, values and codes read
+    a_tf = score_flops / (stage_ms[0] * 1e-3) / 1e12
+    g_gbs = agg_bytes / (stage_ms[1] * 1e-3) / 1e9
+    return dict(
+        assign_codes=dict(kernel="assign_tc_kernel", bound="tensor", achieved=a_tf, peak=peaks["tensor"], unit="TFLOP/s",
+                          frac=a_tf / peaks["tensor"], note="algorithmic score FLOPs; the kernel is bound by the per-key "
+                          "scan / exact re-score / residual chain between its MMAs, not by the tensor pipe"),
+        build_aggregates=dict(kernel="build_aggregates_reg_kernel", bound="hbm", achieved=g_gbs, peak=peaks["hbm"], unit="GB/s",
+                              frac=g_gbs / peaks["hbm"]),
+    )
+
+
 def load_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -388,6 +405,7 @@ def main():
                       traffic_note="algorithmic bytes x 1.009, the DRAM read+write / algorithmic ratio ncu measured on the c2 "
                                    "capture (profiles/); traffic grows in proportion to the units processed",
                       flops_per_launch=flops),
+        stage_rooflines=stage_rooflines(w, stage_ms, peaks),
         cpu_baseline=cpu, e2e=e2e, gpu_launches=4 * args.steps, clocks=clocks, decode=decode, gather_ms=gather_ms,
     )
     print(json.dumps(line))
