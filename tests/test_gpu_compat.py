@@ -71,8 +71,8 @@ def test_cache_prefill_then_decode_steps(dtype, L0, T, hq, hkv, D):
     twice in the long cases); every generated row must match the naive per-query attention over the whole sequence."""
     from oracle import vq_oracle as vo
     from vqtree_b200 import api
-    from vqtree_b200.attn_vq import (AttentionMode, VectorQuantizedReRoPECache, decode_step,
-                                     long_prefilling_sort_based_linear, rope_cos_sin, rotate_half)
+    from vqtree_b200.attn_vq import (AttentionMode, VectorQuantizedReRoPECache, dispatch_attn_impl, rope_cos_sin,
+                                     rotate_half)
     B, M, K, W = 1, 2, 128, 256
     L = L0 + T
     g = torch.Generator(device="cpu").manual_seed(77)
@@ -82,10 +82,12 @@ def test_cache_prefill_then_decode_steps(dtype, L0, T, hq, hkv, D):
     cb = (torch.randn(hkv, M, K, D, generator=g) * 0.7).to(dtype).float().cuda()
     cache = VectorQuantizedReRoPECache(W, cb, False, attention_mode=AttentionMode.SORT_BASED_LINEAR)
     pos = torch.arange(L, device="cuda")[None].expand(B, -1)
-    got = [long_prefilling_sort_based_linear(q[:, :, :L0], k[:, :, :L0], v[:, :, :L0], pos[:, :L0], cache)]
+    got = [dispatch_attn_impl(q[:, :, :L0], k[:, :, :L0], v[:, :, :L0], pos[:, :L0], cache)]
     assert cache.get_seq_length(0) == L0
+    with pytest.raises(AssertionError):   # a second prefill is refused like the reference does (ops/attn_vq.py:192-196)
+        dispatch_attn_impl(q[:, :, :2], k[:, :, :2], v[:, :, :2], pos[:, :2], cache)
     for i in range(L0, L):
-        got.append(decode_step(q[:, :, i:i + 1], k[:, :, i:i + 1], v[:, :, i:i + 1], pos[:, i:i + 1], cache))
+        got.append(dispatch_attn_impl(q[:, :, i:i + 1], k[:, :, i:i + 1], v[:, :, i:i + 1], pos[:, i:i + 1], cache))
     assert cache.get_seq_length(0) == L and cache.seen_tokens == L
     got = torch.cat(got, dim=1).float().cpu().numpy()
 

@@ -156,3 +156,23 @@ def decode_step(query_states, key_states, value_states, position_ids, past_key_v
     if layer_idx == 0:
         past_key_value.seen_tokens += 1
     return out.reshape(bsz, 1, hq * d)
+
+
+def dispatch_attn_impl(query_states, key_states, value_states, position_ids, past_key_value: VectorQuantizedReRoPECache,
+                       layer_idx: int = 0, rope_base: float = 10000.0):
+    """The routing of ops/attn_vq.py:192-196,225-248 over this module's entry points.
+
+    An empty cache means prefilling (any length: without far keys the fused kernel computes the exact window
+    attention the reference hands to its short-sequence path); a filled cache accepts one token at a time.
+    Returns [B, q_len, Hq*D].
+    """
+    q_len = query_states.shape[2]
+    seen = past_key_value.get_seq_length(layer_idx)
+    assert seen == 0 or q_len == 1, "Only support prefilling or generation"  # ops/attn_vq.py:192-196
+    if seen == 0:
+        if past_key_value.attention_mode not in (AttentionMode.SORT_BASED_LINEAR, AttentionMode.SLOW_REFERNECE):
+            raise KeyError(f"Bad attention mode: {past_key_value.attention_mode}")  # ops/attn_vq.py:246
+        # SLOW_REFERNECE names the reference's per-query loop; its results are what the fused path is tested against
+        return long_prefilling_sort_based_linear(query_states, key_states, value_states, position_ids, past_key_value,
+                                                 layer_idx, rope_base)
+    return decode_step(query_states, key_states, value_states, position_ids, past_key_value, layer_idx, rope_base)
