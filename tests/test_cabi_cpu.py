@@ -57,6 +57,15 @@ def test_validation_rejects_bad_arguments_without_a_device():
     assert lib.vqattn_assign_codes(desc(k.transpose(2, 3)), desc(cb), None, desc(codes), None) == -3
     # host tensors are not on the current device (or there is no device): device error, not a crash
     assert lib.vqattn_assign_codes(desc(k), desc(cb), None, desc(codes), None) == -4
+    # RoPE: null input, missing tables, no output asked for, constant position outside the tables, odd head dim
+    x = torch.zeros(1, 2, 16, 64)
+    tab = torch.zeros(32, 32)
+    tp = ctypes.c_void_p(tab.data_ptr())
+    assert lib.vqattn_rope(None, None, tp, tp, 32, 0, desc(x), None, None, None) == -7
+    assert lib.vqattn_rope(desc(x), None, None, tp, 32, 0, desc(x), None, None, None) == -7
+    assert lib.vqattn_rope(desc(x), None, tp, tp, 32, 0, None, None, None, None) == -7
+    assert lib.vqattn_rope(desc(x), None, tp, tp, 32, 40, None, desc(x), None, None) == -7
+    assert lib.vqattn_rope(desc(torch.zeros(1, 2, 16, 36)), None, tp, tp, 32, 0, desc(torch.zeros(1, 2, 16, 36)), None, None, None) == -1
     assert lib.vqattn_prefill(None, None) == -7
     assert lib.vqattn_decode(None, None) == -7
     assert lib.vqattn_decode_workspace_bytes(16, 32, 32, 128) >= 16 * 32 * 130 * 4
