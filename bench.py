@@ -185,6 +185,112 @@ def cpu_baseline_run(w, seconds_budget=25.0):
                 seconds=per, flops=flops)
 
 
+# ------------------------------------------------------------------------------------ parity (checker, not timed)
+
+def parity_check(api, w, tensors, cb, codes, out):
+    """Sampled rows of the benchmarked launch against the naive CPU oracle, and the tensor-core codes against the
+    exact kernel on every key.  Runs after the timed region; the oracle is only the checker here."""
+    from oracle import sampled
+    q1, q2, k1, k3, v = tensors
+    B, Hkv, M, K, D, L, W = w["B"], w["Hkv"], w["M"], w["K"], w["D"], w["L"], w["W"]
+    exact = api.assign_codes(k3, cb, impl="simt")
+    codes_equal = bool(torch.equal(codes, exact))
+    del exact
+    units = [(0, 0), (B - 1, Hkv - 1)]
+    codes_equal = codes_equal and sampled.codes_equal_on_ranges(codes, k3, cb, units, [(0, 256), (L - 256, L)])
+    cb_seen = cb.reshape(Hkv, M * K, D).to(torch.bfloat16).float().reshape(Hkv, M, K, D)
+    err, rows = sampled.prefill_rows_max_err(out, q1, q2, k1, k3, v, cb_seen, codes, W, units,
+                                             sampled.row_ranges(L, W, seed=w["seed"]))
+    return dict(max_abs=err, rows_checked=rows, codes_equal=codes_equal, tolerance=2e-2, ok=bool(err <= 2e-2 and codes_equal),
+                oracle="oracle/vq_oracle.c naive per-query loop on sampled rows of 2 (batch, kv-head) units; codes: exact "
+                       "kernel on all keys + oracle on sampled key ranges")
+
+
+# ------------------------------------------------------------------------------------ one fixed job split over the ranks
+
+STRONG = dict(B=8, Hq=32, Hkv=8, D=128, L=131072, W=2048, M=8, K=256, decode_steps=256, seed=4)   # config 5
+
+
+def strong_job(dist, dev, rank, world, barrier, L=None):
+    """Config 5 as ONE job: its 64 (batch, kv-head) units are split over the ranks (64 / 32 / 16 / 8 per rank), each
+    rank prefills its units through the attention module's own entry point (rotations, codes, aggregates, fused
+    attention, cache state) and then generates 256 tokens from the cache.  No collective on the path; times are
+    device times, maximum over ranks.  Inputs are seeded per unit, so every N computes the same job."""
+    from vqtree_b200 import attn_vq, sharding
+    w = dict(STRONG)
+    if L:
+        w["L"] = L
+    B, Hq, Hkv, D, L, W, M, K = (w[k] for k in ("B", "Hq", "Hkv", "D", "L", "W", "M", "K"))
+    G = Hq // Hkv
+    lo, hi = sharding.unit_range(B * Hkv, world, rank)
+    torch.manual_seed(0)
+    cb_all = torch.empty(Hkv, M, K, D, device=dev)
+    for h in range(Hkv):
+        g = torch.Generator(device=dev).manual_seed(w["seed"] * 7919 + h)
+        cb_all[h] = torch.randn(M, K, D, generator=g, device=dev) * D ** -0.25
+    pieces = []
+    for (b0, b1, h0, h1) in sharding.unit_pieces(B, Hkv, lo, hi):
+        nb_, nh = b1 - b0, h1 - h0
+        q = torch.empty(nb_, L, nh * G, D, dtype=torch.bfloat16, device=dev)
+        k = torch.empty(nb_, L, nh, D, dtype=torch.bfloat16, device=dev)
+        v = torch.empty(nb_, L, nh, D, dtype=torch.bfloat16, device=dev)
+        for bi in range(nb_):
+            for hi_ in range(nh):
+                u = (b0 + bi) * Hkv + h0 + hi_
+                g = torch.Generator(device=dev).manual_seed(w["seed"] * 1000003 + u)
+                q[bi, :, hi_ * G:(hi_ + 1) * G] = torch.randn(L, G, D, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+                k[bi, :, hi_] = torch.randn(L, D, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+                v[bi, :, hi_] = torch.randn(L, D, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        steps = w["decode_steps"]
+        qd = torch.randn(nb_, steps, nh * G, D, device=dev).to(torch.bfloat16)
+        kd = torch.randn(nb_, steps, nh, D, device=dev).to(torch.bfloat16)
+        vd = torch.randn(nb_, steps, nh, D, device=dev).to(torch.bfloat16)
+        pieces.append(dict(q=q.transpose(1, 2), k=k.transpose(1, 2), v=v.transpose(1, 2), cb=cb_all[h0:h1].contiguous(),
+                           qd=qd.transpose(1, 2), kd=kd.transpose(1, 2), vd=vd.transpose(1, 2)))
+
+    def prefill():
+        caches = []
+        for p in pieces:
+            c = attn_vq.VectorQuantizedReRoPECache(W, p["cb"])
+            attn_vq.long_prefilling_sort_based_linear(p["q"], p["k"], p["v"], None, L, c)
+            caches.append(c)
+        return caches
+
+    def timed(fn):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r = fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, r
+
+    prefill()                                   # warm-up (allocator, tensor maps, rope tables)
+    torch.cuda.empty_cache()
+    ms_prefill, caches = min((timed(prefill) for _ in range(2)), key=lambda x: x[0])
+
+    def decode():
+        for t in range(w["decode_steps"]):
+            for p, c in zip(pieces, caches):
+                attn_vq.decode_step(p["qd"][:, :, t:t + 1], p["kd"][:, :, t:t + 1], p["vd"][:, :, t:t + 1], None, c)
+
+    ms_decode, _ = timed(decode)
+    flops = contraction_flops(**w)
+    from vqtree_b200 import api
+    api.check_status(dev)
+    return dict(workload=f"config 5 as one job: B{B} Hq{Hq} Hkv{Hkv} D{D} L{L} W{W} M{M}xK{K} bf16 ReRoPE, {B * Hkv} units split "
+                         f"{hi - lo} per rank, then {w['decode_steps']} decode steps through the cache",
+                units_per_rank=hi - lo, prefill_ms=ms_prefill, prefill_tflops=flops / (ms_prefill * 1e-3) / 1e12,
+                decode_ms_per_step=ms_decode / w["decode_steps"], decode_tok_s=B / (ms_decode / w["decode_steps"] * 1e-3),
+                decode_launches_per_token="2 per piece (rotate-and-append, attention) + 2 when a block leaves the window",
+                timing="CUDA events around the whole phase, max over ranks; no collective inside")
+
+
 # ------------------------------------------------------------------------------------ main
 
 def main():
@@ -200,6 +306,9 @@ def main():
     ap.add_argument("--decode-codebook", default="bf16", choices=["bf16", "f32"],
                     help="dtype of the codebook the decode kernel scores with (bf16: the copy the prefill uses too)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-strong", action="store_true", help="skip the fixed config-5 job split over the ranks")
+    ap.add_argument("--strong-len", type=int, default=0, help="context length of the split job (default: config 5's 131072)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -252,6 +361,8 @@ def main():
     nb = api.far_blocks(L, W)
     cb_act = cb.reshape(Hkv, M * K, D).to(torch.bfloat16)
 
+    last = {}
+
     def step(events=None):
         rec = (lambda i: events[i].record()) if events else (lambda i: None)
         rec(0)
@@ -261,6 +372,7 @@ def main():
         rec(2)
         out = api.prefill_from_aggregates(q1, q2, k1, k3, v, cb_act, cnt, vsum, W, impl=args.attn_impl)
         rec(3)
+        last["codes"] = codes
         return out
 
     for _ in range(args.warmup):
@@ -292,6 +404,12 @@ def main():
     value = world * flops / (ms_per_step * 1e-3) / 1e12
     peaks = load_peaks()
     attn_tflops = flops / (stage_ms[2] * 1e-3) / 1e12
+
+    # ---- parity of the benchmarked launch (rank 0, outside the timed region) ----
+    parity = None
+    if rank == 0 and not args.no_parity:
+        parity = parity_check(api, w, (q1, q2, k1, k3, v), cb, last["codes"], out)
+    last.clear()
 
     # ---- final output gather (outside the timed hot path, reported on its own) ----
     gather_ms = None
@@ -332,7 +450,10 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             el = float(t.item())
         e2e = dict(value=world * flops / (el / n_e2e) / 1e12, unit="TFLOP/s", h2d_bytes_per_step=h2d,
-                   d2h_bytes_per_step=d2h, ms_per_step=el / n_e2e * 1e3, steps=n_e2e)
+                   d2h_bytes_per_step=d2h, ms_per_step=el / n_e2e * 1e3, steps=n_e2e,
+                   h2d_gbs_per_rank=h2d / (el / n_e2e) / 1e9,
+                   note="bounded by the host link: every rank streams its inputs from pinned host memory; ranks of one "
+                        "node share the host's memory and PCIe fabric")
         del host, hq1, hq2, hk1, hk3, hv
     torch.cuda.empty_cache()
 
@@ -384,6 +505,13 @@ def main():
                       config=f"B{d['B']} H{d['Hq']} D{d['D']} ctx{d['ctx']} W{d['W']} M{d['M']}xK{d['K']} bf16, {args.decode_codebook} codebooks")
         del bufs
 
+    # ---- one fixed job (config 5) split over the ranks: strong scaling, prefill + decode through the cache ----
+    strong = None
+    if not args.no_strong:
+        torch.cuda.empty_cache()
+        strong = strong_job(dist, dev, rank, world, barrier, args.strong_len)
+        torch.cuda.empty_cache()
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -407,6 +535,7 @@ def main():
                       flops_per_launch=flops),
         stage_rooflines=stage_rooflines(w, stage_ms, peaks),
         cpu_baseline=cpu, e2e=e2e, gpu_launches=4 * args.steps, clocks=clocks, decode=decode, gather_ms=gather_ms,
+        parity=parity, strong=strong,
     )
     print(json.dumps(line))
     if dist is not None:

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define VQATTN_VERSION 100
+#define VQATTN_VERSION 200
 #define VQATTN_BLOCK 128   /* key/query block size; ops/attn_vq.py:23 BLOCK_SIZE ("MUST MATCH KERNEL") */
 #define VQATTN_MAX_DIMS 5
 
@@ -30,7 +30,8 @@ typedef enum VqDtype {
     VQ_U8 = 2,
     VQ_U16 = 3,
     VQ_I32 = 4,
-    VQ_I64 = 5
+    VQ_I64 = 5,
+    VQ_F16 = 6   /* IEEE half: the dtype of the reference's own self-test (ops/attn_vq.py:534-556) */
 } VqDtype;
 
 typedef enum VqStatus {
@@ -56,17 +57,38 @@ typedef struct VqTensorDesc {
     int32_t device;
 } VqTensorDesc;
 
-/* Which prefill kernel to run; AUTO picks the pipelined tensor-core kernel for bf16 and the fp32
- * kernel for f32.  Earlier tensor-core designs stay selectable: TENSOR_FOURWAY (four softmax threads
- * per query row), TENSOR_TWOSTREAM (two softmax states merged at the end), TENSOR_SERIAL (not
- * pipelined); all compute the same arithmetic up to rounding. */
-typedef enum VqPrefillImpl {
-    VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2, VQ_IMPL_TENSOR_SERIAL = 3, VQ_IMPL_TENSOR_TWOSTREAM = 4,
-    VQ_IMPL_TENSOR_FOURWAY = 5, VQ_IMPL_TENSOR_PAIR = 6
-} VqPrefillImpl;
+/* Which prefill kernel to run; AUTO picks the tensor-core kernel for 16-bit activations and the fp32
+ * kernel for f32 (SIMT also accepts 16-bit activations: an on-device cross-check of the same arithmetic). */
+typedef enum VqPrefillImpl { VQ_IMPL_AUTO = 0, VQ_IMPL_SIMT = 1, VQ_IMPL_TENSOR = 2 } VqPrefillImpl;
+
+/*
+ * Status word: kernels that can detect a problem on the device (an expired bounded wait, an input value
+ * they must not use as an index) take a pointer to a device int32 (`status_word`, may be NULL).  It stays 0
+ * when all is well; a kernel that finds a problem stores one of the values below, leaves the offending
+ * element out and finishes normally.  The host reads the word when it wants to know (one copy per step is
+ * enough), maps it with vqattn_status_from_word and resets it to 0.  Replaces the reference's Python
+ * asserts, which cannot see device-side values (ops/attn_vq.py:192-198).
+ */
+#define VQ_WORD_TIMEOUT 1       /* a bounded device-side wait expired            -> VQ_ETIMEOUT   */
+#define VQ_WORD_BAD_POSITION 2  /* vqattn_rope: position outside the cos/sin tables -> VQ_EINVAL_ARG */
+#define VQ_WORD_BAD_CODE 3      /* vqattn_cache_advance: code outside [0, K)       -> VQ_EINVAL_ARG */
 
 int vqattn_version(void);
 const char *vqattn_status_string(int status);
+int vqattn_status_from_word(int32_t word);
+
+/*
+ * Every wait inside a kernel (on a barrier another warp, the tensor pipe or a tile copy completes) gives up
+ * after a number of SM clock cycles, raises VQ_WORD_TIMEOUT in the status word and lets the kernel end.
+ * vqattn_set_wait_limit_cycles sets that number for launches made after it, process-wide (cycles <= 0:
+ * the default, four thousand million cycles, about two seconds); it returns the previous value.
+ * vqattn_wait_selftest launches one warp that waits on a barrier nothing arrives at, so that a host can
+ * check its handling of the time-out path without any kernel misbehaving: with a limit of a few million
+ * cycles it ends within milliseconds and leaves VQ_WORD_TIMEOUT in *status_word.
+ * No counterpart in the reference (its Triton kernels have no device-side waits).
+ */
+int64_t vqattn_set_wait_limit_cycles(int64_t cycles);
+int vqattn_wait_selftest(int32_t *status_word, void *stream);
 
 /*
  * Key -> code assignment.  Replaces ops/mini_vq.py:4-18 multi_head_single_quantize (scores by
@@ -74,7 +96,7 @@ const char *vqattn_status_string(int status);
  * assignment: r0 = k; c_m = argmax_c(r_m.C_m[c] + bias_m[c]); r_{m+1} = r_m - C_m[c_m].
  * Arithmetic is fp32 with a fixed order (one fused-multiply-add chain over d = 0..D-1), so the
  * codes are reproducible bit for bit.
- *   k         [B,Hkv,L,D]  f32 | bf16      (D in {64,128})
+ *   k         [B,Hkv,L,D]  f32 | bf16 | f16  (D in {64,128})
  *   codebooks [Hkv,M,K,D]  f32             (K % 64 == 0, K <= 65536)
  *   bias      NULL or [Hkv,M,K] f32
  *   codes     [B,Hkv,L,M]  u8 (K <= 256) | u16 | i32 | i64
@@ -88,7 +110,7 @@ int vqattn_assign_codes(const VqTensorDesc *k, const VqTensorDesc *codebooks, co
  * codebook, then an exact fp32 re-score of every key whose two best approximate
  * scores are closer than the proven error bound.  Needs `workspace` (256-byte aligned) of
  * vqattn_assign_workspace_bytes(B, Hkv, L, M, K, D) bytes for the split codebook.  Inputs outside the
- * tensor-core path (fp32 keys, larger K or M) are forwarded to vqattn_assign_codes.
+ * tensor-core path (fp32 or f16 keys, larger K or M) are forwarded to vqattn_assign_codes.
  * `status_word`: device int32 or NULL, raised if a bounded device-side wait expires.
  */
 size_t vqattn_assign_workspace_bytes(int64_t B, int64_t Hkv, int64_t L, int64_t M, int64_t K, int64_t D);
@@ -100,9 +122,10 @@ int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc *codebooks,
  * Per-block aggregates.  Replaces the host preparation at ops/attn_vq.py:352-384,411-417 (one-hot
  * cumsum, argsort, gather, prefix sums): block n of the outputs describes the keys [0,128(n+1)):
  *   cnt  [B,Hkv,NB,M*K]    f32  number of those keys whose code in codebook m is c  (row m*K+c)
- *   vsum [B,Hkv,NB,M*K,D]  f32 | bf16  sum of their value rows, accumulated in fp32 in position order
+ *   vsum [B,Hkv,NB,M*K,D]  f32 | bf16 | f16  sum of their value rows, accumulated in fp32 in position order
  * from
- *   codes [B,Hkv,L,M] u8|u16|i32|i64,  v [B,Hkv,L,D] f32|bf16,   NB <= L/128.
+ *   codes [B,Hkv,L,M] u8|u16|i32|i64,  v [B,Hkv,L,D] f32|bf16|f16,   NB <= L/128.
+ * (f16 sums saturate at 65504 like the reference's cast of its prefix sums, ops/attn_vq.py:383.)
  */
 int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
                             VqTensorDesc *vsum, void *stream);
@@ -130,9 +153,9 @@ int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensorDesc *vi, c
  *   keys j <  boundary                   through the aggregates of block boundary/128 - 1:
  *       score q2_i.codebook[r] for every row r with cnt[r] > 0, numerator weight vsum[r],
  *       denominator weight cnt[r]                         (ops/triton_fused_vq_attn.py:38-68)
- * All of q1,q2,k1,k3,v,codebook,vsum,out share one dtype (f32 or bf16); math is fp32.
- * vsum rows of codes with cnt == 0 must be zero (vqattn_build_aggregates and vqattn_gather_aggregates
- * with cnt produce them so): the tensor-core kernel lets such codes take part with weight zero.
+ * All of q1,q2,k1,k3,v,codebook,vsum,out share one dtype (f32, bf16 or f16); math is fp32.
+ * Codes with cnt == 0 are excluded from the softmax like the reference does (:44-46); their vsum rows
+ * should still be zero (vqattn_build_aggregates and vqattn_gather_aggregates with cnt produce them so).
  *   q1,q2,out [B,Hq,L,D]; k1,k3,v [B,Hkv,L,D]; codebook [Hkv,MK,D]; cnt [B,Hkv,NB,MK] f32;
  *   vsum [B,Hkv,NB,MK,D]; lse2 NULL or [B,Hq,L] f32 (base-2 log-sum-exp of the scaled scores).
  * Constraints: D in {64,128}; window % 128 == 0; MK % 128 == 0; Hq % Hkv == 0;
@@ -199,7 +222,7 @@ size_t vqattn_decode_static_capacity(void);
 int vqattn_decode_static(const VqDecodeArgs *args, void *stream);
 
 /*
- * Rotary position embedding of x [B,H,L,D] (f32|bf16) in the HF Llama half-split convention the
+ * Rotary position embedding of x [B,H,L,D] (f32|bf16|f16) in the HF Llama half-split convention the
  * reference applies before its kernels (ops/attn_vq.py:55-64,296-299: x*cos + rotate_half(x)*sin):
  *   out_pos   (optional) [B,H,L,D]: every row rotated to its own position, positions[b*L + l]
  *             (int64, device) or l when positions is NULL          (ops/attn_vq.py:402-404)
@@ -207,11 +230,33 @@ int vqattn_decode_static(const VqDecodeArgs *args, void *stream);
  *             window + 1                                             (ops/attn_vq.py:405-407)
  * cos_tab, sin_tab: device fp32 tables [n_pos, D/2] (angle = pos * base^(-2i/D)).  Products and sum
  * are rounded separately in fp32, then once to the output dtype.  A position outside [0, n_pos)
- * sets *status_word to 2 (status_word may be NULL) and uses the nearest table row.
+ * sets *status_word to VQ_WORD_BAD_POSITION (status_word may be NULL) and uses the nearest table row.
  * Constraints: D % 16 == 0 (bf16) or D % 8 == 0 (f32); 16-byte aligned rows.
  */
 int vqattn_rope(const VqTensorDesc *x, const int64_t *positions, const float *cos_tab, const float *sin_tab, int64_t n_pos,
                 int64_t const_pos, VqTensorDesc *out_pos, VqTensorDesc *out_const, int32_t *status_word, void *stream);
+
+/*
+ * The rotations of one prefill in a single launch (ops/attn_vq.py:402-407): q [B,Hq,L,D] -> q1 (each row at
+ * its position) and q2 (every row at const_pos = window + 1; NULL or ptr NULL to skip), k [B,Hkv,L,D] -> k1.
+ * Inputs and outputs may be strided views ([B,L,H,D] storage viewed as [B,H,L,D] included); arguments as in
+ * vqattn_rope.
+ */
+int vqattn_rope_qk(const VqTensorDesc *q, const VqTensorDesc *k, const int64_t *positions, const float *cos_tab,
+                   const float *sin_tab, int64_t n_pos, int64_t const_pos, VqTensorDesc *q1, VqTensorDesc *q2,
+                   VqTensorDesc *k1, int32_t *status_word, void *stream);
+
+/*
+ * The per-token bookkeeping of a decode step in one launch: rotates the new query (q [B,Hq,1,D] -> q1, q2
+ * [B,Hq,1,D]) and writes the new key and value into row `row` of the window caches: k1_win gets the key
+ * rotated to its position, k3_win the key as it is, v_win the value (all [B,Hkv,Nwin,D]).  The position of
+ * batch b is positions[b] (device int64) or `pos` when positions is NULL.  Stands in for the cache update the
+ * reference left unfinished (ops/attn_vq.py:128-165) and its per-step rotations (:402-407).
+ */
+int vqattn_decode_append(const VqTensorDesc *q, const VqTensorDesc *k, const VqTensorDesc *v, const int64_t *positions,
+                         int64_t pos, const float *cos_tab, const float *sin_tab, int64_t n_pos, int64_t const_pos,
+                         VqTensorDesc *q1, VqTensorDesc *q2, VqTensorDesc *k1_win, VqTensorDesc *k3_win,
+                         VqTensorDesc *v_win, int64_t row, int32_t *status_word, void *stream);
 
 /*
  * Cache advance: folds `n_new` (a multiple of 128 is not required) keys that cross the boundary
@@ -219,10 +264,13 @@ int vqattn_rope(const VqTensorDesc *x, const int64_t *positions, const float *co
  * ops/attn_vq.py:128-165 VectorQuantizedReRoPECache.update.
  *   codes [B,Hkv,n_new,M] ; v_new [B,Hkv,n_new,D] ;
  *   cnt [B,Hkv,MK] f32 (in/out) ; vsum_f32 [B,Hkv,MK,D] f32 master (in/out) ;
- *   vsum_act NULL or [B,Hkv,MK,D] bf16 shadow refreshed for the touched rows.
+ *   vsum_act NULL or [B,Hkv,MK,D] 16-bit shadow (the dtype of v_new; bf16 for f32 values) refreshed for
+ *   the touched rows.
+ * A code outside [0,K) (a foreign quantizer, 8-bit codes with K < 256) is skipped and reported as
+ * VQ_WORD_BAD_CODE in *status_word (may be NULL); nothing outside the code's own rows is written.
  */
 int vqattn_cache_advance(const VqTensorDesc *codes, const VqTensorDesc *v_new, int32_t K, VqTensorDesc *cnt,
-                         VqTensorDesc *vsum_f32, VqTensorDesc *vsum_act_or_null, void *stream);
+                         VqTensorDesc *vsum_f32, VqTensorDesc *vsum_act_or_null, int32_t *status_word, void *stream);
 
 #ifdef __cplusplus
 }

@@ -1,8 +1,8 @@
 """Generate the golden vectors in this folder by running the reference's own code.
 
-Run once, in a container that has the reference checkout (default ``/root/reference``):
+Run once, in a container that has the reference checkout:
 
-    TRITON_INTERPRET=1 python tests/golden/gen_golden.py [--ref /root/reference]
+    TRITON_INTERPRET=1 python tests/golden/gen_golden.py --ref <reference checkout>
 
 Nothing from the reference is copied: its files are loaded (or, for two methods of a class
 that cannot be imported with the installed transformers, parsed and executed) where they lie,
@@ -173,7 +173,7 @@ def interpreted_fused_kernel(mods, captured):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of the reference checkout")
     args = ap.parse_args()
     ref = Path(args.ref)
     mods = load_ref_modules(ref)

@@ -154,7 +154,7 @@ PREFILL_CASES = [
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,L,D,M,K,W,seed,rerope,dtype", PREFILL_CASES)
-@pytest.mark.parametrize("impl", ["simt", "tensor", "tensor_fourway", "tensor_pair", "tensor_twostream", "tensor_serial"])
+@pytest.mark.parametrize("impl", ["simt", "tensor"])
 def test_prefill_matches_naive_oracle(api, impl, B, Hq, Hkv, L, D, M, K, W, seed, rerope, dtype):
     if impl.startswith("tensor") and dtype != torch.bfloat16:
         pytest.skip("the tensor-core kernel computes in bf16")
@@ -382,6 +382,205 @@ def test_rope_reports_positions_outside_the_tables():
     x = torch.randn(1, 1, 16, 64, device="cuda")
     pos = torch.arange(16, device="cuda")[None] + 10**6   # far beyond any table built so far (tables are cached and only grow)
     api.rope(x, pos, n_pos=32)
-    with pytest.raises(native.VqError):
+    with pytest.raises(native.VqError) as e:
         api.check_status()
+    assert e.value.status == -7      # an invalid argument, not a time-out
     api.check_status()   # the word was cleared
+
+
+def test_rope_qk_and_decode_append_match_the_rope_kernel():
+    """The fused launches (q and k of a prefill; the per-token rotate-and-append of a decode) produce bit for bit
+    what the single-tensor kernel produces, on [B,L,H,D] storage viewed as [B,H,L,D]."""
+    from vqtree_b200 import api
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        B, L, Hq, Hkv, D, W = 2, 77, 4, 2, 128, 128
+        g = torch.Generator(device="cpu").manual_seed(3)
+        q = torch.randn(B, L, Hq, D, generator=g).cuda().to(dtype).transpose(1, 2)
+        k = torch.randn(B, L, Hkv, D, generator=g).cuda().to(dtype).transpose(1, 2)
+        v = torch.randn(B, L, Hkv, D, generator=g).cuda().to(dtype).transpose(1, 2)
+        pos = (torch.arange(L) + 5)[None].expand(B, L).cuda()
+        q1, q2, k1 = api.rope_qk(q, k, pos, const_pos=W + 1, like_input=True)
+        assert q1.stride() == q.stride() and k1.stride() == k.stride()
+        wq1, wq2 = api.rope(q.contiguous(), pos, const_pos=W + 1)
+        wk1, _ = api.rope(k.contiguous(), pos)
+        assert torch.equal(q1, wq1) and torch.equal(q2, wq2) and torch.equal(k1, wk1)
+        # one token into row 9 of window caches
+        wins = [torch.zeros(B, Hkv, 32, D, dtype=dtype, device="cuda") for _ in range(3)]
+        oq1, oq2 = torch.empty(B, Hq, 1, D, dtype=dtype, device="cuda"), torch.empty(B, Hq, 1, D, dtype=dtype, device="cuda")
+        t = 40
+        api.decode_append(q[:, :, t:t + 1], k[:, :, t:t + 1], v[:, :, t:t + 1], t + 5, W + 1, oq1, oq2, *wins, row=9)
+        assert torch.equal(oq1[:, :, 0], wq1[:, :, t]) and torch.equal(oq2[:, :, 0], wq2[:, :, t])
+        assert torch.equal(wins[0][:, :, 9], wk1[:, :, t]) and torch.equal(wins[1][:, :, 9], k[:, :, t]) and torch.equal(wins[2][:, :, 9], v[:, :, t])
+        assert float(wins[0][:, :, :9].abs().max()) == 0 and float(wins[2][:, :, 10:].abs().max()) == 0
+        # positions from a device tensor instead of the scalar
+        api.decode_append(q[:, :, t:t + 1], k[:, :, t:t + 1], v[:, :, t:t + 1], 0, W + 1, oq1, oq2, *wins, row=10,
+                          positions=pos[:, t].contiguous(), n_pos=L + 6)
+        assert torch.equal(wins[0][:, :, 10], wk1[:, :, t])
+    api.check_status()
+
+
+# ----------------------------------------------------------------------------- fp16 (the reference's self-test dtype)
+
+@pytest.mark.parametrize("impl", ["simt", "tensor"])
+@pytest.mark.parametrize("B,Hq,Hkv,L,D,M,K,W,seed,rerope", [
+    (1, 2, 2, 511, 64, 1, 128, 256, 0, True),      # the reference's self-test shape (ops/attn_vq.py:534-556)
+    (1, 4, 2, 1024, 128, 2, 256, 256, 5, True),    # GQA, D = 128, two codebooks
+    (2, 2, 2, 700, 128, 4, 128, 128, 6, False),    # ragged, plain RoPE
+])
+def test_prefill_fp16_matches_naive_oracle(api, impl, B, Hq, Hkv, L, D, M, K, W, seed, rerope):
+    case = make_case(B, Hq, Hkv, L, D, M, K, W, seed, rerope, torch.float16)
+    want, codes = oracle_prefill(case)
+    got, st = _run_prefill(api, case, impl)
+    np.testing.assert_array_equal(st["codes"].cpu().to(torch.int64).numpy(), codes)
+    assert st["vsum"] is None or st["vsum"].dtype == torch.float16
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 2e-2
+
+
+def test_decode_fp16_matches_oracle(api):
+    B, Hq, Hkv, D, M, K, W, L = 2, 4, 2, 128, 2, 128, 128, 640
+    case = make_case(B, Hq, Hkv, L, D, M, K, W, 23, True, torch.float16)
+    f = lambda t: t.float().numpy()
+    cb = case["cb"].numpy()
+    codes = vo.assign_codes(f(case["k3"]), cb)
+    cnt, vsum = vo.build_aggregates(codes, f(case["v"]), K)
+    cb16 = f(case["cb"].half())
+    full = vo.attn_naive(f(case["q1"]), f(case["q2"]), f(case["k1"]), f(case["k3"]), f(case["v"]), cb16, codes, W)
+    for n in (100, 300, 640):
+        i = n - 1
+        bd = max(0, (i - W) // 128 * 128)
+        far = bd > 0
+        blk = bd // 128 - 1 if far else 0
+        win = lambda t: dev(t[:, :, bd:n].contiguous())
+        got = api.vq_attention_decode(dev(case["q1"][:, :, i].contiguous()), dev(case["q2"][:, :, i].contiguous()),
+                                      win(case["k1"]), win(case["k3"]), win(case["v"]),
+                                      dev(case["cb"].reshape(Hkv, M * K, D).half()) if far else None,
+                                      dev(torch.from_numpy(cnt[:, :, blk].reshape(B, Hkv, M * K).astype(np.float32))) if far else None,
+                                      dev(torch.from_numpy(vsum[:, :, blk].reshape(B, Hkv, M * K, D)).half()) if far else None,
+                                      n_valid=n - bd, n_bd=max(0, i - W) - bd)
+        np.testing.assert_allclose(got.float().cpu().numpy(), full[:, :, i], atol=2e-2, rtol=0)
+
+
+# ----------------------------------------------------------------------------- edges
+
+def test_unused_codeword_with_a_dominating_score_is_excluded(api):
+    """A codeword no key was assigned to, whose score towers over every real one: the reference masks it before
+    its maximum (ops/triton_fused_vq_attn.py:44-46).  Letting it set the maximum would push every real weight
+    below the exponent range and the row would come out as zeros.  The attention's copy of the codebook gets
+    such a row planted (the codes and aggregates are those of the original codebook, so the row stays unused and
+    the naive oracle, which only looks up the codewords of assigned codes, is unaffected)."""
+    B, Hq, Hkv, L, D, M, K, W = 1, 2, 2, 768, 128, 1, 128, 128
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        case = make_case(B, Hq, Hkv, L, D, M, K, W, 41, True, dtype)
+        want, _ = oracle_prefill(case)
+        d = {k: dev(t) if isinstance(t, torch.Tensor) else t for k, t in case.items()}
+        _, st = api.vq_attention_prefill(d["q1"], d["q2"], d["k1"], d["k3"], d["v"], d["cb"], W, return_state=True)
+        cb_act = d["cb"].reshape(Hkv, M * K, D).to(dtype).clone()
+        for h in range(Hkv):
+            free = (st["cnt"][0, h].sum(0) == 0).nonzero().flatten()      # unused in every block
+            assert len(free) > 0
+            qdir = d["q2"][0, h * (Hq // Hkv), 300:].float().mean(0)
+            cb_act[h, int(free[0])] = (qdir / qdir.norm() * 2000.0).to(dtype)   # scores of hundreds of log2 units
+        for impl in (("simt", "tensor") if dtype != torch.float32 else ("simt",)):
+            got = api.prefill_from_aggregates(d["q1"], d["q2"], d["k1"], d["k3"], d["v"], cb_act, st["cnt"], st["vsum"], W,
+                                              impl=impl).float().cpu().numpy()
+            assert np.isfinite(got).all()
+            assert np.abs(got[:, :, 300:]).max() > 1e-3                # not silently zero
+            assert np.abs(got - want).max() <= (1e-4 if dtype == torch.float32 else 2e-2), (dtype, impl)
+    api.check_status()
+
+
+def test_bounded_wait_times_out_and_the_library_keeps_working(api):
+    """A wait nobody satisfies gives up after the configured number of cycles, the status word says so, and the
+    next call works: nothing spins for ever, nothing traps."""
+    from vqtree_b200 import native
+    old = api.set_wait_limit(2_000_000)            # about one millisecond of SM clock
+    try:
+        api.check_status()
+        api.wait_selftest()
+        torch.cuda.synchronize()
+        with pytest.raises(native.VqError) as e:
+            api.check_status()
+        assert e.value.status == -6                # VQ_ETIMEOUT
+        api.check_status()                         # the word was cleared
+    finally:
+        assert api.set_wait_limit(old) == 2_000_000
+    # a real kernel right after, with the short limit restored to the default
+    case = make_case(1, 2, 2, 512, 128, 1, 128, 128, 2, True, torch.bfloat16)
+    want, _ = oracle_prefill(case)
+    got, _ = _run_prefill(api, case, "tensor")
+    assert np.abs(got - want).max() <= 2e-2
+
+
+def test_cache_advance_skips_codes_outside_the_codebook(api):
+    """8-bit codes with K = 128: a code of 200 must not touch any row (canaries either side of the buffers stay
+    intact) and is reported through the status word as an invalid argument."""
+    from vqtree_b200 import native
+    B, Hkv, D, M, K, n = 1, 2, 64, 2, 128, 96
+    g = torch.Generator().manual_seed(8)
+    codes = torch.randint(0, K, (B, Hkv, n, M), generator=g).to(torch.uint8)
+    bad = codes.clone()
+    bad[0, 1, 17, 1] = 200
+    bad[0, 0, 50, 0] = 255
+    v = torch.randn(B, Hkv, n, D, generator=g).bfloat16()
+    pad = 4096
+    def guarded(shape, dtype):
+        n_el = int(np.prod(shape))
+        buf = torch.full((n_el + 2 * pad,), 7.0, dtype=dtype, device="cuda")
+        view = buf[pad: pad + n_el].view(shape)
+        view.zero_()
+        return buf, view
+    bufs = [guarded((B, Hkv, M * K), torch.float32), guarded((B, Hkv, M * K, D), torch.float32), guarded((B, Hkv, M * K, D), torch.bfloat16)]
+    api.check_status()
+    api.cache_advance(dev(bad), dev(v), K, bufs[0][1], bufs[1][1], bufs[2][1])
+    torch.cuda.synchronize()
+    with pytest.raises(native.VqError) as e:
+        api.check_status()
+    assert e.value.status == -7
+    for buf, view in bufs:
+        assert bool((buf[:pad] == 7).all()) and bool((buf[-pad:] == 7).all())
+    # every valid key was still folded in: equal to advancing with the two bad keys removed
+    good_cnt, good_vs = torch.zeros_like(bufs[0][1]), torch.zeros_like(bufs[1][1])
+    keep = torch.ones(B, Hkv, n, M, dtype=torch.bool)
+    keep[0, 1, 17, 1] = False
+    keep[0, 0, 50, 0] = False
+    vf = v.float()
+    for h in range(Hkv):
+        for j in range(n):
+            for m in range(M):
+                if keep[0, h, j, m]:
+                    r = m * K + int(codes[0, h, j, m])
+                    good_cnt[0, h, r] += 1
+                    good_vs[0, h, r] += vf[0, h, j].cuda()
+    assert torch.equal(bufs[0][1], good_cnt)
+    np.testing.assert_allclose(bufs[1][1].cpu().numpy(), good_vs.cpu().numpy(), atol=1e-5, rtol=0)
+    api.check_status()
+
+
+def test_strided_inputs_and_output_in_place(api):
+    """[B,L,H,D] storage viewed as [B,H,L,D] for every activation and for the output: no copies needed, same
+    result as the contiguous call (the layout the attention module works in, ops/attn_vq.py:207-209,442)."""
+    case = make_case(2, 4, 2, 900, 128, 2, 128, 256, 51, True, torch.bfloat16)
+    d = {k: dev(t) for k, t in case.items() if isinstance(t, torch.Tensor)}
+    want = api.vq_attention_prefill(d["q1"], d["q2"], d["k1"], d["k3"], d["v"], d["cb"], 256)
+    blhd = lambda t: t.transpose(1, 2).contiguous().transpose(1, 2)
+    out = torch.empty(2, 900, 4, 128, dtype=torch.bfloat16, device="cuda")
+    got = api.vq_attention_prefill(blhd(d["q1"]), blhd(d["q2"]), blhd(d["k1"]), blhd(d["k3"]), blhd(d["v"]), d["cb"], 256,
+                                   out=out.transpose(1, 2))
+    assert got.data_ptr() == out.data_ptr()
+    assert torch.equal(out.transpose(1, 2), want)
+    api.check_status()
+
+
+def test_prefill_sharded_equals_unsharded(api):
+    """Two ranks' worth of (batch, kv-head) units, run one after the other in this process: concatenated they are
+    the unsharded result bit for bit (uneven split: 3 batches x 2 kv heads over 4 ranks cuts inside a batch row)."""
+    from vqtree_b200 import sharding
+    case = make_case(3, 4, 2, 640, 128, 2, 128, 128, 61, True, torch.bfloat16)
+    d = {k: dev(t) for k, t in case.items() if isinstance(t, torch.Tensor)}
+    want = api.vq_attention_prefill(d["q1"], d["q2"], d["k1"], d["k3"], d["v"], d["cb"], 128)
+    for world in (2, 4):
+        parts = [sharding.prefill_sharded(d["q1"], d["q2"], d["k1"], d["k3"], d["v"], d["cb"], 128, world, r) for r in range(world)]
+        got = torch.cat(parts, 0).view(3, 2, 2, 640, 128).reshape(3, 4, 640, 128)
+        assert torch.equal(got, want)
+    api.check_status()

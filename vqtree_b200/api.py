@@ -16,9 +16,7 @@ import torch
 from . import native
 from .native import BLOCK, VqDecodeArgs, VqPrefillArgs, check, desc, lib, stream_ptr
 
-_IMPL = {"auto": native.IMPL_AUTO, "simt": native.IMPL_SIMT, "tensor": native.IMPL_TENSOR,
-         "tensor_serial": native.IMPL_TENSOR_SERIAL, "tensor_twostream": native.IMPL_TENSOR_TWOSTREAM,
-         "tensor_fourway": native.IMPL_TENSOR_FOURWAY, "tensor_pair": native.IMPL_TENSOR_PAIR}
+_IMPL = {"auto": native.IMPL_AUTO, "simt": native.IMPL_SIMT, "tensor": native.IMPL_TENSOR}
 
 
 def _require_cuda(*ts):
@@ -37,20 +35,42 @@ def _require_cuda(*ts):
 _STATUS = {}
 
 
-def device_status_word(dev) -> torch.Tensor:
-    """Per-device int32 word a kernel sets when one of its bounded waits expires."""
-    key = torch.device(dev).index or 0
+def _device_index(dev) -> int:
+    """CUDA ordinal of ``dev``; a device without an index ("cuda") means the current device."""
+    d = torch.device(dev)
+    return torch.cuda.current_device() if d.index is None else d.index
+
+
+def device_status_word(dev="cuda") -> torch.Tensor:
+    """Per-device int32 word the kernels raise when they find a problem on the device (an expired bounded
+    wait, a position outside the RoPE tables, a code outside its codebook)."""
+    key = _device_index(dev)
     if key not in _STATUS:
-        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
     return _STATUS[key]
 
 
 def check_status(dev="cuda") -> None:
-    """Synchronises and raises VqError(VQ_ETIMEOUT) if a kernel reported an expired wait."""
+    """Synchronises, reads the device's status word and raises VqError with the status the word maps to
+    (VQ_ETIMEOUT for an expired wait, VQ_EINVAL_ARG for a bad position or code).  The word is cleared."""
     w = device_status_word(dev)
-    if int(w.item()) != 0:
+    word = int(w.item())
+    if word != 0:
         w.zero_()
-        raise native.VqError(-6, "device status word")
+        raise native.VqError(lib.vqattn_status_from_word(word), f"device status word {word}")
+
+
+def set_wait_limit(cycles: int) -> int:
+    """Cycles a device-side wait may last before a kernel gives up (<= 0: the default); returns the old value."""
+    return int(lib.vqattn_set_wait_limit_cycles(int(cycles)))
+
+
+def wait_selftest(dev="cuda") -> None:
+    """Launches one warp that waits on a barrier nothing arrives at (see vqattn_wait_selftest)."""
+    idx = _device_index(dev)
+    with torch.cuda.device(idx):
+        check(lib.vqattn_wait_selftest(device_status_word(idx).data_ptr(), stream_ptr(torch.device("cuda", idx))),
+              "vqattn_wait_selftest")
 
 
 def code_dtype_for(K: int) -> torch.dtype:
@@ -113,7 +133,7 @@ _ROPE_TABLES = {}
 def rope_tables(n_pos: int, dim: int, device, base: float = 10000.0):
     """fp32 cos / sin tables [n_pos, dim/2] (angle = pos * base^(-2i/dim), evaluated in float64), cached per device."""
     dev = torch.device(device)
-    key = (dev.index or 0, dim, float(base))
+    key = (_device_index(dev), dim, float(base))
     have = _ROPE_TABLES.get(key)
     if have is None or have[0].shape[0] < n_pos:
         n = max(n_pos, 2 * have[0].shape[0] if have is not None else 0)
@@ -146,6 +166,46 @@ def rope(x: torch.Tensor, positions: Optional[torch.Tensor] = None, const_pos: O
                               cos.shape[0], const_pos if const_pos is not None else 0, desc(out_pos), desc(out_const),
                               device_status_word(dev).data_ptr(), stream_ptr(dev)), "vqattn_rope")
     return out_pos, out_const
+
+
+def rope_qk(q: torch.Tensor, k: torch.Tensor, positions: Optional[torch.Tensor] = None, const_pos: Optional[int] = None,
+            base: float = 10000.0, n_pos: Optional[int] = None, like_input: bool = False):
+    """The rotations of one prefill in one launch (ops/attn_vq.py:402-407): returns (q1, q2 or None, k1).
+
+    q [B,Hq,L,D], k [B,Hkv,L,D]: any strided views with a contiguous last dim.  positions int64 [B,L] (None: 0..L-1).
+    like_input=True allocates the outputs with the memory layout of the inputs ([B,L,H,D] storage stays so)."""
+    dev = _require_cuda(q, k, positions)
+    B, Hq, L, D = q.shape
+    if n_pos is None:
+        n_pos = L if positions is None else int(positions.max().item()) + 1
+    if const_pos is not None:
+        n_pos = max(n_pos, const_pos + 1)
+    cos, sin = rope_tables(n_pos, D, dev, base)
+    if positions is not None:
+        positions = positions.to(torch.int64).expand(B, L).contiguous()
+    new = (lambda t: torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=dev)) if like_input else \
+        (lambda t: torch.empty(t.shape, dtype=t.dtype, device=dev))
+    q1, k1 = new(q), new(k)
+    q2 = new(q) if const_pos is not None else None
+    with torch.cuda.device(dev):
+        check(lib.vqattn_rope_qk(desc(q), desc(k), positions.data_ptr() if positions is not None else None, cos.data_ptr(),
+                                 sin.data_ptr(), cos.shape[0], const_pos if const_pos is not None else 0, desc(q1), desc(q2),
+                                 desc(k1), device_status_word(dev).data_ptr(), stream_ptr(dev)), "vqattn_rope_qk")
+    return q1, q2, k1
+
+
+def decode_append(q, k, v, pos: int, const_pos: int, q1, q2, k1_win, k3_win, v_win, row: int, base: float = 10000.0,
+                  positions: Optional[torch.Tensor] = None, n_pos: Optional[int] = None) -> None:
+    """Per-token step of a decode in one launch: q [B,Hq,1,D] -> q1, q2 [B,Hq,1,D] (rotated to ``pos`` and to
+    ``const_pos``); k, v [B,Hkv,1,D] -> row ``row`` of the window caches (rotated key, raw key, value)."""
+    dev = _require_cuda(q, k, v, q1, q2, k1_win, k3_win, v_win, positions)
+    D = q.shape[-1]
+    cos, sin = rope_tables(max(n_pos or 0, pos + 1, const_pos + 1), D, dev, base)
+    with torch.cuda.device(dev):
+        check(lib.vqattn_decode_append(desc(q), desc(k), desc(v), positions.data_ptr() if positions is not None else None, int(pos),
+                                       cos.data_ptr(), sin.data_ptr(), cos.shape[0], int(const_pos), desc(q1), desc(q2),
+                                       desc(k1_win), desc(k3_win), desc(v_win), int(row), device_status_word(dev).data_ptr(),
+                                       stream_ptr(dev)), "vqattn_decode_append")
 
 
 def gather_aggregates(v_vq: torch.Tensor, vi: torch.Tensor, nb: int, cnt: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -194,12 +254,15 @@ def prefill_from_aggregates(q1, q2, k1, k3, v, codebook_act, cnt, vsum, window: 
 
 def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window: int, scale: Optional[float] = None,
                          bias: Optional[torch.Tensor] = None, impl: str = "auto", return_state: bool = False,
-                         out: Optional[torch.Tensor] = None):
+                         out: Optional[torch.Tensor] = None, codebook_act: Optional[torch.Tensor] = None):
     """The whole prefill path: assign codes to k3, build aggregates of v, fused attention.
 
     q1,q2 [B,Hq,L,D]; k1,k3,v [B,Hkv,L,D] (f32 or bf16); codebooks [Hkv,M,K,D] f32.
     ReRoPE mode: q1,k1 rotated by position, q2 rotated to the constant position window+1, k3 un-rotated
     (ops/attn_vq.py:402-407).  Plain-RoPE mode: pass q2 = q1 and k3 = k1.
+    All five may be strided views with a contiguous last dim, and so may ``out`` ([B,Hq,L,D] view of
+    [B,L,Hq,D] storage gives the layout the reference produces with a transposing copy, :442).
+    codebook_act: [Hkv,M*K,D] copy of the codebooks in the activation dtype, if the caller keeps one.
     """
     B, Hq, L, D = q1.shape
     Hkv, M, K, _ = codebooks.shape
@@ -209,7 +272,7 @@ def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window: int, scale: Optio
         codes = assign_codes(k3, codebooks, bias)
     if nb > 0:
         cnt, vsum = build_aggregates(codes, v, K, nb)
-        cb_act = codebooks.reshape(Hkv, M * K, D).to(q1.dtype)
+        cb_act = codebook_act if codebook_act is not None else codebooks.reshape(Hkv, M * K, D).to(q1.dtype)
     out = prefill_from_aggregates(q1, q2, k1, k3, v, cb_act, cnt, vsum, window, scale, impl, out=out)
     if return_state:
         return out, dict(codes=codes, cnt=cnt, vsum=vsum)
@@ -264,8 +327,8 @@ def cache_advance(codes, v_new, K: int, cnt, vsum_f32, vsum_act=None):
     dev = _require_cuda(codes, v_new, cnt, vsum_f32, vsum_act)
     with torch.cuda.device(dev):
         check(lib.vqattn_cache_advance(desc(codes), desc(v_new), K, desc(cnt), desc(vsum_f32),
-                                       desc(vsum_act) if vsum_act is not None else None, stream_ptr(dev)),
-              "vqattn_cache_advance")
+                                       desc(vsum_act) if vsum_act is not None else None,
+                                       device_status_word(dev).data_ptr(), stream_ptr(dev)), "vqattn_cache_advance")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -283,7 +346,7 @@ _SIDE_STREAMS = {}
 
 
 def _side_streams(dev):
-    key = torch.device(dev).index or 0
+    key = _device_index(dev)
     if key not in _SIDE_STREAMS:
         _SIDE_STREAMS[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
     return _SIDE_STREAMS[key]

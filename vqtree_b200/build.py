@@ -23,7 +23,7 @@ OBJDIR = PKG / "build"
 LIB = LIBDIR / "libvqattn.so"
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-SOURCES = ["api.cu", "assign.cu", "assign_tc.cu", "aggregate.cu", "aggregate_reg.cu", "prefill_simt.cu", "prefill_tc.cu", "prefill_tc2.cu", "prefill_tc3.cu", "prefill_tc4.cu", "prefill_pair.cu", "rope.cu", "decode.cu", "decode_bulk.cu", "decode_tc.cu"]
+SOURCES = ["api.cu", "assign.cu", "assign_tc.cu", "aggregate.cu", "aggregate_reg.cu", "prefill_simt.cu", "prefill_tc4.cu", "rope.cu", "decode.cu", "decode_bulk.cu", "decode_tc.cu"]
 
 
 def nvcc_path() -> str:

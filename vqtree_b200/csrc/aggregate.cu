@@ -30,7 +30,20 @@ template <> __device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bflo
     __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162 *>(&raw.y);
     return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
+template <> __device__ __forceinline__ float4 ld4<__half>(const __half *p)
+{
+    uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = Pair16<__half>::unpack(raw.x), b = Pair16<__half>::unpack(raw.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
 template <typename T> __device__ __forceinline__ void st4(T *p, float4 x);
+template <> __device__ __forceinline__ void st4<__half>(__half *p, float4 x)
+{
+    uint2 raw;
+    raw.x = Pair16<__half>::pack(x.x, x.y);
+    raw.y = Pair16<__half>::pack(x.z, x.w);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
 template <> __device__ __forceinline__ void st4<float>(float *p, float4 x) { *reinterpret_cast<float4 *>(p) = x; }
 template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16 *p, float4 x)
 {
@@ -57,6 +70,16 @@ template <> __device__ __forceinline__ void st8<__nv_bfloat16>(__nv_bfloat16 *p,
     raw.y = *reinterpret_cast<uint32_t *>(&b);
     raw.z = *reinterpret_cast<uint32_t *>(&c);
     raw.w = *reinterpret_cast<uint32_t *>(&d);
+    *reinterpret_cast<uint4 *>(p) = raw;
+}
+
+template <> __device__ __forceinline__ void st8<__half>(__half *p, float4 x, float4 y)
+{
+    uint4 raw;
+    raw.x = Pair16<__half>::pack(x.x, x.y);
+    raw.y = Pair16<__half>::pack(x.z, x.w);
+    raw.z = Pair16<__half>::pack(y.x, y.y);
+    raw.w = Pair16<__half>::pack(y.z, y.w);
     *reinterpret_cast<uint4 *>(p) = raw;
 }
 
@@ -171,26 +194,63 @@ __global__ void gather_aggregates_kernel(const T *__restrict__ v_vq, int64_t s_b
     for (int d = lane; d < D; d += 32) dst[d] = ok ? s[d] : from_f32<T>(0.f);
 }
 
-template <typename TV>
-__global__ void cache_advance_kernel(const void *__restrict__ codes, int code_dtype, int64_t c_sb, int64_t c_sh, int64_t c_sl,
-                                     const TV *__restrict__ v, int64_t v_sb, int64_t v_sh, int64_t v_sl,
-                                     float *__restrict__ cnt, float *__restrict__ vsum, __nv_bfloat16 *__restrict__ shadow,
-                                     int Hkv, int D, int M, int K, int n_new)
+// Cache advance: one CTA owns kAdvRows code rows of one codebook of one (batch, kv head); it keeps their
+// fp32 sums in shared memory, walks the new keys in position order and adds the value rows of the keys
+// whose code falls into its rows - the same left-to-right fp32 sum per row as build_aggregates.
+// A code outside [0, K) would address another row (or memory outside the buffers): such a key is
+// skipped and the status word is raised instead.
+constexpr int kAdvRows = 16;
+constexpr int kAdvThreads = 128;
+
+template <typename TV, typename TS>
+__global__ void __launch_bounds__(kAdvThreads)
+cache_advance_kernel(const void *__restrict__ codes, int code_dtype, int64_t c_sb, int64_t c_sh, int64_t c_sl,
+                     const TV *__restrict__ v, int64_t v_sb, int64_t v_sh, int64_t v_sl, float *__restrict__ cnt,
+                     float *__restrict__ vsum, TS *__restrict__ shadow, int Hkv, int D, int M, int K, int n_new,
+                     int32_t *__restrict__ status)
 {
-    const int u = blockIdx.y, m = blockIdx.x;
+    extern __shared__ float s_acc[];  // [kAdvRows][D]
+    __shared__ int s_rel[kAdvThreads];
+    __shared__ float s_cnt[kAdvRows];
+    const int tid = threadIdx.x;
+    const int parts = (K + kAdvRows - 1) / kAdvRows;
+    const int m = static_cast<int>(blockIdx.x) / parts, r0 = (static_cast<int>(blockIdx.x) % parts) * kAdvRows;
+    const int nrows = min(kAdvRows, K - r0);
+    const int u = blockIdx.y;
     const int b = u / Hkv, h = u % Hkv;
-    const int64_t MK = static_cast<int64_t>(M) * K;
-    const int d = threadIdx.x;
-    for (int j = 0; j < n_new; ++j) {
-        const int code = load_code(codes, code_dtype, b * c_sb + h * c_sh + j * c_sl + m);
-        const int64_t row = static_cast<int64_t>(u) * MK + m * K + code;
-        if (d < D) {
-            const float s = __fadd_rn(vsum[row * D + d], to_f32(v[b * v_sb + h * v_sh + j * v_sl + d]));
-            vsum[row * D + d] = s;
-            if (shadow) shadow[row * D + d] = __float2bfloat16_rn(s);
+    const int64_t row0 = static_cast<int64_t>(u) * M * K + static_cast<int64_t>(m) * K + r0;
+    for (int i = tid; i < nrows * D; i += kAdvThreads) s_acc[i] = vsum[row0 * D + i];
+    if (tid < kAdvRows) s_cnt[tid] = tid < nrows ? cnt[row0 + tid] : 0.f;
+    __syncthreads();
+    const TV *vb = v + b * v_sb + h * v_sh;
+    for (int j0 = 0; j0 < n_new; j0 += kAdvThreads) {
+        int rel = -1;
+        if (j0 + tid < n_new) {
+            const int code = load_code(codes, code_dtype, b * c_sb + h * c_sh + (j0 + tid) * c_sl + m);
+            if (static_cast<unsigned>(code) >= static_cast<unsigned>(K)) {
+                if (status) atomicExch(status, VQ_WORD_BAD_CODE);
+            } else {
+                rel = code - r0;
+            }
         }
-        if (d == 0) cnt[row] += 1.f;
+        s_rel[tid] = rel;
+        __syncthreads();
+        const int nk = min(kAdvThreads, n_new - j0);
+        for (int jj = 0; jj < nk; ++jj) {
+            const int rr = s_rel[jj];
+            if (static_cast<unsigned>(rr) < static_cast<unsigned>(nrows)) {
+                const TV *vr = vb + static_cast<int64_t>(j0 + jj) * v_sl;
+                for (int d = tid; d < D; d += kAdvThreads) s_acc[rr * D + d] = __fadd_rn(s_acc[rr * D + d], to_f32(vr[d]));
+                if (tid == 0) s_cnt[rr] += 1.f;
+            }
+        }
+        __syncthreads();
     }
+    for (int i = tid; i < nrows * D; i += kAdvThreads) {
+        vsum[row0 * D + i] = s_acc[i];
+        if (shadow) shadow[row0 * D + i] = from_f32<TS>(s_acc[i]);
+    }
+    if (tid < nrows) cnt[row0 + tid] = s_cnt[tid];
 }
 
 }  // namespace vq
@@ -242,6 +302,9 @@ extern "C" int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensor
                                              static_cast<int>(M), static_cast<int>(K), static_cast<int>(NB), parts, rows); \
     } while (0)
     if (v->dtype == VQ_F32 && vsum->dtype == VQ_F32) VQ_LAUNCH_AGG(float, float);
+    else if (v->dtype == VQ_F16 && vsum->dtype == VQ_F16) VQ_LAUNCH_AGG(__half, __half);
+    else if (v->dtype == VQ_F16 && vsum->dtype == VQ_F32) VQ_LAUNCH_AGG(__half, float);
+    else if (v->dtype == VQ_F16 || vsum->dtype == VQ_F16) return VQ_EINVAL_DTYPE;
     else if (v->dtype == VQ_F32) VQ_LAUNCH_AGG(float, __nv_bfloat16);
     else if (vsum->dtype == VQ_F32) VQ_LAUNCH_AGG(__nv_bfloat16, float);
     else VQ_LAUNCH_AGG(__nv_bfloat16, __nv_bfloat16);
@@ -283,6 +346,11 @@ extern "C" int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensor
             static_cast<const float *>(v_vq->ptr), v_vq->stride[0], v_vq->stride[1], v_vq->stride[2], vi->ptr, vi->dtype,
             vi->stride[0], vi->stride[1], vi->stride[2], cntp, static_cast<float *>(vsum->ptr), static_cast<int>(H),
             static_cast<int>(NB), static_cast<int>(C), static_cast<int>(D), v_vq->shape[2]);
+    else if (v_vq->dtype == VQ_F16)
+        gather_aggregates_kernel<__half><<<grid, warps * 32, 0, s>>>(
+            static_cast<const __half *>(v_vq->ptr), v_vq->stride[0], v_vq->stride[1], v_vq->stride[2], vi->ptr,
+            vi->dtype, vi->stride[0], vi->stride[1], vi->stride[2], cntp, static_cast<__half *>(vsum->ptr),
+            static_cast<int>(H), static_cast<int>(NB), static_cast<int>(C), static_cast<int>(D), v_vq->shape[2]);
     else
         gather_aggregates_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
             static_cast<const __nv_bfloat16 *>(v_vq->ptr), v_vq->stride[0], v_vq->stride[1], v_vq->stride[2], vi->ptr,
@@ -292,7 +360,7 @@ extern "C" int vqattn_gather_aggregates(const VqTensorDesc *v_vq, const VqTensor
 }
 
 extern "C" int vqattn_cache_advance(const VqTensorDesc *codes, const VqTensorDesc *v_new, int32_t K, VqTensorDesc *cnt,
-                                    VqTensorDesc *vsum_f32, VqTensorDesc *vsum_act, void *stream)
+                                    VqTensorDesc *vsum_f32, VqTensorDesc *vsum_act, int32_t *status_word, void *stream)
 {
     using namespace vq;
     int st;
@@ -306,7 +374,8 @@ extern "C" int vqattn_cache_advance(const VqTensorDesc *codes, const VqTensorDes
     if ((st = check_device(all, 5)) != VQ_OK) return st;
     if (!is_code_dtype(codes->dtype) || !is_act_dtype(v_new->dtype) || cnt->dtype != VQ_F32 || vsum_f32->dtype != VQ_F32)
         return VQ_EINVAL_DTYPE;
-    if (vsum_act && vsum_act->dtype != VQ_BF16) return VQ_EINVAL_DTYPE;
+    // the shadow copy is in the 16-bit activation dtype of the values (bf16 when the values are fp32)
+    if (vsum_act && vsum_act->dtype != (v_new->dtype == VQ_F16 ? VQ_F16 : VQ_BF16)) return VQ_EINVAL_DTYPE;
     const int64_t B = codes->shape[0], Hkv = codes->shape[1], n_new = codes->shape[2], M = codes->shape[3];
     const int64_t D = v_new->shape[3], MK = cnt->shape[2];
     if (K <= 0 || MK != M * K) return VQ_EINVAL_SHAPE;
@@ -317,22 +386,22 @@ extern "C" int vqattn_cache_advance(const VqTensorDesc *codes, const VqTensorDes
     if (vsum_act && (vsum_act->shape[0] != B || vsum_act->shape[1] != Hkv || vsum_act->shape[2] != MK || vsum_act->shape[3] != D))
         return VQ_EINVAL_SHAPE;
     if (!is_dense(*cnt) || !is_dense(*vsum_f32) || (vsum_act && !is_dense(*vsum_act))) return VQ_EINVAL_STRIDE;
-    if (D > 1024 || B * Hkv > 65535) return VQ_EUNSUPPORTED;
+    if (D > 512 || B * Hkv > 65535) return VQ_EUNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    dim3 grid(static_cast<unsigned>(M), static_cast<unsigned>(B * Hkv));
-    const int threads = static_cast<int>((D + 31) / 32 * 32);
-    __nv_bfloat16 *shadow = vsum_act ? static_cast<__nv_bfloat16 *>(vsum_act->ptr) : nullptr;
-    if (v_new->dtype == VQ_F32)
-        cache_advance_kernel<float><<<grid, threads, 0, s>>>(
-            codes->ptr, codes->dtype, codes->stride[0], codes->stride[1], codes->stride[2],
-            static_cast<const float *>(v_new->ptr), v_new->stride[0], v_new->stride[1], v_new->stride[2],
-            static_cast<float *>(cnt->ptr), static_cast<float *>(vsum_f32->ptr), shadow, static_cast<int>(Hkv),
-            static_cast<int>(D), static_cast<int>(M), static_cast<int>(K), static_cast<int>(n_new));
-    else
-        cache_advance_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(
-            codes->ptr, codes->dtype, codes->stride[0], codes->stride[1], codes->stride[2],
-            static_cast<const __nv_bfloat16 *>(v_new->ptr), v_new->stride[0], v_new->stride[1], v_new->stride[2],
-            static_cast<float *>(cnt->ptr), static_cast<float *>(vsum_f32->ptr), shadow, static_cast<int>(Hkv),
-            static_cast<int>(D), static_cast<int>(M), static_cast<int>(K), static_cast<int>(n_new));
+    const int64_t parts = (K + kAdvRows - 1) / kAdvRows;
+    if (M * parts > 0x7fffffff) return VQ_EUNSUPPORTED;
+    dim3 grid(static_cast<unsigned>(M * parts), static_cast<unsigned>(B * Hkv));
+    const size_t smem = sizeof(float) * kAdvRows * static_cast<size_t>(D);
+    void *shadow = vsum_act ? vsum_act->ptr : nullptr;
+#define VQ_ADVANCE(TV, TS)                                                                                              \
+    cache_advance_kernel<TV, TS><<<grid, kAdvThreads, smem, s>>>(                                                              \
+        codes->ptr, codes->dtype, codes->stride[0], codes->stride[1], codes->stride[2], static_cast<const TV *>(v_new->ptr), \
+        v_new->stride[0], v_new->stride[1], v_new->stride[2], static_cast<float *>(cnt->ptr),                           \
+        static_cast<float *>(vsum_f32->ptr), static_cast<TS *>(shadow), static_cast<int>(Hkv), static_cast<int>(D),     \
+        static_cast<int>(M), static_cast<int>(K), static_cast<int>(n_new), status_word)
+    if (v_new->dtype == VQ_F32) VQ_ADVANCE(float, __nv_bfloat16);
+    else if (v_new->dtype == VQ_F16) VQ_ADVANCE(__half, __half);
+    else VQ_ADVANCE(__nv_bfloat16, __nv_bfloat16);
+#undef VQ_ADVANCE
     return launch_status();
 }

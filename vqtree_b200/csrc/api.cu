@@ -1,16 +1,56 @@
-// C-ABI entry points that only validate and dispatch: version, status strings, prefill.
+// C-ABI entry points that only validate and dispatch: version, status strings, the wait bound, prefill.
+#include <atomic>
+
+#include "tc_ptx.cuh"
 #include "vq_common.cuh"
 
 namespace vq {
 int launch_prefill_simt(const VqPrefillArgs *a, cudaStream_t stream);
-int launch_prefill_tensor(const VqPrefillArgs *a, cudaStream_t stream);
-int launch_prefill_tensor_serial(const VqPrefillArgs *a, cudaStream_t stream);
-int launch_prefill_tensor3(const VqPrefillArgs *a, cudaStream_t stream);
 int launch_prefill_tensor4(const VqPrefillArgs *a, cudaStream_t stream);
-int launch_prefill_pair(const VqPrefillArgs *a, cudaStream_t stream);
+}  // namespace vq
+
+namespace vq {
+
+static std::atomic<long long> g_wait_limit{ptx::kDefaultWaitCycles};
+long long wait_limit_cycles() { return g_wait_limit.load(std::memory_order_relaxed); }
+
+// One CTA waits on a barrier that nothing ever arrives at: the wait must give up after `limit` cycles.
+__global__ void wait_selftest_kernel(long long limit, int32_t *status)
+{
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        ptx::fence_mbar_init();
+        if (!ptx::mbar_wait(&bar, 0, limit) && status) atomicExch(status, VQ_WORD_TIMEOUT);
+    }
+}
+
 }  // namespace vq
 
 extern "C" int vqattn_version(void) { return VQATTN_VERSION; }
+
+extern "C" int vqattn_status_from_word(int32_t word)
+{
+    switch (word) {
+    case 0: return VQ_OK;
+    case VQ_WORD_TIMEOUT: return VQ_ETIMEOUT;
+    case VQ_WORD_BAD_POSITION:
+    case VQ_WORD_BAD_CODE: return VQ_EINVAL_ARG;
+    default: return VQ_ELAUNCH;
+    }
+}
+
+extern "C" int64_t vqattn_set_wait_limit_cycles(int64_t cycles)
+{
+    return vq::g_wait_limit.exchange(cycles > 0 ? cycles : vq::ptx::kDefaultWaitCycles);
+}
+
+extern "C" int vqattn_wait_selftest(int32_t *status_word, void *stream)
+{
+    if (status_word == nullptr) return VQ_EINVAL_ARG;
+    vq::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(vq::wait_limit_cycles(), status_word);
+    return vq::launch_status();
+}
 
 extern "C" const char *vqattn_status_string(int status)
 {
@@ -93,15 +133,11 @@ extern "C" int vqattn_prefill(const VqPrefillArgs *a, void *stream)
     if (B * Hq > 65535) return VQ_EUNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int impl = a->impl;
-    if (impl == VQ_IMPL_AUTO) impl = (dt == VQ_BF16) ? VQ_IMPL_TENSOR : VQ_IMPL_SIMT;
+    if (impl == VQ_IMPL_AUTO) impl = is_16bit(dt) ? VQ_IMPL_TENSOR : VQ_IMPL_SIMT;
     if (impl == VQ_IMPL_SIMT) return launch_prefill_simt(a, s);
-    if (impl == VQ_IMPL_TENSOR || impl == VQ_IMPL_TENSOR_SERIAL || impl == VQ_IMPL_TENSOR_TWOSTREAM || impl == VQ_IMPL_TENSOR_FOURWAY ||
-        impl == VQ_IMPL_TENSOR_PAIR) {
-        if (dt != VQ_BF16) return VQ_EINVAL_DTYPE;
-        if (impl == VQ_IMPL_TENSOR) return launch_prefill_tensor4(a, s);
-        if (impl == VQ_IMPL_TENSOR_FOURWAY) return launch_prefill_tensor3(a, s);
-        if (impl == VQ_IMPL_TENSOR_PAIR) return launch_prefill_pair(a, s);
-        return impl == VQ_IMPL_TENSOR_TWOSTREAM ? launch_prefill_tensor(a, s) : launch_prefill_tensor_serial(a, s);
+    if (impl == VQ_IMPL_TENSOR) {
+        if (!is_16bit(dt)) return VQ_EINVAL_DTYPE;
+        return launch_prefill_tensor4(a, s);
     }
     return VQ_EINVAL_ARG;
 }

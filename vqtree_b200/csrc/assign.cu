@@ -27,6 +27,15 @@ template <> struct Vec4Load<__nv_bfloat16> {
     }
 };
 
+template <> struct Vec4Load<__half> {
+    static __device__ __forceinline__ float4 ld(const __half *p)
+    {
+        uint2 raw = *reinterpret_cast<const uint2 *>(p);
+        const float2 a = Pair16<__half>::unpack(raw.x), b = Pair16<__half>::unpack(raw.y);
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kAssignThreads)
 assign_codes_kernel(const T *__restrict__ k, int64_t k_sb, int64_t k_sh, int64_t k_sl,
@@ -208,6 +217,9 @@ extern "C" int vqattn_assign_codes(const VqTensorDesc *k, const VqTensorDesc *co
     if (k->dtype == VQ_F32)
         return D == 64 ? launch_assign<float, 64>(k, codebooks, bias, codes, s)
                        : launch_assign<float, 128>(k, codebooks, bias, codes, s);
+    if (k->dtype == VQ_F16)
+        return D == 64 ? launch_assign<__half, 64>(k, codebooks, bias, codes, s)
+                       : launch_assign<__half, 128>(k, codebooks, bias, codes, s);
     return D == 64 ? launch_assign<__nv_bfloat16, 64>(k, codebooks, bias, codes, s)
                    : launch_assign<__nv_bfloat16, 128>(k, codebooks, bias, codes, s);
 }

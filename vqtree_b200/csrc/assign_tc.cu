@@ -85,6 +85,7 @@ struct AtParams {
     int Hkv, M, K, ntiles;
     int64_t L;
     int32_t *status;
+    long long wait_limit;  // cycles a device-side wait may last before the kernel gives up
 };
 
 template <int D, int NS, int CH>
@@ -209,7 +210,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
                         for (int rem = 0; rem < 2 * NH; ++rem, ++g) {
                             const int slot = g % SL, is_lo = rem / NH, hh = rem % NH;
-                            if (g >= SL && !mbar_wait(&b_free[slot], ((g / SL) - 1) & 1)) {
+                            if (g >= SL && !mbar_wait(&b_free[slot], ((g / SL) - 1) & 1, p.wait_limit)) {
                                 ok = false;
                                 break;
                             }
@@ -231,7 +232,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             for (int m = 0; m < M && ok; ++m)
                 for (int s = 0; s < n_act && ok; ++s) {
                     // the residual terms of (s, m): the key tile itself for m = 0, else written by the scan threads
-                    if (!(m == 0 ? mbar_wait(&bar_k[s], 0) : mbar_wait(&bar_q[s], (m - 1) & 1))) {
+                    if (!(m == 0 ? mbar_wait(&bar_k[s], 0, p.wait_limit) : mbar_wait(&bar_q[s], (m - 1) & 1, p.wait_limit))) {
                         ok = false;
                         break;
                     }
@@ -240,7 +241,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
                         for (int rem = 0; rem < 2 * NH; ++rem, ++g) {
                             const int slot = g % SL, is_lo = rem / NH, hh = rem % NH;
-                            if (!mbar_wait(&b_full[slot], (g / SL) & 1)) {
+                            if (!mbar_wait(&b_full[slot], (g / SL) & 1, p.wait_limit)) {
                                 ok = false;
                                 break;
                             }
@@ -317,7 +318,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll 1
             for (int g = 0; g < groups && ok; ++g) {
                 if (g % C::kGroupsPerChunk == 0) {
-                    ok = __all_sync(kAll, mbar_wait(&bar_c[s][g / C::kGroupsPerChunk], m & 1));
+                    ok = __all_sync(kAll, mbar_wait(&bar_c[s][g / C::kGroupsPerChunk], m & 1, p.wait_limit));
                     tc_fence_after();
                     if (!ok) break;
                 }
@@ -535,7 +536,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     tc_fence_before();
     __syncthreads();
     if (s_err && tid == 0) {
-        if (p.status) atomicExch(p.status, 3);
+        if (p.status) atomicExch(p.status, VQ_WORD_TIMEOUT);
 #pragma unroll 1
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);  // let tile loads in flight land
     }
@@ -575,6 +576,7 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     p.L = L;
     p.ntiles = static_cast<int>((L + kBlock - 1) / kBlock);
     p.status = status;
+    p.wait_limit = wait_limit_cycles();
     auto kern = assign_tc_kernel<D, NS, CH>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
     dim3 grid(static_cast<unsigned>((p.ntiles + NS - 1) / NS), static_cast<unsigned>(B * Hkv));

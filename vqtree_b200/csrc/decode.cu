@@ -77,9 +77,9 @@ __device__ __forceinline__ void stream_rows(DecState<GH, Slice<T>::E> &st, const
 
 // Far rows [r0,r1) with an fp32 codebook (512-byte rows for D = 128) and bf16 value sums: a step
 // covers GPW rows of the warp; their scores are formed by groups of D/4 lanes in GPW/GPWC sub-steps.
-template <int D, int GH, int U>
+template <typename TV, int D, int GH, int U>
 __device__ __forceinline__ void stream_far_f32cb(DecState<GH, 8> &st, const float *__restrict__ C,
-                                                 const __nv_bfloat16 *__restrict__ V, int r0, int r1,
+                                                 const TV *__restrict__ V, int r0, int r1,
                                                  const float *__restrict__ qs, float scale_log2, const float *__restrict__ wts)
 {
     constexpr int LPR = D / 8, GPW = 32 / LPR;     // value-row lane groups
@@ -107,7 +107,7 @@ __device__ __forceinline__ void stream_far_f32cb(DecState<GH, 8> &st, const floa
                 else cx[uu][ss][0] = cx[uu][ss][1] = cx[uu][ss][2] = cx[uu][ss][3] = 0.f;
             }
             const int rv = base + vg;
-            if (rv < r1) Slice<__nv_bfloat16>::ld(V + static_cast<int64_t>(rv) * D + sub * 8, vx[uu]);
+            if (rv < r1) Slice<TV>::ld(V + static_cast<int64_t>(rv) * D + sub * 8, vx[uu]);
             else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) vx[uu][e] = 0.f;
@@ -182,9 +182,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_kernel(DecodeParams p)
     if (f1 > f0) {
         if constexpr (sizeof(TC) == sizeof(T))
             stream_rows<T, D, GH, U>(st, reinterpret_cast<const T *>(cbk), D, vs, D, f0, f1, s_q + GH * D, p.scale_log2, cn);
-        else
-            stream_far_f32cb<D, GH, U>(st, reinterpret_cast<const float *>(cbk), reinterpret_cast<const __nv_bfloat16 *>(vs),
-                                       f0, f1, s_q + GH * D, p.scale_log2, cn);
+        else if constexpr (sizeof(T) == 2)
+            stream_far_f32cb<T, D, GH, U>(st, reinterpret_cast<const float *>(cbk), vs, f0, f1, s_q + GH * D, p.scale_log2, cn);
     }
     // merge the lane groups of a warp, then the warps
 #pragma unroll
@@ -218,7 +217,8 @@ extern "C" size_t vqattn_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t H
     return split_kernel > stream_kernel ? split_kernel : stream_kernel;
 }
 
-extern "C" int vqattn_decode(const VqDecodeArgs *a, void *stream)
+// Argument checks shared by vqattn_decode and vqattn_decode_static (everything but the workspace).
+static int decode_validate(const VqDecodeArgs *a)
 {
     using namespace vq;
     if (a == nullptr) return VQ_EINVAL_ARG;
@@ -271,6 +271,19 @@ extern "C" int vqattn_decode(const VqDecodeArgs *a, void *stream)
     if (far && (reinterpret_cast<uintptr_t>(a->codebook.ptr) % 16 || reinterpret_cast<uintptr_t>(a->vsum.ptr) % 16))
         return VQ_EINVAL_STRIDE;
     if (B * Hkv > 65535 || a->n_valid > (1 << 24) || MK > (1 << 24)) return VQ_EUNSUPPORTED;
+    return VQ_OK;
+}
+
+extern "C" int vqattn_decode(const VqDecodeArgs *a, void *stream)
+{
+    using namespace vq;
+    int st = decode_validate(a);
+    if (st != VQ_OK) return st;
+    const bool far = a->use_far != 0;
+    const int dt = a->q1.dtype;
+    const int64_t B = a->q1.shape[0], Hq = a->q1.shape[1], D = a->q1.shape[2];
+    const int64_t Hkv = a->k1_win.shape[1];
+    const int64_t MK = far ? a->codebook.shape[1] : 0;
     if (a->workspace == nullptr || a->workspace_bytes < vqattn_decode_workspace_bytes(B, Hq, Hkv, D)) return VQ_EWORKSPACE;
 
     const int G = static_cast<int>(Hq / Hkv);
@@ -327,6 +340,12 @@ extern "C" int vqattn_decode(const VqDecodeArgs *a, void *stream)
     if (dt == VQ_F32) {
         if (D == 64) VQ_DEC_G(float, float, 64);
         else VQ_DEC_G(float, float, 128);
+    } else if (dt == VQ_F16 && cb32) {
+        if (D == 64) VQ_DEC_G(__half, float, 64);
+        else VQ_DEC_G(__half, float, 128);
+    } else if (dt == VQ_F16) {
+        if (D == 64) VQ_DEC_G(__half, __half, 64);
+        else VQ_DEC_G(__half, __half, 128);
     } else if (cb32) {
         if (D == 64) VQ_DEC_G(__nv_bfloat16, float, 64);
         else VQ_DEC_G(__nv_bfloat16, float, 128);
@@ -355,10 +374,11 @@ extern "C" size_t vqattn_decode_static_capacity(void) { return VQATTN_DECODE_STA
 extern "C" int vqattn_decode_static(const VqDecodeArgs *a, void *stream)
 {
     using namespace vq;
-    if (a == nullptr) return VQ_EINVAL_ARG;
-    if (a->q1.ndim != 3 || a->k1_win.ndim != 4) return VQ_EINVAL_SHAPE;
+    // every argument check comes first: a rejected call must not touch the shared array, which a
+    // previous call's kernel may still be using
+    const int vst = decode_validate(a);
+    if (vst != VQ_OK) return vst;
     const int64_t B = a->q1.shape[0], Hq = a->q1.shape[1], D = a->q1.shape[2], Hkv = a->k1_win.shape[1];
-    if (B <= 0 || Hq <= 0 || D <= 0 || Hkv <= 0) return VQ_EINVAL_SHAPE;
     // the built-in scratch has a fixed size: larger problems must use vqattn_decode with their own workspace
     if (vqattn_decode_workspace_bytes(B, Hq, Hkv, D) > VQATTN_DECODE_STATIC_BYTES) return VQ_EWORKSPACE;
 

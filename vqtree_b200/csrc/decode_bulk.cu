@@ -65,6 +65,7 @@ struct BulkParams {
     float *partial;         // [(num_ctas + units)][GH][D+2]
     int *ticket;            // [units]
     int32_t *status;
+    long long wait_limit;  // cycles a device-side wait may last before the kernel gives up
 };
 
 __device__ __forceinline__ void ld_slice_bf16(const uint8_t *p, float (&x)[8])
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(kBulkThreads, VQ_BULK_CTAS_PER_SM) decode_bulk
                     tt = 0;
                     ++ue;
                 }
-                if (t >= kBulkStages && !mbar_wait(&empty[sidx], ((t / kBulkStages) - 1) & 1)) {
+                if (t >= kBulkStages && !mbar_wait(&empty[sidx], ((t / kBulkStages) - 1) & 1, bp.wait_limit)) {
                     ok = false;
                     break;
                 }
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(kBulkThreads, VQ_BULK_CTAS_PER_SM) decode_bulk
                 if (cur_ue >= 0) flush(cur_ue);
                 st.init();
             }
-            if (!mbar_wait(&full[sidx], (t / kBulkStages) & 1)) {
+            if (!mbar_wait(&full[sidx], (t / kBulkStages) & 1, bp.wait_limit)) {
                 ok = false;
                 break;
             }
@@ -433,7 +434,7 @@ __global__ void __launch_bounds__(kBulkThreads, VQ_BULK_CTAS_PER_SM) decode_bulk
     }
     __syncthreads();
     if (s_err) {
-        if (tid == 0 && bp.status) atomicExch(bp.status, 2);
+        if (tid == 0 && bp.status) atomicExch(bp.status, VQ_WORD_TIMEOUT);
         // copies still in flight must land before the shared memory is released
         if (tid == 0)
 #pragma unroll 1
@@ -492,6 +493,7 @@ int launch_decode_bulk(const DecodeParams &p, int64_t units, int D, int GH, bool
     bp.ticket = static_cast<int *>(workspace);
     bp.partial = reinterpret_cast<float *>(static_cast<char *>(workspace) + tickets);
     bp.status = status;
+    bp.wait_limit = wait_limit_cycles();
 #define VQ_BULK_G(TC, DD)                                            \
     do {                                                             \
         if (GH == 4) return launch_bulk_t<TC, DD, 4>(bp, s);         \

@@ -44,6 +44,22 @@ template <> struct Slice<__nv_bfloat16> {
     }
 };
 
+template <> struct Slice<__half> {
+    static constexpr int E = 8;
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float (&x)[8])
+    {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 t = Pair16<__half>::unpack(w[i]);
+            x[2 * i] = t.x;
+            x[2 * i + 1] = t.y;
+        }
+    }
+    static __device__ __forceinline__ void ld(const __half *p, float (&x)[8]) { unpack(__ldcs(reinterpret_cast<const uint4 *>(p)), x); }
+    static __device__ __forceinline__ void ld_cached(const __half *p, float (&x)[8]) { unpack(__ldg(reinterpret_cast<const uint4 *>(p)), x); }
+};
+
 struct DecodeParams {
     const void *q1, *q2, *k1w, *k3w, *vw, *codebook, *vsum;
     const float *cnt;

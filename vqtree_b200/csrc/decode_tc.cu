@@ -49,6 +49,7 @@ struct DtParams {
     float *partial;      // [(num_ctas + units)][G][D+2]
     int *ticket;         // [units]
     int32_t *status;
+    long long wait_limit;  // cycles a device-side wait may last before the kernel gives up
 };
 
 struct DtItem {
@@ -152,7 +153,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             }
             const int ue = pr_ue, tt = pr_tt;
             const int b = ue / p.Hkv, hk = ue % p.Hkv;
-            if (t >= NS && !mbar_wait(&empty[st], ((t / NS) - 1) & 1)) {
+            if (t >= NS && !mbar_wait(&empty[st], ((t / NS) - 1) & 1, bp.wait_limit)) {
                 pr_ok = false;
                 break;
             }
@@ -160,7 +161,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 pr_cur = ue;
                 ++pr_seg;
                 const int slot = pr_seg & 1;
-                if (pr_seg >= 2 && !mbar_wait(&q_free[slot], ((pr_seg >> 1) - 1) & 1)) {
+                if (pr_seg >= 2 && !mbar_wait(&q_free[slot], ((pr_seg >> 1) - 1) & 1, bp.wait_limit)) {
                     pr_ok = false;
                     break;
                 }
@@ -225,12 +226,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 const int tt = tt_s;
                 if (t == 0 || tt == 0) {         // first item of a unit segment
                     ++seg;
-                    if (!mbar_wait(&q_full[seg & 1], (seg >> 1) & 1)) {
+                    if (!mbar_wait(&q_full[seg & 1], (seg >> 1) & 1, bp.wait_limit)) {
                         ok = false;
                         return;
                     }
                 }
-                if (!mbar_wait(&full[st], (t / NS) & 1)) {
+                if (!mbar_wait(&full[st], (t / NS) & 1, bp.wait_limit)) {
                     ok = false;
                     return;
                 }
@@ -254,7 +255,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 const int st = t % NS, sb = t & 1;
                 if (++tt_p == TU) tt_p = 0;
                 const bool first_of_seg = (t == 0) || tt_p == 0;
-                if (!mbar_wait(&p_ready[sb], (t >> 1) & 1)) {
+                if (!mbar_wait(&p_ready[sb], (t >> 1) & 1, bp.wait_limit)) {
                     ok = false;
                     return;
                 }
@@ -293,14 +294,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
         auto sync4 = [&]() {
             __syncwarp();
             if (lane == 0) mbar_arrive(&xbar);
-            const bool r = __all_sync(kAll, mbar_wait(&xbar, xph & 1));
+            const bool r = __all_sync(kAll, mbar_wait(&xbar, xph & 1, bp.wait_limit));
             ++xph;
             return r;
         };
 
         // write this CTA's partial of unit `ue` (its last tile was t_last) and let the last contributor merge the unit
         auto flush = [&](int ue, int t_last) {
-            if (!__all_sync(kAll, mbar_wait(&o_done[t_last & 1], (t_last >> 1) & 1))) {
+            if (!__all_sync(kAll, mbar_wait(&o_done[t_last & 1], (t_last >> 1) & 1, bp.wait_limit))) {
                 ok = false;
                 return;
             }
@@ -402,7 +403,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             last_t = t;
             const DtItem it = dt_item(bp, tt);
             // the counts of a far tile arrive with the tile; the scores once the MMAs have finished
-            if (!__all_sync(kAll, mbar_wait(&full[st], (t / NS) & 1) && mbar_wait(&s_ready[sb], (t >> 1) & 1))) {
+            if (!__all_sync(kAll, mbar_wait(&full[st], (t / NS) & 1, bp.wait_limit) && mbar_wait(&s_ready[sb], (t >> 1) & 1, bp.wait_limit))) {
                 ok = false;
                 break;
             }
@@ -458,7 +459,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 }
                 if (any_scale && !first_of_seg) {
                     // O^T holds the products up to the previous tile: wait for the last one, then scale column g by alpha[g]
-                    if (!__all_sync(kAll, mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1))) {
+                    if (!__all_sync(kAll, mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1, bp.wait_limit))) {
                         ok = false;
                         break;
                     }
@@ -493,7 +494,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
     tc_fence_before();
     __syncthreads();
     if (s_err && tid == 0) {
-        if (bp.status) atomicExch(bp.status, 2);
+        if (bp.status) atomicExch(bp.status, VQ_WORD_TIMEOUT);
         // a bounded wait expired: give tile loads still in flight time to land before leaving
 #pragma unroll 1
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
@@ -559,6 +560,7 @@ int launch_decode_tc(const VqDecodeArgs *a, const DecodeParams &p, cudaStream_t 
     bp.ticket = static_cast<int *>(a->workspace);
     bp.partial = reinterpret_cast<float *>(static_cast<char *>(a->workspace) + tickets);
     bp.status = a->status_word;
+    bp.wait_limit = wait_limit_cycles();
 
     CUtensorMap mk1, mk3, mv, mcb, mvs, mq1, mq2;
     auto win_map = [&](CUtensorMap *m, const VqTensorDesc &t) {

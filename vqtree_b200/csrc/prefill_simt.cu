@@ -54,6 +54,25 @@ template <int D> struct RowDot<__nv_bfloat16, D> {
     }
 };
 
+template <int D> struct RowDot<__half, D> {
+    static __device__ __forceinline__ float dot(const float *__restrict__ q, const __half *__restrict__ k)
+    {
+        float s = 0.f;
+#pragma unroll
+        for (int d = 0; d < D; d += 8) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(k + d);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 kk = Pair16<__half>::unpack(w[i]);
+                s = fmaf(q[d + 2 * i], kk.x, s);
+                s = fmaf(q[d + 2 * i + 1], kk.y, s);
+            }
+        }
+        return s;
+    }
+};
+
 struct SimtPrefillParams {
     const void *q1, *q2, *k1, *k3, *v, *codebook, *vsum;
     const float *cnt;
@@ -196,6 +215,9 @@ int launch_prefill_simt(const VqPrefillArgs *a, cudaStream_t stream)
     if (a->q1.dtype == VQ_F32) {
         if (D == 64) prefill_simt_kernel<float, 64><<<grid, kSimtWarps * 32, 0, stream>>>(p);
         else prefill_simt_kernel<float, 128><<<grid, kSimtWarps * 32, 0, stream>>>(p);
+    } else if (a->q1.dtype == VQ_F16) {
+        if (D == 64) prefill_simt_kernel<__half, 64><<<grid, kSimtWarps * 32, 0, stream>>>(p);
+        else prefill_simt_kernel<__half, 128><<<grid, kSimtWarps * 32, 0, stream>>>(p);
     } else {
         if (D == 64) prefill_simt_kernel<__nv_bfloat16, 64><<<grid, kSimtWarps * 32, 0, stream>>>(p);
         else prefill_simt_kernel<__nv_bfloat16, 128><<<grid, kSimtWarps * 32, 0, stream>>>(p);

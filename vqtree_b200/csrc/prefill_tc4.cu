@@ -46,22 +46,28 @@ struct T4Cfg {
     static constexpr int kOq = D / 2;                          // O columns written by one thread at the end
 };
 
-// MODE 0: no mask; 1: columns [lo, hi) valid (relative to the chunk's first column); 2: far tile.
-// A far tile needs no mask: a code without members has a zero value-sum row and weight 0 in the
-// denominator, so its P contributes nothing; it can only raise the reference maximum, which the
-// softmax is invariant to (scores are far inside the exponent range).
+// MODE 0: no mask; 1: columns [lo, hi) valid (relative to the chunk's first column); 2: far tile in
+// which every code has members (count-weighted sum, no mask); 3: far tile with empty codes: a code
+// with cnt == 0 is excluded from the maximum and from P, as the reference does before its maximum
+// (ops/triton_fused_vq_attn.py:44-46) - otherwise an unused codeword with a dominating score could
+// push every real weight below the exponent range.  cw: the counts of the chunk's 32 columns.
 template <int MODE>
-__device__ __forceinline__ void t4_mask2(float &x0, float &x1, int c0, int lo, int hi)
+__device__ __forceinline__ void t4_mask2(float &x0, float &x1, int c0, int lo, int hi, const float *cw)
 {
     if (MODE == 1) {
         x0 = (c0 >= lo && c0 < hi) ? x0 : -INFINITY;
         x1 = (c0 + 1 >= lo && c0 + 1 < hi) ? x1 : -INFINITY;
     }
+    if (MODE == 3) {
+        const float2 w = *reinterpret_cast<const float2 *>(cw + c0);
+        x0 = w.x > 0.f ? x0 : -INFINITY;
+        x1 = w.y > 0.f ? x1 : -INFINITY;
+    }
 }
 
 // maximum of 32 score columns of the thread's row
 template <int MODE>
-__device__ __forceinline__ float t4_max_pass(uint32_t s_addr, int lo, int hi)
+__device__ __forceinline__ float t4_max_pass(uint32_t s_addr, int lo, int hi, const float *cw = nullptr)
 {
     uint32_t r[32];
     tmem_ld32(s_addr, r);
@@ -70,15 +76,15 @@ __device__ __forceinline__ float t4_max_pass(uint32_t s_addr, int lo, int hi)
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         float a0 = __uint_as_float(r[2 * j]), a1 = __uint_as_float(r[2 * j + 1]);
-        t4_mask2<MODE>(a0, a1, 2 * j, lo, hi);
+        t4_mask2<MODE>(a0, a1, 2 * j, lo, hi, cw);
         mx[j & 3] = fmax3(mx[j & 3], a0, a1);
     }
     return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
-// P = exp2(S * scale - m) for 32 columns, packed bf16 written to 16 columns at p_addr; returns the
-// (count-weighted for MODE 2) sum of the 32 values.
-template <int MODE>
+// P = exp2(S * scale - m) for 32 columns, packed 16-bit floats written to 16 columns at p_addr; returns
+// the (count-weighted for MODE 2 and 3) sum of the 32 values.
+template <int MODE, bool F16>
 __device__ __forceinline__ float t4_exp_pass(uint32_t s_addr, uint32_t p_addr, const float *cw, int lo, int hi,
                                              float scale_log2, float neg_m)
 {
@@ -91,18 +97,18 @@ __device__ __forceinline__ float t4_exp_pass(uint32_t s_addr, uint32_t p_addr, c
         const int c0 = 2 * j;
         float x0 = __uint_as_float(r[c0]), x1 = __uint_as_float(r[c0 + 1]);
         float t0, t1;
-        t4_mask2<MODE>(x0, x1, c0, lo, hi);
+        t4_mask2<MODE>(x0, x1, c0, lo, hi, cw);
         ffma2(t0, t1, x0, x1, scale_log2, scale_log2, neg_m, neg_m);
         const float p0 = ex2(t0), p1 = ex2(t1);
-        if (MODE == 2) ffma2(ls[2 * (j & 1)], ls[2 * (j & 1) + 1], p0, p1, cw[c0], cw[c0 + 1], ls[2 * (j & 1)], ls[2 * (j & 1) + 1]);
+        if (MODE >= 2) ffma2(ls[2 * (j & 1)], ls[2 * (j & 1) + 1], p0, p1, cw[c0], cw[c0 + 1], ls[2 * (j & 1)], ls[2 * (j & 1) + 1]);
         else fadd2(ls[2 * (j & 1)], ls[2 * (j & 1) + 1], ls[2 * (j & 1)], ls[2 * (j & 1) + 1], p0, p1);
-        pk[j] = pack_bf16(p0, p1);
+        pk[j] = pack16<F16>(p0, p1);
     }
     tmem_st16(p_addr, pk);
     return (ls[0] + ls[1]) + (ls[2] + ls[3]);
 }
 
-template <int D>
+template <int D, bool F16>
 __global__ void __launch_bounds__(T4Cfg<D>::kThreads, 1)
 prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                    const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k3,
@@ -174,7 +180,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             auto load = [&](int it, bool is_v) {
                 if (!ok) return;
                 const int slot = q % NS;
-                if (q >= NS && !mbar_wait(&kv_empty[slot], ((q / NS) - 1) & 1)) {
+                if (q >= NS && !mbar_wait(&kv_empty[slot], ((q / NS) - 1) & 1, p.wait_limit)) {
                     ok = false;
                     return;
                 }
@@ -203,19 +209,19 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     } else if (warp == C::kWarpMma) {
         // ================================================================== MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = idesc_bf16(128, 128, 0, 0);
-            constexpr uint32_t idesc_pv = idesc_bf16(128, D, 0, 1);
+            constexpr uint32_t idesc_qk = idesc_f16kind(128, 128, 0, 0, F16 ? 0u : 1u);
+            constexpr uint32_t idesc_pv = idesc_f16kind(128, D, 0, 1, F16 ? 0u : 1u);
             // operand descriptors differ only in their 16-byte-granular start address
             const uint64_t d_q1 = smem_desc_sw128(smem_u32(smem + C::kQ1), 16, 1024);
             const uint64_t d_q2 = p.rerope ? smem_desc_sw128(smem_u32(smem + C::kQ2), 16, 1024) : d_q1;
             const uint64_t d_k0 = smem_desc_sw128(smem_u32(smem + C::kRing), 16, 1024);          // K tiles: K-major
             const uint64_t d_v0 = smem_desc_sw128(smem_u32(smem + C::kRing), kHalfBytes, 1024);  // V tiles: MN-major
-            bool ok = mbar_wait(&bar_q, 0);
+            bool ok = mbar_wait(&bar_q, 0, p.wait_limit);
             int q = 0;
             auto qk = [&](int it) {  // S(it) = Q K(it)^T into buffer it % 3 (free: the product of item it - 3 was issued before)
                 if (!ok) return;
                 const int slot = q % NS, buf = it % NB3;
-                if (!mbar_wait(&kv_full[slot], (q / NS) & 1)) {
+                if (!mbar_wait(&kv_full[slot], (q / NS) & 1, p.wait_limit)) {
                     ok = false;
                     return;
                 }
@@ -238,7 +244,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             auto pv = [&](int it) {  // O += P(it) V(it)
                 if (!ok) return;
                 const int slot = q % NS, buf = it % NB3;
-                if (!mbar_wait(&p_full[buf], (it / NB3) & 1) || !mbar_wait(&kv_full[slot], (q / NS) & 1)) {
+                if (!mbar_wait(&p_full[buf], (it / NB3) & 1, p.wait_limit) || !mbar_wait(&kv_full[slot], (q / NS) & 1, p.wait_limit)) {
                     ok = false;
                     return;
                 }
@@ -281,10 +287,12 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         for (int it = g; it < n; it += NB3) {
             const int par = (it / NB3) & 1;
             const int kind = work.kind(it);
+            bool has_empty = false;                       // warp-uniform: some code of this far tile has no member
             if (kind == kFar) {
                 __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) cw[32 * i + lane] = cnt_reg[i];
+                has_empty = __any_sync(kAll, !(cnt_reg[0] > 0.f && cnt_reg[1] > 0.f && cnt_reg[2] > 0.f && cnt_reg[3] > 0.f));
                 __syncwarp();
                 if (it + NB3 < work.n_far) {
 #pragma unroll
@@ -296,14 +304,17 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             if (kind == kDiag) hi = row + 1;
             else if (kind == kBdA) hi = row;
             else if (kind == kBdB) lo = row;
-            if (!__all_sync(kAll, mbar_wait(&s_full[g], par))) {
+            if (!__all_sync(kAll, mbar_wait(&s_full[g], par, p.wait_limit))) {
                 ok = false;
                 break;
             }
             tc_fence_after();
             // ---- row maximum of this item
             float mx = -INFINITY;
-            if (kind == kFar || kind == kFull) {
+            if (kind == kFar && has_empty) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) mx = fmaxf(mx, t4_max_pass<3>(sa + 32 * c, 0, 0, cw + 32 * c));
+            } else if (kind == kFar || kind == kFull) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) mx = fmaxf(mx, t4_max_pass<0>(sa + 32 * c, 0, 0));
             } else {
@@ -312,7 +323,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             }
             const float m_tile = mx * p.scale_log2;
             // ---- the reference left by the previous item; raise it only when this item is far above it
-            if (it > 0 && !__all_sync(kAll, mbar_wait(&refbar[(g + NB3 - 1) % NB3][lq], ((it - 1) / NB3) & 1))) {
+            if (it > 0 && !__all_sync(kAll, mbar_wait(&refbar[(g + NB3 - 1) % NB3][lq], ((it - 1) / NB3) & 1, p.wait_limit))) {
                 ok = false;
                 break;
             }
@@ -327,7 +338,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             const bool rescale = (m_use != ref) && (ref != -INFINITY);
             if (__any_sync(kAll, rescale)) {
                 // O may be touched once the product of the previous item has finished (it >= 1 here)
-                if (!__all_sync(kAll, mbar_wait(&pv_done[(it - 1) % NB3], ((it - 1) / NB3) & 1))) {
+                if (!__all_sync(kAll, mbar_wait(&pv_done[(it - 1) % NB3], ((it - 1) / NB3) & 1, p.wait_limit))) {
                     ok = false;
                     break;
                 }
@@ -349,15 +360,18 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             }
             // ---- exponentials: chunk c reads columns [32c, 32c+32) and writes P over [16c, 16c+16), never ahead of a read
             float ls = 0.f;
-            if (kind == kFar) {
+            if (kind == kFar && has_empty) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) ls += t4_exp_pass<2>(sa + 32 * c, sa + 16 * c, cw + 32 * c, 0, 0, p.scale_log2, -m_safe);
+                for (int c = 0; c < 4; ++c) ls += t4_exp_pass<3, F16>(sa + 32 * c, sa + 16 * c, cw + 32 * c, 0, 0, p.scale_log2, -m_safe);
+            } else if (kind == kFar) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) ls += t4_exp_pass<2, F16>(sa + 32 * c, sa + 16 * c, cw + 32 * c, 0, 0, p.scale_log2, -m_safe);
             } else if (kind == kFull) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) ls += t4_exp_pass<0>(sa + 32 * c, sa + 16 * c, cw, 0, 0, p.scale_log2, -m_safe);
+                for (int c = 0; c < 4; ++c) ls += t4_exp_pass<0, F16>(sa + 32 * c, sa + 16 * c, cw, 0, 0, p.scale_log2, -m_safe);
             } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) ls += t4_exp_pass<1>(sa + 32 * c, sa + 16 * c, cw, lo - 32 * c, hi - 32 * c, p.scale_log2, -m_safe);
+                for (int c = 0; c < 4; ++c) ls += t4_exp_pass<1, F16>(sa + 32 * c, sa + 16 * c, cw, lo - 32 * c, hi - 32 * c, p.scale_log2, -m_safe);
             }
             l_part += ls;
             tc_wait_st();
@@ -370,8 +384,8 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         s_mend[g][row] = my_ref;
         __syncwarp();
         if (lane == 0) mbar_arrive(&endbar);
-        if (ok && !__all_sync(kAll, mbar_wait(&endbar, 0))) ok = false;
-        if (ok && !__all_sync(kAll, mbar_wait(&pv_done[(n - 1) % NB3], ((n - 1) / NB3) & 1))) ok = false;
+        if (ok && !__all_sync(kAll, mbar_wait(&endbar, 0, p.wait_limit))) ok = false;
+        if (ok && !__all_sync(kAll, mbar_wait(&pv_done[(n - 1) % NB3], ((n - 1) / NB3) & 1, p.wait_limit))) ok = false;
         tc_fence_after();
         if (!ok) s_err = 1;
         if (ok && g < 2) {
@@ -384,7 +398,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             }
             const float inv = den > 0.f ? 1.f / den : 0.f;
             const int64_t grow = static_cast<int64_t>(m) * kBlock + row;
-            __nv_bfloat16 *o = p.out + b * p.o_sb + hq * p.o_sh + grow * p.o_sl + g * C::kOq;
+            uint16_t *o = p.out + b * p.o_sb + hq * p.o_sh + grow * p.o_sl + g * C::kOq;
             uint32_t r[C::kOq];
 #pragma unroll
             for (int c = 0; c < C::kOq / 32; ++c) tmem_ld32(o_addr + g * C::kOq + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
@@ -393,10 +407,10 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
 #pragma unroll
                 for (int j = 0; j < C::kOq / 8; ++j) {
                     uint4 w;
-                    w.x = pack_bf16(__uint_as_float(r[8 * j]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
-                    w.y = pack_bf16(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
-                    w.z = pack_bf16(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
-                    w.w = pack_bf16(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
+                    w.x = pack16<F16>(__uint_as_float(r[8 * j]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
+                    w.y = pack16<F16>(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
+                    w.z = pack16<F16>(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
+                    w.w = pack16<F16>(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
                     *reinterpret_cast<uint4 *>(o + 8 * j) = w;
                 }
                 if (g == 0 && p.lse2) p.lse2[static_cast<int64_t>(bh) * p.L + grow] = ref + log2f(den);
@@ -406,7 +420,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     tc_fence_before();
     __syncthreads();
     if (s_err && tid == 0) {
-        if (p.status) atomicExch(p.status, 1);
+        if (p.status) atomicExch(p.status, VQ_WORD_TIMEOUT);
         // a bounded wait expired: give tile loads still in flight time to land before leaving
 #pragma unroll 1
         for (int w = 0; w < (1 << 14); ++w) __nanosleep(256);
@@ -418,7 +432,7 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
     }
 }
 
-template <int D>
+template <int D, bool F16>
 static int launch_tc4(const VqPrefillArgs *a, cudaStream_t stream)
 {
     using C = T4Cfg<D>;
@@ -426,7 +440,7 @@ static int launch_tc4(const VqPrefillArgs *a, cudaStream_t stream)
     TcParams p;
     const int st = tc_setup<D>(a, m, p);
     if (st != VQ_OK) return st;
-    auto kern = prefill_tc4_kernel<D>;
+    auto kern = prefill_tc4_kernel<D, F16>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
     dim3 grid(static_cast<unsigned>(p.ntiles * (p.Hq / p.Hkv)), static_cast<unsigned>(a->q1.shape[0] * p.Hkv));
     kern<<<grid, C::kThreads, C::kTotal, stream>>>(m.q1, m.q2, m.k1, m.k3, m.v, m.cb, m.vs, p);
@@ -438,7 +452,8 @@ int launch_prefill_tensor4(const VqPrefillArgs *a, cudaStream_t stream)
     const int D = static_cast<int>(a->q1.shape[3]);
     // 16-byte aligned rows for the output stores and the tensor maps
     if (a->out.stride[2] % 8 || a->out.stride[1] % 8 || a->out.stride[0] % 8) return VQ_EINVAL_STRIDE;
-    return D == 64 ? launch_tc4<64>(a, stream) : launch_tc4<128>(a, stream);
+    if (a->q1.dtype == VQ_F16) return D == 64 ? launch_tc4<64, true>(a, stream) : launch_tc4<128, true>(a, stream);
+    return D == 64 ? launch_tc4<64, false>(a, stream) : launch_tc4<128, false>(a, stream);
 }
 
 }  // namespace vq

@@ -18,10 +18,11 @@ struct TcParams {
     int wblocks;  // window / 128
     float scale_log2;
     const float *cnt;  // [B*Hkv, NB, MK]
-    __nv_bfloat16 *out;
+    uint16_t *out;     // 16-bit activation dtype (bf16 or half)
     int64_t o_sb, o_sh, o_sl;
     float *lse2;
     int32_t *status;
+    long long wait_limit;  // cycles a device-side wait may last before the kernel gives up
 };
 
 // Work list of query tile m: far codebook tiles, the boundary block (two masked passes in ReRoPE
@@ -79,7 +80,7 @@ inline EncodeTiledFn encode_fn()
 
 // bf16 tensor with up to 4 dims given innermost-first; box = 64 x box_rows (x 1 x 1), 128-byte swizzle.
 inline bool make_map(CUtensorMap *out, const void *ptr, int rank, const uint64_t *dims, const uint64_t *strides_elems,
-                     int box_rows = kBlock)
+                     int box_rows = kBlock, bool f16 = false)
 {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
@@ -91,7 +92,7 @@ inline bool make_map(CUtensorMap *out, const void *ptr, int rank, const uint64_t
         estr[i] = 1;
         if (i > 0) gstride[i - 1] = strides_elems[i] * 2;
     }
-    return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(ptr), gdim, gstride, box, estr,
+    return fn(out, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(ptr), gdim, gstride, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -102,7 +103,7 @@ inline bool map_bhld(CUtensorMap *out, const VqTensorDesc &t)
                               static_cast<uint64_t>(t.shape[1]), static_cast<uint64_t>(t.shape[0])};
     const uint64_t str[4] = {1, static_cast<uint64_t>(t.stride[2]), static_cast<uint64_t>(t.stride[1]),
                              static_cast<uint64_t>(t.stride[0])};
-    return make_map(out, t.ptr, 4, dims, str);
+    return make_map(out, t.ptr, 4, dims, str, kBlock, t.dtype == VQ_F16);
 }
 
 struct TcMaps {
@@ -124,7 +125,9 @@ inline int tc_setup(const VqPrefillArgs *a, TcMaps &m, TcParams &p)
         const uint64_t cd[3] = {static_cast<uint64_t>(D), MK, static_cast<uint64_t>(Hkv)};
         const uint64_t cs[3] = {1, static_cast<uint64_t>(D), MK * D};
         const uint64_t vd[3] = {static_cast<uint64_t>(D), MK, static_cast<uint64_t>(B * Hkv) * NB};
-        if (!make_map(&m.cb, a->codebook.ptr, 3, cd, cs) || !make_map(&m.vs, a->vsum.ptr, 3, vd, cs)) return VQ_ELAUNCH;
+        const bool f16 = a->q1.dtype == VQ_F16;
+        if (!make_map(&m.cb, a->codebook.ptr, 3, cd, cs, kBlock, f16) || !make_map(&m.vs, a->vsum.ptr, 3, vd, cs, kBlock, f16))
+            return VQ_ELAUNCH;
         p.MK = static_cast<int>(MK);
         p.NB = static_cast<int>(NB);
         p.cnt = static_cast<const float *>(a->cnt.ptr);
@@ -139,10 +142,11 @@ inline int tc_setup(const VqPrefillArgs *a, TcMaps &m, TcParams &p)
     p.rerope = (a->q2.ptr != a->q1.ptr || a->k3.ptr != a->k1.ptr) ? 1 : 0;
     const float scale = a->scale > 0.f ? a->scale : 1.0f / sqrtf(static_cast<float>(D));
     p.scale_log2 = scale * 1.4426950408889634f;
-    p.out = static_cast<__nv_bfloat16 *>(a->out.ptr);
+    p.out = static_cast<uint16_t *>(a->out.ptr);
     p.o_sb = a->out.stride[0]; p.o_sh = a->out.stride[1]; p.o_sl = a->out.stride[2];
     p.lse2 = static_cast<float *>(a->lse2.ptr);
     p.status = a->status_word;
+    p.wait_limit = wait_limit_cycles();
     return VQ_OK;
 }
 

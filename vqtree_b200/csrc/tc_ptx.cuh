@@ -42,13 +42,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: polls for about two seconds of SM clock, then reports failure.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
+// Bounded wait: polls for `limit` cycles of SM clock (default: about two seconds), then reports failure.
+constexpr long long kDefaultWaitCycles = 4000000000LL;
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, long long limit = kDefaultWaitCycles)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity))
-        if (clock64() - t0 > 4000000000LL) return false;
+        if (clock64() - t0 > limit) return false;
     return true;
 }
 
@@ -111,6 +112,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
 // bits: c_format[4,6)=1(f32)  a_format[7,10)=1(bf16)  b_format[10,13)=1(bf16)  a_major[15]  b_major[16]
 //       n_dim[17,23)=N>>3  m_dim[24,29)=M>>4        (major: 0 = K-major, 1 = MN-major)
 //       a_negate[13]: multiply A by -1
+// idesc_f16kind: the same with A/B both bf16 (ab_format 1) or both IEEE half (ab_format 0).
+__host__ __device__ constexpr uint32_t idesc_f16kind(int M, int N, int a_mn_major, int b_mn_major, uint32_t ab_format)
+{
+    return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+           (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+           (static_cast<uint32_t>(M >> 4) << 24);
+}
 __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major, int a_negate = 0)
 {
     return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_negate) << 13) |
@@ -222,6 +230,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// two fp32 -> packed 16-bit pair in the activation dtype (F16: IEEE half, else bf16)
+template <bool F16> __device__ __forceinline__ uint32_t pack16(float lo, float hi) { return F16 ? pack_f16(lo, hi) : pack_bf16(lo, hi); }
 
 }  // namespace ptx
 }  // namespace vq

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -44,6 +45,9 @@ inline int check_device(const VqTensorDesc *const *ts, int n)
     return VQ_OK;
 }
 
+// Cycles a device-side wait may last before a kernel gives up (set by vqattn_set_wait_limit_cycles).
+long long wait_limit_cycles();
+
 inline int launch_status()
 {
     return cudaGetLastError() == cudaSuccess ? VQ_OK : VQ_ELAUNCH;
@@ -51,9 +55,30 @@ inline int launch_status()
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
 template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+
+// Two packed 16-bit floats <-> two fp32 values, for either 16-bit activation type.
+template <typename T> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 unpack(uint32_t w) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&w)); }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi)
+    {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+};
+template <> struct Pair16<__half> {
+    static __device__ __forceinline__ float2 unpack(uint32_t w) { return __half22float2(*reinterpret_cast<__half2 *>(&w)); }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi)
+    {
+        __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+};
 
 // Reads one code of any supported integer width.
 __device__ __forceinline__ int load_code(const void *base, int dtype, int64_t idx)
@@ -77,6 +102,7 @@ __device__ __forceinline__ void store_code(void *base, int dtype, int64_t idx, i
 }
 
 inline bool is_code_dtype(int dt) { return dt == VQ_U8 || dt == VQ_U16 || dt == VQ_I32 || dt == VQ_I64; }
-inline bool is_act_dtype(int dt) { return dt == VQ_F32 || dt == VQ_BF16; }
+inline bool is_act_dtype(int dt) { return dt == VQ_F32 || dt == VQ_BF16 || dt == VQ_F16; }
+inline bool is_16bit(int dt) { return dt == VQ_BF16 || dt == VQ_F16; }
 
 }  // namespace vq

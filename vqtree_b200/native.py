@@ -6,23 +6,23 @@ module raises at import time - there is no fallback implementation.
 from __future__ import annotations
 
 import ctypes
-import os
 from pathlib import Path
 
 import torch
 
-# VQATTN_LIB overrides the location of the shared library (e.g. an out-of-tree build of the same sources)
-_LIB_PATH = Path(os.environ.get("VQATTN_LIB") or Path(__file__).resolve().parent / "lib" / "libvqattn.so")
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libvqattn.so"
 
 MAX_DIMS = 5
 BLOCK = 128
 
-VQ_F32, VQ_BF16, VQ_U8, VQ_U16, VQ_I32, VQ_I64 = range(6)
-IMPL_AUTO, IMPL_SIMT, IMPL_TENSOR, IMPL_TENSOR_SERIAL, IMPL_TENSOR_TWOSTREAM, IMPL_TENSOR_FOURWAY, IMPL_TENSOR_PAIR = 0, 1, 2, 3, 4, 5, 6
+VQ_F32, VQ_BF16, VQ_U8, VQ_U16, VQ_I32, VQ_I64, VQ_F16 = range(7)
+WORD_TIMEOUT, WORD_BAD_POSITION, WORD_BAD_CODE = 1, 2, 3
+IMPL_AUTO, IMPL_SIMT, IMPL_TENSOR = 0, 1, 2
 
 _DTYPES = {
     torch.float32: VQ_F32,
     torch.bfloat16: VQ_BF16,
+    torch.float16: VQ_F16,
     torch.uint8: VQ_U8,
     torch.uint16: VQ_U16,
     torch.int32: VQ_I32,
@@ -34,6 +34,8 @@ EXPORTS = (
     "vqattn_gather_aggregates", "vqattn_prefill", "vqattn_decode_workspace_bytes", "vqattn_decode",
     "vqattn_cache_advance", "vqattn_decode_static_capacity", "vqattn_decode_static",
     "vqattn_assign_workspace_bytes", "vqattn_assign_codes_ws", "vqattn_rope",
+    "vqattn_status_from_word", "vqattn_set_wait_limit_cycles", "vqattn_wait_selftest", "vqattn_rope_qk",
+    "vqattn_decode_append",
 )
 
 
@@ -96,12 +98,23 @@ def _load() -> ctypes.CDLL:
     lib.vqattn_decode_static.argtypes = [P(VqDecodeArgs), ctypes.c_void_p]
     lib.vqattn_decode_static_capacity.restype = ctypes.c_size_t
     lib.vqattn_cache_advance.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc),
-                                         P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
+                                         P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p, ctypes.c_void_p]
+    lib.vqattn_rope_qk.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                   ctypes.c_int64, ctypes.c_int64, P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc),
+                                   ctypes.c_void_p, ctypes.c_void_p]
+    lib.vqattn_decode_append.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p, ctypes.c_int64,
+                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, P(VqTensorDesc),
+                                         P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int64,
+                                         ctypes.c_void_p, ctypes.c_void_p]
+    lib.vqattn_status_from_word.argtypes = [ctypes.c_int32]
+    lib.vqattn_set_wait_limit_cycles.argtypes = [ctypes.c_int64]
+    lib.vqattn_set_wait_limit_cycles.restype = ctypes.c_int64
+    lib.vqattn_wait_selftest.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.vqattn_rope.argtypes = [P(VqTensorDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                 P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p, ctypes.c_void_p]
     for name in EXPORTS:
         if name not in ("vqattn_status_string", "vqattn_decode_workspace_bytes", "vqattn_decode_static_capacity",
-                        "vqattn_assign_workspace_bytes"):
+                        "vqattn_assign_workspace_bytes", "vqattn_set_wait_limit_cycles"):
             getattr(lib, name).restype = ctypes.c_int
     return lib
 
