@@ -259,6 +259,26 @@ int vqattn_decode_append(const VqTensorDesc *q, const VqTensorDesc *k, const VqT
                          VqTensorDesc *v_win, int64_t row, int32_t *status_word, void *stream);
 
 /*
+ * One generated token in one call: vqattn_decode_append followed by vqattn_decode on the same stream (two
+ * launches).  `decode.q1` / `decode.q2` must describe the [B,Hq,D] views of the scratch tensors q1 / q2
+ * ([B,Hq,1,D]) that the first launch fills, `decode.k1_win` / `k3_win` / `v_win` the window caches the new
+ * key and value are written into at row `row`, and `decode.n_valid` must count that row.  A host keeps one
+ * such struct per layer and changes only q/k/v.ptr, pos, row, n_valid, n_bd and out.ptr from token to token.
+ */
+typedef struct VqDecodeStepArgs {
+    VqTensorDesc q, k, v;        /* the new token: [B,Hq,1,D], [B,Hkv,1,D], [B,Hkv,1,D], un-rotated */
+    const int64_t *positions;    /* device [B] or NULL */
+    int64_t pos;                 /* position of the token when positions is NULL */
+    const float *cos_tab, *sin_tab;
+    int64_t n_pos, const_pos;
+    VqTensorDesc q1, q2;         /* scratch [B,Hq,1,D] */
+    int64_t row;
+    VqDecodeArgs decode;
+} VqDecodeStepArgs;
+
+int vqattn_decode_step(const VqDecodeStepArgs *args, void *stream);
+
+/*
  * Cache advance: folds `n_new` (a multiple of 128 is not required) keys that cross the boundary
  * into the running aggregates of a decode cache.  Stands in for the unfinished
  * ops/attn_vq.py:128-165 VectorQuantizedReRoPECache.update.

@@ -130,12 +130,29 @@ def vq_attention_decode(q1, q2, k1_win, k3_win, v_win, codebook, cnt, vsum, n_va
     return res
 
 
+class DecodeStepCall:
+    """Same interface as ``api.DecodeStepCall``: append, then attention, by the functions above."""
+
+    def __init__(self, q1, q2, win_k1, win_k3, win_v, codebook, cnt, vsum, workspace, const_pos, base, scale):
+        self.q1, self.q2, self.windows = q1, q2, (win_k1, win_k3, win_v)
+        self.far = (codebook, cnt, vsum)
+        self.const_pos, self.base, self.scale = const_pos, base, scale
+
+    def rebind_windows(self, win_k1, win_k3, win_v):
+        self.windows = (win_k1, win_k3, win_v)
+
+    def __call__(self, q, k, v, pos, row, n_valid, n_bd, use_far, positions=None):
+        decode_append(q, k, v, pos, self.const_pos, self.q1, self.q2, *self.windows, row, self.base, positions)
+        cb, cnt, vsum = self.far if use_far else (None, None, None)
+        return vq_attention_decode(self.q1[:, :, 0], self.q2[:, :, 0], *self.windows, cb, cnt, vsum, n_valid, n_bd, self.scale)
+
+
 @contextlib.contextmanager
 def installed():
     """Replaces the kernel-calling functions of ``vqtree_b200.api`` for the duration of the context."""
     from vqtree_b200 import api
     names = ("rope_qk", "decode_append", "assign_codes", "cache_advance", "vq_attention_prefill", "prefill_from_aggregates",
-             "decode_workspace", "vq_attention_decode")
+             "decode_workspace", "vq_attention_decode", "DecodeStepCall")
     saved = {n: getattr(api, n) for n in names}
     try:
         for n in names:

@@ -322,6 +322,72 @@ def vq_attention_decode(q1, q2, k1_win, k3_win, v_win, codebook, cnt, vsum, n_va
     return out
 
 
+class DecodeStepCall:
+    """The argument block of ``vqattn_decode_step`` for one layer of a cache, kept between tokens: the host fills
+    the descriptors of the caches once and changes a handful of fields per token, so that generating a token costs
+    one call into the library (two kernel launches: rotate-and-append, attention)."""
+
+    def __init__(self, q1, q2, win_k1, win_k3, win_v, codebook, cnt, vsum, workspace, const_pos: int, base: float,
+                 scale: float):
+        self.dev = _require_cuda(q1, q2, win_k1, win_k3, win_v, codebook, cnt, vsum, workspace)
+        self.base, self.far_tensors = base, (codebook, cnt, vsum)
+        self.keep = (q1, q2, win_k1, win_k3, win_v, workspace)
+        a = self.args = native.VqDecodeStepArgs()
+        desc(q1, a.q1)
+        desc(q2, a.q2)
+        a.const_pos = int(const_pos)
+        d = a.decode
+        desc(q1[:, :, 0], d.q1)
+        desc(q2[:, :, 0], d.q2)
+        self.rebind_windows(win_k1, win_k3, win_v)
+        desc(codebook, d.codebook)
+        desc(cnt, d.cnt)
+        desc(vsum, d.vsum)
+        d.scale = float(scale)
+        d.workspace = workspace.data_ptr()
+        d.workspace_bytes = workspace.numel() * workspace.element_size()
+        d.status_word = device_status_word(self.dev).data_ptr()
+        self._tables(max(const_pos + 1, 2))
+        self._in = None
+
+    def _tables(self, n_pos):
+        D = self.keep[0].shape[-1]
+        self.cos, self.sin = rope_tables(n_pos, D, self.dev, self.base)
+        a = self.args
+        a.cos_tab, a.sin_tab, a.n_pos = self.cos.data_ptr(), self.sin.data_ptr(), self.cos.shape[0]
+
+    def rebind_windows(self, win_k1, win_k3, win_v):
+        """The window views moved (a block left the window, or the buffers were compacted)."""
+        d = self.args.decode
+        desc(win_k1, d.k1_win)
+        desc(win_k3, d.k3_win)
+        desc(win_v, d.v_win)
+        self.windows = (win_k1, win_k3, win_v)
+
+    def __call__(self, q, k, v, pos: int, row: int, n_valid: int, n_bd: int, use_far: bool, positions=None):
+        a = self.args
+        B, Hq, _, D = q.shape
+        out = torch.empty((B, Hq, D), dtype=q.dtype, device=self.dev)
+        sig = (q.shape, q.stride(), k.stride(), v.stride())
+        if self._in != sig:                      # layout of the new token's tensors: usually the same every step
+            desc(q, a.q)
+            desc(k, a.k)
+            desc(v, a.v)
+            desc(out, a.decode.out)
+            self._in = sig
+        else:
+            a.q.ptr, a.k.ptr, a.v.ptr, a.decode.out.ptr = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+        if pos + 1 > a.n_pos:
+            self._tables(pos + 1)
+        a.positions = positions.data_ptr() if positions is not None else None
+        a.pos, a.row = int(pos), int(row)
+        d = a.decode
+        d.n_valid, d.n_bd, d.use_far = int(n_valid), int(n_bd), 1 if use_far else 0
+        with torch.cuda.device(self.dev):
+            check(lib.vqattn_decode_step(ctypes.byref(a), stream_ptr(self.dev)), "vqattn_decode_step")
+        return out
+
+
 def cache_advance(codes, v_new, K: int, cnt, vsum_f32, vsum_act=None):
     """Fold keys that crossed the boundary into a decode cache's aggregates (in place)."""
     dev = _require_cuda(codes, v_new, cnt, vsum_f32, vsum_act)

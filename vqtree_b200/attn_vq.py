@@ -182,18 +182,37 @@ class VectorQuantizedReRoPECache(_HFCache):
         self.states[layer_idx] = dict(
             n=num_tokens, bd=num_tokens - n_local, start=0, cap=cap, win_k1=bufs[0], win_k3=bufs[1], win_v=bufs[2],
             cnt=cumulated_key.float().contiguous(), vsum32=vs32, vsum=None if dt == torch.float32 else vs32.to(dt),
-            q1=None, q2=None, ws=None, out=None)
+            q1=None, q2=None, call=None)
         if layer_idx == 0:
             self.seen_tokens += num_tokens
 
-    def _make_room(self, st):
-        """Moves the live window back to the front of its buffers when the next block would not fit."""
-        live = st["n"] - st["bd"]
+    def _admit(self, st, dev):
+        """Makes room for the token at position ``st["n"]``: when it crosses a 128-block boundary the 128 oldest
+        window keys are quantised and folded into the aggregates first.  Returns its buffer row."""
+        W = self.window_length
+        i = st["n"]
+        bd = max(0, (i - W) // BLOCK_SIZE * BLOCK_SIZE)
+        moved = False
+        if bd > st["bd"]:
+            assert bd == st["bd"] + BLOCK_SIZE
+            K = self.codebooks.shape[2]
+            s0 = st["start"]
+            codes = api.assign_codes(st["win_k3"][:, :, s0: s0 + BLOCK_SIZE], self.codebooks_f32(dev))
+            api.cache_advance(codes, st["win_v"][:, :, s0: s0 + BLOCK_SIZE], K, st["cnt"], st["vsum32"], st["vsum"])
+            st["start"] += BLOCK_SIZE
+            st["bd"] = bd
+            moved = True
+        live = i - st["bd"]
         if st["start"] + live + BLOCK_SIZE + 1 > st["cap"]:
-            for name in ("win_k1", "win_k3", "win_v"):
+            for name in ("win_k1", "win_k3", "win_v"):      # slide the live window back to the front of its buffer
                 buf = st[name]
                 buf[:, :, :live] = buf[:, :, st["start"]: st["start"] + live].clone()
             st["start"] = 0
+            moved = True
+        if moved and st.get("call") is not None:
+            s0 = st["start"]
+            st["call"].rebind_windows(*(st[n][:, :, s0:] for n in ("win_k1", "win_k3", "win_v")))
+        return st["start"] + live
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
                cache_kwargs: Optional[Dict[str, Any]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -201,27 +220,16 @@ class VectorQuantizedReRoPECache(_HFCache):
         calls it, ops/attn_vq.py:458): ``key_states`` / ``value_states`` [B,Hkv,1,D] are the RAW key and the
         value; ``cache_kwargs`` must hold ``query`` [B,Hq,1,D] (raw) and may hold ``position_ids`` [B,1] and
         ``rope_base``.  When the token crosses a 128-block boundary the 128 oldest window keys are quantised
-        and folded into the aggregates first.  Returns the window's rotated keys and values."""
+        and folded into the aggregates first.  Returns the window's rotated keys and values; the rotated
+        queries are left in the layer state (``q1``, ``q2``)."""
         st = self.states[layer_idx]
         W = self.window_length
         kw = cache_kwargs or {}
         i = st["n"]                                         # position of the new token
-        H, M, K, D = self.codebooks.shape
-        dev = key_states.device
-        bd = max(0, (i - W) // BLOCK_SIZE * BLOCK_SIZE)
-        if bd > st["bd"]:
-            assert bd == st["bd"] + BLOCK_SIZE
-            s0 = st["start"]
-            old_k3 = st["win_k3"][:, :, s0: s0 + BLOCK_SIZE]
-            codes = api.assign_codes(old_k3, self.codebooks_f32(dev))
-            api.cache_advance(codes, st["win_v"][:, :, s0: s0 + BLOCK_SIZE], K, st["cnt"], st["vsum32"], st["vsum"])
-            st["start"] += BLOCK_SIZE
-            st["bd"] = bd
-        self._make_room(st)
+        r = self._admit(st, key_states.device)
         q = kw["query"]
         if st["q1"] is None:
-            st["q1"], st["q2"] = torch.empty_like(q, memory_format=torch.contiguous_format), torch.empty_like(q, memory_format=torch.contiguous_format)
-        r = st["start"] + i - bd                            # buffer row of the new key
+            st["q1"], st["q2"] = (torch.empty(q.shape, dtype=q.dtype, device=q.device) for _ in range(2))
         pos_t = kw.get("position_ids")
         base = kw.get("rope_base") or self.rope_base or 10000.0
         api.decode_append(q, key_states, value_states, i, W + 1, st["q1"], st["q2"], st["win_k1"], st["win_k3"], st["win_v"],
@@ -342,30 +350,30 @@ def decode_step(query_states, key_states, value_states, position_ids, past_key_v
                 layer_idx: int = 0, rope_base: Optional[float] = None):
     """One generated token (seqlen_q == 1): the decode kernel the reference's README names, on the cache
     this module maintains.  query_states [B,Hq,1,D], key/value_states [B,Hkv,1,D] (un-rotated), position_ids
-    [B,1] or None (the cache's own count).  Two launches in the steady state (rotate-and-append, attention);
-    two more every 128 tokens when a block leaves the window.  Returns [B, 1, Hq*D]."""
+    [B,1] or None (the cache's own count).  One call into the library, two launches (rotate-and-append,
+    attention); two more every 128 tokens when a block leaves the window.  Returns [B, 1, Hq*D]."""
     st = past_key_value.states[layer_idx]
     W = past_key_value.window_length
     bsz, hq, _, d = query_states.shape
     hkv = key_states.shape[1]
-    past_key_value.update(key_states, value_states, layer_idx,
-                          {"query": query_states, "position_ids": position_ids, "rope_base": _rope_base(past_key_value, rope_base)})
-    i = st["n"] - 1
-    bd, s0 = st["bd"], st["start"]
-    far = bd > 0
     dev = query_states.device
-    if st["ws"] is None:
-        st["ws"] = api.decode_workspace(bsz, hq, hkv, d, dev)
-        st["out"] = torch.empty(bsz, hq, d, dtype=query_states.dtype, device=dev)
-    cap_view = slice(s0, st["cap"])
-    vs = st["vsum"] if st["vsum"] is not None else st["vsum32"]
-    api.vq_attention_decode(st["q1"][:, :, 0], st["q2"][:, :, 0], st["win_k1"][:, :, cap_view], st["win_k3"][:, :, cap_view],
-                            st["win_v"][:, :, cap_view],
-                            past_key_value.codebook_act(query_states.dtype, dev) if far else None,
-                            st["cnt"] if far else None, vs if far else None,
-                            n_valid=i - bd + 1, n_bd=max(0, i - W) - bd, scale=1.0 / math.sqrt(d), workspace=st["ws"],
-                            out=st["out"])
-    return st["out"].reshape(bsz, 1, hq * d)
+    if st["call"] is None:
+        dt = query_states.dtype
+        st["q1"], st["q2"] = (torch.empty(bsz, hq, 1, d, dtype=dt, device=dev) for _ in range(2))
+        s0 = st["start"]
+        st["call"] = api.DecodeStepCall(
+            st["q1"], st["q2"], *(st[n][:, :, s0:] for n in ("win_k1", "win_k3", "win_v")),
+            past_key_value.codebook_act(dt, dev), st["cnt"], st["vsum"] if st["vsum"] is not None else st["vsum32"],
+            api.decode_workspace(bsz, hq, hkv, d, dev), W + 1, _rope_base(past_key_value, rope_base), 1.0 / math.sqrt(d))
+    i = st["n"]
+    r = past_key_value._admit(st, dev)
+    bd = st["bd"]
+    pos_t = position_ids.reshape(-1).to(torch.int64).contiguous() if position_ids is not None else None
+    out = st["call"](query_states, key_states, value_states, i, r - st["start"], i - bd + 1, max(0, i - W) - bd, bd > 0, pos_t)
+    st["n"] = i + 1
+    if layer_idx == 0:
+        past_key_value.seen_tokens += 1
+    return out.reshape(bsz, 1, hq * d)
 
 
 def dispatch_attn_impl(query_states, key_states, value_states, position_ids, past_key_value: VectorQuantizedReRoPECache,

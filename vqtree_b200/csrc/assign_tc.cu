@@ -20,13 +20,21 @@
 //      eps_m = (4 + D/64 + (2 or 3) D/32 + 1.1 m) 2^-18, one unit above that.
 //      A key whose best approximate score leads the runner-up by more than thr = 2 eps |r| max|C_m|
 //      has a unique arg-max: that code is final.
-//   3. The other keys (a few per cent for random data) are settled exactly on the spot: every
-//      (key, candidate code within thr of the best) pair of a warp gets a lane, which runs the
-//      defining fp32 chain from global memory; first maximum wins.
-// One CTA owns NS key tiles of 128 keys ("streams", NS = 2 when K <= 256): per stream four warps
-// with one key per thread scan the scores in tensor memory; one warp issues the MMAs of the
-// streams in turn, so the scan of one stream overlaps the MMAs of the other; one warp issues the
-// TMA loads of the codebook terms (16 KB units, 6-slot ring).  Every wait is bounded.
+//   3. The other keys (well under one per cent of the (key, codebook) pairs for random data) keep the
+//      approximate winner for the time being.  Their candidates - the codes whose approximate score is
+//      within thr of the best; the exact arg-max is among them - are written to a record (up to four codes;
+//      more, as for an all-zero key, means "all of them"), the records of a key are chained, and the key
+//      goes on a work list.  A second, small kernel (assign_repair_kernel) walks the list: it follows the
+//      key through the codebooks with the defining fp32 arithmetic, runs the defining chain for the
+//      candidates of every doubtful codebook (first maximum wins), and - in the rare case that this changes
+//      a code - recomputes every later codebook of that key over all its codewords, since its residual
+//      changed.  The scan kernel never waits for any of this.
+// One CTA owns NS key tiles of 128 keys ("streams", NS = 2 when K <= 256): per stream eight warps,
+// two threads per key, each ranking half of the key's scores in tensor memory and updating half of
+// its residual row (the arithmetic between the MMAs is a chain of dependent instructions and loads
+// from L2: it needs the warps to hide its latency); one warp issues the MMAs of the streams in turn,
+// so the scan of one stream overlaps the MMAs of the other; one warp issues the TMA loads of the
+// codebook terms (16 KB units, 5-slot ring).  Every wait is bounded.
 #include "prefill_tc_common.cuh"
 
 namespace vq {
@@ -36,16 +44,17 @@ using namespace ptx;
 constexpr int kAtMinChunk = 128;   // codewords per MMA chunk: 128, or 256 (one N = 256 instruction) when K allows
 constexpr int kAtMaxM = 8;
 constexpr int kAtMaxK = 512;
-constexpr int kAtPairCap = 32;     // (key, candidate) pairs re-scored per pass of a warp
-constexpr int kAtLanesPerPair = 8;  // ... eight lanes per pair when there are at most four
+constexpr int kAtRepairWarps = 4;  // warps per CTA of the repair kernel (one doubtful key per warp at a time)
 
 // ------------------------------------------------------------------------------------------------
-// fp32 codebook -> bf16 hi / lo terms [Hkv, M*K, D] and the largest row norm of every codebook.
+// fp32 codebook -> bf16 hi / lo terms [Hkv, M*K, D], the squared norm of every row and the largest row
+// norm of every codebook.
 __global__ void __launch_bounds__(256)
 split_codebook_kernel(const float *__restrict__ cb, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo,
-                      float *__restrict__ cmax, int K, int D)
+                      float *__restrict__ cmax, float *__restrict__ cn2, unsigned int *__restrict__ work_count, int K, int D)
 {
     __shared__ float s_max[8];
+    if (blockIdx.x == 0 && threadIdx.x < 2) work_count[threadIdx.x] = 0u;   // the scan kernel that follows fills the lists
     const int hm = blockIdx.x;  // h * M + m
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float wmax = 0.f;
@@ -62,6 +71,7 @@ split_codebook_kernel(const float *__restrict__ cb, __nv_bfloat16 *__restrict__ 
         }
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if (lane == 0) cn2[row] = ss;
         wmax = fmaxf(wmax, sqrtf(ss));
     }
     if (lane == 0) s_max[warp] = wmax;
@@ -79,6 +89,7 @@ struct AtParams {
     const float *cb;     // [Hkv, M, K, D]
     const float *bias;   // nullptr or [Hkv, M, K]
     const float *cmax;   // [Hkv, M]
+    const float *cn2;    // [Hkv, M*K] squared row norms
     void *codes;
     int code_dtype;
     int64_t c_sb, c_sh, c_sl;
@@ -86,6 +97,10 @@ struct AtParams {
     int64_t L;
     int32_t *status;
     long long wait_limit;  // cycles a device-side wait may last before the kernel gives up
+    uint4 *work;                // doubtful keys: {key index lo, hi, last record, doubtful codebooks | brute-force codebooks << 8}
+    uint4 *pool;                // candidate records: {previous record of the key, m | n << 8, codes 0-1, codes 2-3}
+    unsigned int *counters;     // [0] entries in `work`, [1] records in `pool` (zeroed by split_codebook_kernel)
+    unsigned int pool_cap;
 };
 
 template <int D, int NS, int CH>
@@ -93,15 +108,16 @@ struct AtCfg {
     static constexpr int NH = D / 64;
     static constexpr int kATile = NH * kHalfBytes;     // 128 keys x D bf16 (one term of the residual)
     static constexpr int kUnit = CH * 64 * 2;          // CH codewords x 64 columns of one term: one ring slot
-    static constexpr int kSlots = 96 * 1024 / kUnit;   // 96 KB of ring
+    static constexpr int kSlots = 80 * 1024 / kUnit;   // 80 KB of ring
     static constexpr int kB = NS * 2 * kATile;         // per stream: Rh then Rl
     static constexpr int kTotal = kB + kSlots * kUnit + 1024;
     static constexpr int kRegion = NS == 2 ? 256 : 512;  // score columns of a stream in tensor memory
     static constexpr int kMaxChunks = kRegion / CH;
     static constexpr int kGroupsPerChunk = CH / 32;
     static constexpr int kMaxGroups = kRegion / 32;
-    static constexpr int kWarpMma = 4 * NS, kWarpTma = 4 * NS + 1;
-    static constexpr int kThreads = (4 * NS + 2) * 32;
+    static constexpr int kScanWarps = 8;               // per stream: two threads per key
+    static constexpr int kWarpMma = kScanWarps * NS, kWarpTma = kScanWarps * NS + 1;
+    static constexpr int kThreads = (kScanWarps * NS + 2) * 32;
 };
 
 // Largest (hi) and second largest (lo) of 32 values: pairs, then merges of (hi, lo) pairs.
@@ -155,9 +171,10 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(8) uint64_t bar_k[NS], bar_q[NS], bar_c[NS][C::kMaxChunks], b_full[SL], b_free[SL];
+    __shared__ __align__(8) uint64_t x_half[NS][4], x_done[NS][4];   // hand-offs between the two warps of a lane quarter
+    __shared__ __align__(16) float4 s_x[NS][kBlock];                  // per key: what its two threads tell each other
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
-    __shared__ uint16_t s_pairs[4 * NS][kAtPairCap];  // per scan warp: (owner lane << 9) | candidate code
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int u = blockIdx.y, b = u / p.Hkv, h = u % p.Hkv;
@@ -169,7 +186,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (tid == 0) {
         for (int i = 0; i < NS; ++i) {
             mbar_init(&bar_k[i], 1);
-            mbar_init(&bar_q[i], 128);
+            mbar_init(&bar_q[i], 32 * C::kScanWarps);
+            for (int qd = 0; qd < 4; ++qd) {
+                mbar_init(&x_half[i][qd], 1);
+                mbar_init(&x_done[i][qd], 1);
+            }
             for (int c = 0; c < C::kMaxChunks; ++c) mbar_init(&bar_c[i][c], 1);
         }
         for (int i = 0; i < SL; ++i) {
@@ -265,29 +286,31 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 }
             if (!ok) s_err = 1;
         }
-    } else if ((warp >> 2) < n_act) {
-        // ============================================================ scan warps: one key per thread
-        // Loops are kept rolled on purpose: the warps of the two streams run different phases of this
-        // code at the same time, and it has to stay inside the instruction cache.
+    } else if (warp / C::kScanWarps < n_act) {
+        // ============================================================ scan warps: two threads per key
+        // Thread (hf, row) ranks the groups [hf * groups / 2, (hf + 1) * groups / 2) of its key's scores and
+        // updates half hf of its residual row; the two meet through shared memory once per codebook.
         constexpr unsigned kAll = 0xffffffffu;
-        const int s = warp >> 2, wq = warp & 3;
+        const int s = warp / C::kScanWarps, hf = (warp >> 2) & 1, wq = warp & 3;
         const int row = wq * 32 + lane;
         const int64_t j0 = static_cast<int64_t>(tile0 + s) * kBlock;
         const int64_t j = j0 + row;
         const bool valid = j < p.L;
         const uint32_t tbase = tmem + (static_cast<uint32_t>(wq * 32) << 16) + s * C::kRegion;
-        const __nv_bfloat16 *kbase = p.k + b * p.k_sb + h * p.k_sh;
-        const __nv_bfloat16 *krow = kbase + (valid ? j : 0) * p.k_sl;
         const float *cbh = p.cb + static_cast<int64_t>(h) * MK * D;
         uint8_t *a_rh = smem + s * 2 * C::kATile, *a_rl = a_rh + C::kATile;
-        const int groups = K / 32;
+        const int groups = K / 32, g_lo = hf * (groups / 2), g_hi = g_lo + groups / 2;
+        float4 *xch = &s_x[s][row];
         float rbound;  // |k| + sum of the largest codeword norms so far: a priori bound of the residual's norm
-        float rnow;    // bound of the current residual's norm from the residual itself (tighter)
+        float rnow;    // bound of the current residual's norm (tighter): see the residual update below
+        bool ok = __all_sync(kAll, mbar_wait(&bar_k[s], 0, p.wait_limit));
         {
+            // |k| from the key tile the TMA load put into shared memory (this thread's row, 16-byte chunks in the
+            // 128-byte swizzle: eight consecutive rows read eight different chunks, so the reads do not collide)
             float ss = 0.f;
 #pragma unroll 4
-            for (int d = 0; d < D; d += 8) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(krow + d);
+            for (int ck = 0; ck < D / 8; ++ck) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(a_rh + (ck >> 3) * kHalfBytes + row * 128 + (((ck & 7) ^ (row & 7)) << 4));
                 const __nv_bfloat162 *hp = reinterpret_cast<const __nv_bfloat162 *>(&raw);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -298,26 +321,23 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             rbound = sqrtf(ss) * 1.0001f;
             rnow = rbound;
         }
-        bool ok = true;
-        int prev[kAtMaxM];
-#pragma unroll
-        for (int mm = 0; mm < kAtMaxM; ++mm) prev[mm] = 0;
+        uint32_t doubt = 0;   // bit m: the lead of codebook m's best score did not prove its arg-max (bit 8 + m: no record)
+        uint32_t last_rec = 0xffffffffu;   // the key's most recent candidate record
         for (int m = 0; m < M && ok; ++m) {
             const float cm = p.cmax[h * M + m];
             // eps of this codebook in units of 2^-18: the terms listed at the top of the file plus one unit of slack
             const float eps_m = (4.f + D / 64 + (m > 0 ? 3 : 2) * (D / 32) + 1.1f * m) * 3.814697265625e-6f;
             const float thr0 = 2.f * eps_m * rnow * cm + 1e-30f;
             const float *bm = p.bias ? p.bias + (static_cast<int64_t>(h) * M + m) * K : nullptr;
-            // ---- scan, chunk by chunk as the tensor pipe finishes them: best and runner-up of the tagged
-            // scores (the tag of the best gives its index inside its group of 32).  gbits marks the groups
-            // whose maximum was within the threshold of the running best: a superset of the groups that
-            // can hold a candidate at the end.
+            // ---- scan of this thread's groups, chunk by chunk as the tensor pipe finishes them: best and runner-up
+            // of the tagged scores (the tag of the best gives its index inside its group of 32)
             float best = -INFINITY, second = -INFINITY;
-            int bgrp = 0;
-            uint32_t gbits = 0;
+            int bgrp = g_lo;
+            uint32_t gbits = 0;   // groups whose maximum came within the threshold of the running best: a superset of
+                                  // the groups that can hold a candidate at the end
 #pragma unroll 1
-            for (int g = 0; g < groups && ok; ++g) {
-                if (g % C::kGroupsPerChunk == 0) {
+            for (int g = g_lo; g < g_hi && ok; ++g) {
+                if (g == g_lo || g % C::kGroupsPerChunk == 0) {
                     ok = __all_sync(kAll, mbar_wait(&bar_c[s][g / C::kGroupsPerChunk], m & 1, p.wait_limit));
                     tc_fence_after();
                     if (!ok) break;
@@ -336,158 +356,94 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 gbits |= (hi >= best - thr_g ? 1u : 0u) << g;
             }
             if (!ok) break;
-            int code = bgrp * 32 + 31 - static_cast<int>(__float_as_uint(best) & 31u);  // first group holding the maximum
-            const float thr = bm ? thr0 + fabsf(best) * 4.76837158203125e-7f : thr0;
-            const bool flagged = valid && !(best - second > thr);
-            if (__ballot_sync(kAll, flagged)) {
-                // ---- exact settlement of the warp's doubtful keys: every (key, candidate code) pair gets a
-                // lane; pairs are collected in a list and re-scored whenever it is full, and at the end
-                const float cut = best - thr;
-                float bv = -INFINITY;
-                int bi = 0x7fffffff;
-                uint16_t *list = s_pairs[warp];
-                int n = 0;  // pairs in the list (same in all lanes)
+            // ---- the two halves meet: the upper half hands its result over, the lower half merges (a tie between
+            // the halves goes to the lower one, which holds the lower codes) and hands the verdict back
+            int code;
+            if (hf == 1) {
+                *xch = make_float4(best, second, __int_as_float(bgrp), __uint_as_float(gbits));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&x_half[s][wq]);
+                ok = __all_sync(kAll, mbar_wait(&x_done[s][wq], m & 1, p.wait_limit));
+                if (!ok) break;
+                const float4 r = *xch;
+                best = r.x;
+                code = __float_as_int(r.y);
+            } else {
+                ok = __all_sync(kAll, mbar_wait(&x_half[s][wq], m & 1, p.wait_limit));
+                if (!ok) break;
+                const float4 o = *xch;
+                second = fmax3(second, fminf(best, o.x), o.y);
+                if (o.x > best) {
+                    best = o.x;
+                    bgrp = __float_as_int(o.z);
+                }
+                code = bgrp * 32 + 31 - static_cast<int>(__float_as_uint(best) & 31u);  // first group holding the maximum
+                *xch = make_float4(best, __int_as_float(code), 0.f, 0.f);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&x_done[s][wq]);
+                // with a bias the fp32 additions s + bias round by up to 2^-24 |s + bias| each
+                const float thr = bm ? thr0 + fabsf(best) * 4.76837158203125e-7f : thr0;
+                const bool dflag = valid && !(best - second > thr);
+                if (__ballot_sync(kAll, dflag)) {
+                    // ---- some key of this warp is doubtful: its candidates (scores within thr of the best) go into a
+                    // record for the repair kernel; carry on with the approximate winner.  Tensor-memory loads are
+                    // warp-wide, so the warp re-reads the union of its doubtful keys' marked groups.
+                    const uint32_t gb = dflag ? (gbits | __float_as_uint(o.w)) : 0u;
+                    const uint32_t un = __reduce_or_sync(kAll, gb);
+                    const float cut = best - thr;
+                    int n = 0;
+                    uint32_t c01 = 0, c23 = 0;
 #pragma unroll 1
-                for (int g = 0; g <= groups; ++g) {
-                    const bool flush = g == groups;
-                    uint32_t bits = 0;  // this thread's candidates inside group g
-                    if (!flush) {
-                        const bool cg = flagged && ((gbits >> g) & 1u);
-                        if (!__ballot_sync(kAll, cg)) continue;
+                    for (int g = 0; g < groups; ++g) {
+                        if (!((un >> g) & 1u)) continue;
+                        if (!__all_sync(kAll, mbar_wait(&bar_c[s][g / C::kGroupsPerChunk], m & 1, p.wait_limit))) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
                         float v[32];
                         load_scores(tbase + 32 * g, bm, 32 * g, v);
+                        if ((gb >> g) & 1u) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (v[i] >= cut) bits |= 1u << i;
-                        bits = cg ? bits : 0u;
+                            for (int i = 0; i < 32; ++i)
+                                if (v[i] >= cut) {
+                                    const uint32_t c = static_cast<uint32_t>(g * 32 + i);
+                                    if (n < 2) c01 |= c << (16 * n);
+                                    else if (n < 4) c23 |= c << (16 * (n - 2));
+                                    ++n;
+                                }
+                        }
                     }
-                    for (;;) {
-                        const int cnt = __popc(bits);
-                        int incl = cnt;
-#pragma unroll
-                        for (int off = 1; off < 32; off <<= 1) {
-                            const int t = __shfl_up_sync(kAll, incl, off);
-                            if (lane >= off) incl += t;
+                    if (!ok) break;
+                    if (dflag) {
+                        const unsigned int at = atomicAdd(p.counters + 1, 1u);
+                        if (at < p.pool_cap) {
+                            p.pool[at] = make_uint4(last_rec, static_cast<uint32_t>(m) | (static_cast<uint32_t>(n > 4 ? 255 : n) << 8), c01, c23);
+                            last_rec = at;
+                            doubt |= 1u << m;
+                        } else {
+                            doubt |= 0x100u << m;   // no room for the record: the repair kernel scores every code of this codebook
                         }
-                        const int total = __shfl_sync(kAll, incl, 31);
-                        if (total == 0 && !(flush && n > 0)) break;
-                        int q = n + incl - cnt;
-                        while (bits != 0 && q < kAtPairCap) {
-                            const int bit = __ffs(bits) - 1;
-                            list[q++] = static_cast<uint16_t>((lane << 9) | (g * 32 + bit));
-                            bits &= bits - 1;
-                        }
-                        n = min(kAtPairCap, n + total);
-                        if (n < kAtPairCap && !flush) break;  // room left: collect from the next group first
-                        __syncwarp();
-                        // A few pairs (the usual case): eight lanes per pair, each loads one eighth of the rows (all
-                        // loads in flight at once) and the FMA chain walks from lane to lane in d order.  Many pairs:
-                        // one lane per pair.
-                        const bool few = n <= 32 / kAtLanesPerPair;
-                        const int slot = few ? lane / kAtLanesPerPair : lane;   // pair of this lane
-                        const bool act = slot < n;
-                        int owner = lane, c = 0;
-                        if (act) {
-                            const int e = list[slot];
-                            owner = e >> 9;
-                            c = e & 511;
-                        }
-                        int pv[kAtMaxM];
-#pragma unroll
-                        for (int mm = 0; mm < kAtMaxM; ++mm) pv[mm] = (mm < m) ? __shfl_sync(kAll, prev[mm], owner) : 0;
-                        float sc = -INFINITY;
-                        // the defining chain: r_m = ((k - C_0[c_0]) - C_1[c_1]) - ..., one FMA chain over d
-                        const __nv_bfloat16 *ks = kbase + (j0 + wq * 32 + owner) * p.k_sl;
-                        const float *cc = cbh + (static_cast<int64_t>(m) * K + c) * D;
-                        auto residual4 = [&](int d) {
-                            const uint2 raw = *reinterpret_cast<const uint2 *>(ks + d);
-                            const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.x);
-                            const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162 *>(&raw.y);
-                            float4 r4 = make_float4(__low2float(lo2), __high2float(lo2), __low2float(hi2), __high2float(hi2));
-#pragma unroll
-                            for (int mm = 0; mm < kAtMaxM; ++mm)
-                                if (mm < m) {
-                                    const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(mm) * K + pv[mm]) * D + d));
-                                    r4.x = __fsub_rn(r4.x, c4.x);
-                                    r4.y = __fsub_rn(r4.y, c4.y);
-                                    r4.z = __fsub_rn(r4.z, c4.z);
-                                    r4.w = __fsub_rn(r4.w, c4.w);
-                                }
-                            return r4;
-                        };
-                        if (few) {
-                            constexpr int SEG = D / kAtLanesPerPair, STEPS = SEG / 4;  // columns / float4 steps of a lane
-                            const int q = lane % kAtLanesPerPair;
-                            float4 r4[STEPS], c4[STEPS];
-                            if (act) {
-#pragma unroll
-                                for (int st = 0; st < STEPS; ++st) {
-                                    r4[st] = residual4(SEG * q + 4 * st);
-                                    c4[st] = __ldg(reinterpret_cast<const float4 *>(cc + SEG * q + 4 * st));
-                                }
-                            } else {
-#pragma unroll
-                                for (int st = 0; st < STEPS; ++st) r4[st] = c4[st] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-                            float acc = 0.f;
-#pragma unroll 1
-                            for (int seg = 0; seg < kAtLanesPerPair; ++seg) {
-                                if (q == seg) {
-#pragma unroll
-                                    for (int st = 0; st < STEPS; ++st) {
-                                        acc = __fmaf_rn(r4[st].x, c4[st].x, acc);
-                                        acc = __fmaf_rn(r4[st].y, c4[st].y, acc);
-                                        acc = __fmaf_rn(r4[st].z, c4[st].z, acc);
-                                        acc = __fmaf_rn(r4[st].w, c4[st].w, acc);
-                                    }
-                                }
-                                acc = __shfl_sync(kAll, acc, (lane & ~(kAtLanesPerPair - 1)) | seg);
-                            }
-                            if (act) sc = bm ? __fadd_rn(acc, __ldg(bm + c)) : acc;
-                        } else if (act) {
-                            float acc = 0.f;
-#pragma unroll 8
-                            for (int d = 0; d < D; d += 4) {
-                                const float4 r4 = residual4(d);
-                                const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cc + d));
-                                acc = __fmaf_rn(r4.x, c4.x, acc);
-                                acc = __fmaf_rn(r4.y, c4.y, acc);
-                                acc = __fmaf_rn(r4.z, c4.z, acc);
-                                acc = __fmaf_rn(r4.w, c4.w, acc);
-                            }
-                            sc = bm ? __fadd_rn(acc, __ldg(bm + c)) : acc;
-                        }
-                        __syncwarp();
-                        const int stride = few ? kAtLanesPerPair : 1;
-#pragma unroll 1
-                        for (int t = 0; t < n; ++t) {
-                            const int ot = __shfl_sync(kAll, owner, t * stride), ct = __shfl_sync(kAll, c, t * stride);
-                            const float st = __shfl_sync(kAll, sc, t * stride);
-                            if (lane == ot && (st > bv || (st == bv && ct < bi))) {
-                                bv = st;
-                                bi = ct;
-                            }
-                        }
-                        n = 0;
                     }
                 }
-                if (flagged && bi != 0x7fffffff) code = bi;
+                if (valid) store_code(p.codes, p.code_dtype, b * p.c_sb + h * p.c_sh + j * p.c_sl + m, code);
             }
-#pragma unroll
-            for (int mm = 0; mm < kAtMaxM; ++mm)
-                if (mm == m) prev[mm] = code;
-            if (valid) store_code(p.codes, p.code_dtype, b * p.c_sb + h * p.c_sh + j * p.c_sl + m, code);
             rbound += cm;
             if (m + 1 < M) {
                 // ---- residual -= C_m[code], re-split into bf16 hi / lo in the 128B-swizzled operand layout.
-                // Every thread updates its own key's row, 8 columns (one 16-byte chunk of each term) at a time.
-                const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D;
+                // This thread updates half hf of its key's row, 8 columns (one 16-byte chunk of each term) at a time;
+                // its part of the codebook row is loaded first (independent 16-byte loads, all in flight: the rows
+                // of a tile's keys are scattered over the codebook, every load is a trip to L2).
+                constexpr int CPT = D / 16;                    // 16-byte chunks per thread
+                const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D + hf * (D / 2);
                 const uint32_t rbase = row * 128;
-                float ss = 0.f;  // squared norm of the new residual
-#pragma unroll 16
-                for (int ck = 0; ck < D / 8; ++ck) {
-                    const float4 ca = __ldg(reinterpret_cast<const float4 *>(crow + 8 * ck));
-                    const float4 cb4 = __ldg(reinterpret_cast<const float4 *>(crow + 8 * ck + 4));
+                float4 crow4[2 * CPT];
+#pragma unroll
+                for (int i = 0; i < 2 * CPT; ++i) crow4[i] = __ldg(reinterpret_cast<const float4 *>(crow + 4 * i));
+#pragma unroll
+                for (int cc = 0; cc < CPT; ++cc) {
+                    const int ck = hf * CPT + cc;
+                    const float4 ca = crow4[2 * cc], cb4 = crow4[2 * cc + 1];
                     const uint32_t off = (ck >> 3) * kHalfBytes + rbase + (((ck & 7) ^ (row & 7)) << 4);
                     uint4 *ph = reinterpret_cast<uint4 *>(a_rh + off);
                     uint4 *pl = reinterpret_cast<uint4 *>(a_rl + off);
@@ -510,8 +466,6 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     }
                     x[0] -= ca.x; x[1] -= ca.y; x[2] -= ca.z; x[3] -= ca.w;
                     x[4] -= cb4.x; x[5] -= cb4.y; x[6] -= cb4.z; x[7] -= cb4.w;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
                     uint32_t wh[4], wl[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -523,13 +477,27 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     *ph = make_uint4(wh[0], wh[1], wh[2], wh[3]);
                     *pl = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
-                // The operand of the next scores is this residual (norm sqrt(ss) up to rounding); the exact chain's
+                // Norm of the new residual rho' = rho - C[code] without another pass over it:
+                //   |rho'|^2 = |rho|^2 - 2 rho.C + |C|^2,   rho.C >= s - eps |rho| max|C|
+                // where s is the tensor-core score the code was chosen with (within eps |rho| max|C| of rho.C; the
+                // bias taken out again), |rho| <= rnow, and |C|^2 comes from the table the split kernel wrote.  The
+                // stored terms round rho' (the factor 1.001 covers that and the table's rounding); the exact chain's
                 // residual differs from it by at most (m + 1) (2^-18 + 3 * 2^-24) times the a priori bound.
+                float s_code = best;
+                if (bm) s_code -= __ldg(bm + code);
+                const float c2 = __ldg(p.cn2 + static_cast<int64_t>(h) * MK + m * K + code);
+                const float slack = 2.f * eps_m * rnow * cm + (bm ? fabsf(best) * 4.76837158203125e-7f : 0.f);
+                const float ss = fmaxf(rnow * rnow - 2.f * (s_code - slack) + c2, 0.f);
                 rnow = sqrtf(ss) * 1.001f + static_cast<float>(m + 1) * 7.7e-6f * rbound;
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(&bar_q[s]);
             }
+        }
+        if (doubt != 0 && ok) {
+            const unsigned int at = atomicAdd(p.counters, 1u);   // at most one entry per key: the list holds every key if need be
+            const unsigned long long lin = static_cast<unsigned long long>(static_cast<int64_t>(u) * p.L + j);
+            p.work[at] = make_uint4(static_cast<uint32_t>(lin), static_cast<uint32_t>(lin >> 32), last_rec, doubt);
         }
         if (!ok) s_err = 1;
     }
@@ -547,6 +515,134 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Exact settlement of the doubtful keys.  One warp per list entry: it follows the key through the
+// codebooks with the defining arithmetic - residual r_0 = k, r_{m+1} = r_m - C_m[code_m] (fp32
+// subtraction) - and settles every doubtful codebook: each score is ONE fused-multiply-add chain over
+// d = 0..D-1 starting from +0 (+ bias), ties go to the lowest code.  With a candidate record, one lane
+// per candidate runs the chain; without one (too many candidates, no room for the record, or a code of
+// an earlier codebook has changed and with it the residual) lane l scores the codes l, l + 32, ... of
+// the whole codebook.  The residual is broadcast from shared memory.
+template <int D>
+__global__ void __launch_bounds__(kAtRepairWarps * 32)
+assign_repair_kernel(AtParams p)
+{
+    __shared__ __align__(16) float s_r[kAtRepairWarps][D];
+    __shared__ uint4 s_rec[kAtRepairWarps][kAtMaxM];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned int count = p.counters[0];
+    const int M = p.M, K = p.K;
+    float *r = s_r[warp];
+    constexpr int PER = D / 32;   // residual elements a lane keeps up to date
+    for (unsigned int e = blockIdx.x * kAtRepairWarps + warp; e < count; e += gridDim.x * kAtRepairWarps) {
+        const uint4 ent = p.work[e];
+        const uint32_t doubt = ent.w & 0xffu, brute = (ent.w >> 8) & 0xffu;
+        const int64_t lin = static_cast<int64_t>((static_cast<unsigned long long>(ent.y) << 32) | ent.x);
+        const int64_t u = lin / p.L, j = lin % p.L;
+        const int b = static_cast<int>(u / p.Hkv), h = static_cast<int>(u % p.Hkv);
+        const __nv_bfloat16 *krow = p.k + b * p.k_sb + h * p.k_sh + j * p.k_sl;
+        const float *cbh = p.cb + static_cast<int64_t>(h) * M * K * D;
+        __syncwarp();
+        // the key's records, newest first, into a table indexed by codebook
+        if (lane == 0) {
+            uint32_t at = ent.z;
+            for (int guard = 0; guard < kAtMaxM && at != 0xffffffffu && at < p.pool_cap; ++guard) {
+                const uint4 rec = p.pool[at];
+                s_rec[warp][rec.y & 0xffu & (kAtMaxM - 1)] = rec;
+                at = rec.x;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) r[lane + 32 * i] = __bfloat162float(krow[lane + 32 * i]);
+        __syncwarp();
+        const int64_t cbase = b * p.c_sb + h * p.c_sh + j * p.c_sl;
+        bool changed = false;
+        for (int m = 0; m < M; ++m) {
+            int code = load_code(p.codes, p.code_dtype, cbase + m);
+            const bool dm = (doubt >> m) & 1u;
+            const uint4 rec = dm ? s_rec[warp][m] : make_uint4(0, 0, 0, 0);
+            const int ncand = static_cast<int>((rec.y >> 8) & 0xffu);
+            const bool all = changed || ((brute >> m) & 1u) || (dm && (ncand > 4 || ncand == 0));
+            if (all || dm) {
+                const float *cm = cbh + static_cast<int64_t>(m) * K * D;
+                const float *bm = p.bias ? p.bias + (static_cast<int64_t>(h) * M + m) * K : nullptr;
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                if (all) {
+                    for (int c0 = 0; c0 < K; c0 += 128) {       // four codes per lane at a time: four independent chains
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                        const float *row[4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) row[t] = cm + static_cast<int64_t>(min(c0 + lane + 32 * t, K - 1)) * D;
+#pragma unroll 4
+                        for (int d = 0; d < D; d += 4) {
+                            const float4 r4 = *reinterpret_cast<const float4 *>(r + d);
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                const float4 c4 = __ldg(reinterpret_cast<const float4 *>(row[t] + d));
+                                acc[t] = __fmaf_rn(r4.x, c4.x, acc[t]);
+                                acc[t] = __fmaf_rn(r4.y, c4.y, acc[t]);
+                                acc[t] = __fmaf_rn(r4.z, c4.z, acc[t]);
+                                acc[t] = __fmaf_rn(r4.w, c4.w, acc[t]);
+                            }
+                        }
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const int c = c0 + lane + 32 * t;
+                            if (c < K) {
+                                const float sc = bm ? __fadd_rn(acc[t], __ldg(bm + c)) : acc[t];
+                                if (sc > bv) {      // codes come in increasing order: the first maximum stays
+                                    bv = sc;
+                                    bi = c;
+                                }
+                            }
+                        }
+                    }
+                } else if (lane < ncand) {
+                    const int c = static_cast<int>(((lane < 2 ? rec.z : rec.w) >> (16 * (lane & 1))) & 0xffffu);
+                    if (c < K) {
+                        const float *crow = cm + static_cast<int64_t>(c) * D;
+                        float acc = 0.f;
+#pragma unroll 8
+                        for (int d = 0; d < D; d += 4) {
+                            const float4 r4 = *reinterpret_cast<const float4 *>(r + d);
+                            const float4 c4 = __ldg(reinterpret_cast<const float4 *>(crow + d));
+                            acc = __fmaf_rn(r4.x, c4.x, acc);
+                            acc = __fmaf_rn(r4.y, c4.y, acc);
+                            acc = __fmaf_rn(r4.z, c4.z, acc);
+                            acc = __fmaf_rn(r4.w, c4.w, acc);
+                        }
+                        bv = bm ? __fadd_rn(acc, __ldg(bm + c)) : acc;
+                        bi = c;
+                    }
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+                    if (ov > bv || (ov == bv && oi < bi)) {
+                        bv = ov;
+                        bi = oi;
+                    }
+                }
+                if (bi != code && bi != 0x7fffffff) {
+                    changed = true;
+                    code = bi;
+                    if (lane == 0) store_code(p.codes, p.code_dtype, cbase + m, code);
+                }
+            }
+            if (m + 1 < M) {
+                const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D;
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < PER; ++i) r[lane + 32 * i] = __fsub_rn(r[lane + 32 * i], __ldg(crow + lane + 32 * i));
+                __syncwarp();
+            }
+        }
+    }
+}
+
 template <int D, int NS, int CH>
 static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const VqTensorDesc *bias, VqTensorDesc *codes,
                             void *workspace, int32_t *status, cudaStream_t stream)
@@ -557,8 +653,12 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     __nv_bfloat16 *hi = static_cast<__nv_bfloat16 *>(workspace);
     __nv_bfloat16 *lo = hi + Hkv * MK * D;
     float *cmax = reinterpret_cast<float *>(lo + Hkv * MK * D);
-    split_codebook_kernel<<<static_cast<unsigned>(Hkv * M), 256, 0, stream>>>(static_cast<const float *>(cb->ptr), hi, lo, cmax,
-                                                                              static_cast<int>(K), D);
+    float *cn2 = cmax + (Hkv * M + 63) / 64 * 64;
+    unsigned int *counters = reinterpret_cast<unsigned int *>(cn2 + (Hkv * MK + 63) / 64 * 64);
+    uint4 *work = reinterpret_cast<uint4 *>(counters + 64);
+    uint4 *pool = work + B * Hkv * L;
+    split_codebook_kernel<<<static_cast<unsigned>(Hkv * M), 256, 0, stream>>>(static_cast<const float *>(cb->ptr), hi, lo, cmax, cn2,
+                                                                              counters, static_cast<int>(K), D);
     if (launch_status() != VQ_OK) return VQ_ELAUNCH;
     CUtensorMap mk, mhi, mlo;
     const uint64_t cd[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(Hkv * MK), 1};
@@ -570,6 +670,11 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     p.cb = static_cast<const float *>(cb->ptr);
     p.bias = bias ? static_cast<const float *>(bias->ptr) : nullptr;
     p.cmax = cmax;
+    p.cn2 = cn2;
+    p.work = work;
+    p.pool = pool;
+    p.counters = counters;
+    p.pool_cap = static_cast<unsigned int>(B * Hkv * L < 0xfffffff0ll ? B * Hkv * L : 0xfffffff0ll);
     p.codes = codes->ptr; p.code_dtype = codes->dtype;
     p.c_sb = codes->stride[0]; p.c_sh = codes->stride[1]; p.c_sl = codes->stride[2];
     p.Hkv = static_cast<int>(Hkv); p.M = static_cast<int>(M); p.K = static_cast<int>(K);
@@ -581,6 +686,11 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
     dim3 grid(static_cast<unsigned>((p.ntiles + NS - 1) / NS), static_cast<unsigned>(B * Hkv));
     kern<<<grid, C::kThreads, C::kTotal, stream>>>(mk, mhi, mlo, p);
+    if (launch_status() != VQ_OK) return VQ_ELAUNCH;
+    // the doubtful keys, exactly; the list length is only known on the device: a fixed grid walks it
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return VQ_EDEVICE;
+    assign_repair_kernel<D><<<static_cast<unsigned>(sms * 8), kAtRepairWarps * 32, 0, stream>>>(p);
     return launch_status();
 }
 
@@ -588,11 +698,11 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
 
 extern "C" size_t vqattn_assign_workspace_bytes(int64_t B, int64_t Hkv, int64_t L, int64_t M, int64_t K, int64_t D)
 {
-    (void)B;
-    (void)L;
     const size_t split = static_cast<size_t>(Hkv) * M * K * D * 2 * 2;                           // bf16 hi / lo codebooks
     const size_t norms = (static_cast<size_t>(Hkv) * M * sizeof(float) + 255) / 256 * 256;        // max row norm per codebook
-    return split + norms + 256;
+    const size_t rows = (static_cast<size_t>(Hkv) * M * K * sizeof(float) + 255) / 256 * 256;    // squared norm of every row
+    const size_t list = 256 + 2 * static_cast<size_t>(B) * Hkv * L * 16;   // counters; doubtful keys and candidate records, 16 bytes each, one per key at most
+    return split + norms + rows + list + 256;
 }
 
 extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc *codebooks, const VqTensorDesc *bias,

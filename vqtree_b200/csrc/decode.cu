@@ -408,3 +408,17 @@ extern "C" int vqattn_decode_static(const VqDecodeArgs *a, void *stream)
     b.workspace_bytes = VQATTN_DECODE_STATIC_BYTES;
     return vqattn_decode(&b, stream);
 }
+
+// One generated token: rotate-and-append, then attention, on one stream (see vqattn.h).
+extern "C" int vqattn_decode_step(const VqDecodeStepArgs *a, void *stream)
+{
+    if (a == nullptr) return VQ_EINVAL_ARG;
+    // validate the attention's arguments before the append writes anything into the caches
+    const int vst = decode_validate(&a->decode);
+    if (vst != VQ_OK) return vst;
+    VqTensorDesc q1 = a->q1, q2 = a->q2, k1w = a->decode.k1_win, k3w = a->decode.k3_win, vw = a->decode.v_win;
+    const int st = vqattn_decode_append(&a->q, &a->k, &a->v, a->positions, a->pos, a->cos_tab, a->sin_tab, a->n_pos, a->const_pos,
+                                        &q1, &q2, &k1w, &k3w, &vw, a->row, a->decode.status_word, stream);
+    if (st != VQ_OK) return st;
+    return vqattn_decode(&a->decode, stream);
+}

@@ -35,7 +35,7 @@ EXPORTS = (
     "vqattn_cache_advance", "vqattn_decode_static_capacity", "vqattn_decode_static",
     "vqattn_assign_workspace_bytes", "vqattn_assign_codes_ws", "vqattn_rope",
     "vqattn_status_from_word", "vqattn_set_wait_limit_cycles", "vqattn_wait_selftest", "vqattn_rope_qk",
-    "vqattn_decode_append",
+    "vqattn_decode_append", "vqattn_decode_step",
 )
 
 
@@ -69,6 +69,13 @@ class VqDecodeArgs(ctypes.Structure):
         ("workspace_bytes", ctypes.c_size_t),
         ("status_word", ctypes.c_void_p),
     ]
+
+
+class VqDecodeStepArgs(ctypes.Structure):
+    _fields_ = [("q", VqTensorDesc), ("k", VqTensorDesc), ("v", VqTensorDesc), ("positions", ctypes.c_void_p),
+                ("pos", ctypes.c_int64), ("cos_tab", ctypes.c_void_p), ("sin_tab", ctypes.c_void_p), ("n_pos", ctypes.c_int64),
+                ("const_pos", ctypes.c_int64), ("q1", VqTensorDesc), ("q2", VqTensorDesc), ("row", ctypes.c_int64),
+                ("decode", VqDecodeArgs)]
 
 
 def _load() -> ctypes.CDLL:
@@ -106,6 +113,7 @@ def _load() -> ctypes.CDLL:
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, P(VqTensorDesc),
                                          P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int64,
                                          ctypes.c_void_p, ctypes.c_void_p]
+    lib.vqattn_decode_step.argtypes = [P(VqDecodeStepArgs), ctypes.c_void_p]
     lib.vqattn_status_from_word.argtypes = [ctypes.c_int32]
     lib.vqattn_set_wait_limit_cycles.argtypes = [ctypes.c_int64]
     lib.vqattn_set_wait_limit_cycles.restype = ctypes.c_int64
@@ -133,10 +141,12 @@ def check(status: int, where: str) -> None:
         raise VqError(status, where)
 
 
-def desc(t: torch.Tensor | None) -> VqTensorDesc:
-    """Describe a tensor for the C ABI (None -> a descriptor with a NULL pointer)."""
-    d = VqTensorDesc()
+def desc(t: torch.Tensor | None, d: VqTensorDesc | None = None) -> VqTensorDesc:
+    """Describe a tensor for the C ABI (None -> a descriptor with a NULL pointer); ``d``: a descriptor to refill."""
+    if d is None:
+        d = VqTensorDesc()
     if t is None:
+        d.ptr = None
         return d
     if t.dtype not in _DTYPES:
         raise TypeError(f"unsupported dtype {t.dtype}")
