@@ -206,6 +206,75 @@ def parity_check(api, w, tensors, cb, codes, out):
                        "kernel on all keys + oracle on sampled key ranges")
 
 
+# ------------------------------------------------------------------------------------ the reference's own GPU kernels
+
+REFGPU = dict(B=1, Hq=32, Hkv=32, D=128, L=32768, W=1024, M=1, K=1024)   # config 2's shape at 32K, ONE codebook of 1024
+
+
+def reference_gpu_leg(dev, reps=5):
+    """The reference's Triton kernels (JIT-compiled here by the installed Triton) and its PyTorch host preparation on
+    the B200, and this library on the SAME tensors: the reference handles one codebook per head and no grouped-query
+    heads, so the workload is config 2's shape at 32K with a single codebook of M*K = 1024 codewords (the same far
+    work per query).  Returns times, the TFLOP/s of both, and the largest difference between the two outputs."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_gpu as rg
+    ok, why = rg.available()
+    if not ok:
+        return dict(unavailable=why)
+    from vqtree_b200 import api
+    from vqtree_b200.fused_vq_attn import vq_attn_forward
+    w = REFGPU
+    try:
+        ref = rg.run(w["B"], w["Hq"], w["L"], w["D"], w["K"], w["W"], reps=reps, device=dev)
+    except Exception as e:  # e.g. the Triton JIT refusing the kernels on this architecture
+        return dict(unavailable=f"{type(e).__name__}: {str(e)[:300]}")
+    flops = contraction_flops(**w)
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            r = fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / n, r
+
+    args, kw = ref["kernel_args"], ref["kernel_kw"]
+    # (1) the drop-in entry point on exactly the tensors the reference handed to its kernel
+    compat_ms, ours = timed(lambda: vq_attn_forward(*args, **kw), reps)
+    diff = float((ours.transpose(1, 2).flatten(2).float() - ref["out"].float()).abs().max())
+    # (2) this library's own preparation + attention from the same raw q/k/v
+    q1, q2, k1, k_vq, k_cnt, k3, v = args[0], args[1], args[2], args[3], args[4], args[5], args[6]
+    cb32 = ref["inputs"]["codebook"].float()[:, None].contiguous()
+    nb = api.far_blocks(w["L"], w["W"])
+
+    def native():
+        codes = api.assign_codes(k3, cb32)
+        cnt, vsum = api.build_aggregates(codes, v, w["K"], nb)
+        return api.prefill_from_aggregates(q1, q2, k1, k3, v, k_vq.contiguous(), cnt, vsum, w["W"])
+
+    native_ms, ours2 = timed(native, reps)
+    cnt, vsum = api.build_aggregates(api.assign_codes(k3, cb32), v, w["K"], nb)
+    kern_ms, _ = timed(lambda: api.prefill_from_aggregates(q1, q2, k1, k3, v, k_vq.contiguous(), cnt, vsum, w["W"]), reps)
+    diff2 = float((ours2.transpose(1, 2).flatten(2).float() - ref["out"].float()).abs().max())
+    tf = lambda ms: flops / (ms * 1e-3) / 1e12
+    return dict(workload=f"B{w['B']} H{w['Hq']} D{w['D']} L{w['L']} W{w['W']} one codebook of {w['K']} bf16 ReRoPE (the reference's limits: "
+                         "single codebook, no grouped-query heads, L % 128 == 0)",
+                reference=dict(kernels_ms=ref["kernel_ms"], host_prep_ms=ref["prep_ms"], total_ms=ref["total_ms"],
+                               kernels_tflops=tf(ref["kernel_ms"]), total_tflops=tf(ref["total_ms"]),
+                               what="ops/triton_fused_vq_attn.py vq_attn_forward (two Triton kernels + flashinfer merge), "
+                                    "ops/attn_vq.py:352-417 host preparation (PyTorch)"),
+                ours=dict(attention_ms=kern_ms, attention_tflops=tf(kern_ms), prep_plus_attention_ms=native_ms,
+                          total_tflops=tf(native_ms), drop_in_call_ms=compat_ms,
+                          what="attention_ms: vqattn_prefill alone; prep_plus_attention: assign (exact kernel: K = 1024 is outside "
+                               "the tensor-core assignment) + aggregates + attention; drop_in_call: fused_vq_attn.vq_attn_forward "
+                               "on the reference's kernel arguments (format conversion included)"),
+                speedup_kernels=ref["kernel_ms"] / kern_ms, speedup_total=ref["total_ms"] / native_ms,
+                max_abs_diff_drop_in=diff, max_abs_diff_native=diff2, tolerance=2e-2)
+
+
 # ------------------------------------------------------------------------------------ one fixed job split over the ranks
 
 STRONG = dict(B=8, Hq=32, Hkv=8, D=128, L=131072, W=2048, M=8, K=256, decode_steps=256, seed=4)   # config 5
@@ -299,7 +368,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="c2_32k", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the timing of the reference's own GPU kernels")
     ap.add_argument("--attn-impl", default="auto", choices=["auto", "simt", "tensor"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
@@ -342,6 +412,18 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
     from vqtree_b200 import api
+
+    if args.impl == "reference-gpu":
+        if rank != 0:
+            return
+        torch.cuda.set_device(local)
+        leg = reference_gpu_leg(torch.device("cuda", local), reps=max(3, args.steps))
+        r = leg.get("reference", {})
+        print(json.dumps(dict(metric="vq_attn_prefill_tflops_32k_ctx", value=r.get("total_tflops"), unit="TFLOP/s", impl="reference-gpu",
+                              n_gpus=1, steps=args.steps, warmup=args.warmup, ms_per_step=r.get("total_ms"), higher_is_better=True,
+                              scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                              config=dict(workload=leg.get("workload")), reference_gpu=leg)))
+        return
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -517,6 +599,12 @@ def main():
             dist.destroy_process_group()
         return
 
+    refgpu = None
+    if world == 1 and not args.no_reference_gpu:
+        torch.cuda.empty_cache()
+        refgpu = reference_gpu_leg(dev, reps=5)
+        torch.cuda.empty_cache()
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_run(w)
@@ -535,7 +623,7 @@ def main():
                       flops_per_launch=flops),
         stage_rooflines=stage_rooflines(w, stage_ms, peaks),
         cpu_baseline=cpu, e2e=e2e, gpu_launches=4 * args.steps, clocks=clocks, decode=decode, gather_ms=gather_ms,
-        parity=parity, strong=strong,
+        parity=parity, strong=strong, reference_gpu=refgpu,
     )
     print(json.dumps(line))
     if dist is not None:

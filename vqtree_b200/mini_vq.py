@@ -15,7 +15,7 @@ def multi_head_single_quantize(inp: torch.Tensor, codebook: torch.Tensor):
     """
     bsz, head, seqlen, hsz = inp.shape
     assert codebook.shape[0] == head and codebook.shape[2] == hsz
-    k = inp if inp.dtype in (torch.float32, torch.bfloat16) else inp.float()
+    k = inp if inp.dtype in (torch.float32, torch.bfloat16, torch.float16) else inp.float()
     ids = api.assign_codes(k, codebook[:, None].float().contiguous(), out_dtype=torch.int64)[..., 0]
     quantized = torch.gather(codebook[None].expand(bsz, -1, -1, -1), 2, ids[..., None].expand(-1, -1, -1, hsz))
     onehot = torch.nn.functional.one_hot(ids, codebook.shape[1])
