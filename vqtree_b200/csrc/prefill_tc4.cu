@@ -176,11 +176,12 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
                 if (p.rerope) tma_load_4d(smem + C::kQ2 + h * kHalfBytes, &tm_q2, &bar_q, 64 * h, m * kBlock, hq, b);
             }
             bool ok = true;
-            int q = 0;  // position in the consumption sequence K0 K1 K2 V0 K3 V1 ...
+            int slot = 0;               // ring slot of the next load (consumption sequence K0 K1 K2 V0 K3 V1 ...)
+            uint32_t free_par = 1u;     // phase of kv_empty[slot] that frees it; the first round needs no wait
+            bool first_round = true;
             auto load = [&](int it, bool is_v) {
                 if (!ok) return;
-                const int slot = q % NS;
-                if (q >= NS && !mbar_wait(&kv_empty[slot], ((q / NS) - 1) & 1, p.wait_limit)) {
+                if (!first_round && !mbar_wait(&kv_empty[slot], free_par, p.wait_limit)) {
                     ok = false;
                     return;
                 }
@@ -197,7 +198,11 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
                         tma_load_4d(dst + h * kHalfBytes, tm, &kv_full[slot], 64 * h, blk * kBlock, hk, b);
                     }
                 }
-                ++q;
+                if (++slot == NS) {
+                    slot = 0;
+                    free_par ^= 1u;
+                    first_round = false;
+                }
             };
             for (int j = 0; j < NB3 && j < n; ++j) load(j, false);
             for (int j = 0; j < n; ++j) {
@@ -208,56 +213,75 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
         }
     } else if (warp == C::kWarpMma) {
         // ================================================================== MMA issuer
+        // The tensor pipe's queue is shallow: whatever this thread does between two groups of MMAs is time the
+        // pipe idles.  So the loop carries no divisions, no per-item classification and no 64-bit descriptor
+        // arithmetic: ring slot, score buffer and their barrier phases are running counters, the operand
+        // descriptors of the three slots are built once (only the low word of a descriptor depends on the
+        // address), and an item needs the constant-position query exactly when it comes before `n_q2`.
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_f16kind(128, 128, 0, 0, F16 ? 0u : 1u);
             constexpr uint32_t idesc_pv = idesc_f16kind(128, D, 0, 1, F16 ? 0u : 1u);
-            // operand descriptors differ only in their 16-byte-granular start address
             const uint64_t d_q1 = smem_desc_sw128(smem_u32(smem + C::kQ1), 16, 1024);
             const uint64_t d_q2 = p.rerope ? smem_desc_sw128(smem_u32(smem + C::kQ2), 16, 1024) : d_q1;
             const uint64_t d_k0 = smem_desc_sw128(smem_u32(smem + C::kRing), 16, 1024);          // K tiles: K-major
             const uint64_t d_v0 = smem_desc_sw128(smem_u32(smem + C::kRing), kHalfBytes, 1024);  // V tiles: MN-major
+            const int n_q2 = p.rerope ? work.n_far + (work.n_bd == 2 ? 1 : 0) : 0;               // items scored with q2
             bool ok = mbar_wait(&bar_q, 0, p.wait_limit);
-            int q = 0;
-            auto qk = [&](int it) {  // S(it) = Q K(it)^T into buffer it % 3 (free: the product of item it - 3 was issued before)
+            int slot = 0;
+            uint32_t slot_par = 0;                 // phase of the ring slot about to be consumed
+            int sbuf = 0, pbuf = 0;                // score buffer of the next S product / of the next P V product
+            uint32_t p_par = 0;                    // phase of p_full[pbuf]
+            auto next_slot = [&]() {
+                if (++slot == NS) {
+                    slot = 0;
+                    slot_par ^= 1u;
+                }
+            };
+            auto qk = [&](int it) {  // S(it) = Q K(it)^T into the next score buffer (free: its previous product was issued before)
                 if (!ok) return;
-                const int slot = q % NS, buf = it % NB3;
-                if (!mbar_wait(&kv_full[slot], (q / NS) & 1, p.wait_limit)) {
+                if (!mbar_wait(&kv_full[slot], slot_par, p.wait_limit)) {
                     ok = false;
                     return;
                 }
                 tc_fence_after();
-                const int kind = work.kind(it);
-                const uint64_t da = (kind == kFar || kind == kBdA) ? d_q2 : d_q1;
+                const uint64_t da = it < n_q2 ? d_q2 : d_q1;
                 const uint64_t db = d_k0 + static_cast<uint64_t>((slot * C::kTile) >> 4);
-                const uint32_t sdst = tmem + C::kColS + 128 * buf;
+                const uint32_t sdst = tmem + C::kColS + 128 * sbuf;
 #pragma unroll
                 for (int h = 0; h < NH; ++h)
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4) {
-                        const uint64_t off = static_cast<uint64_t>((h * kHalfBytes + k4 * 32) >> 4);
-                        mma_ss(sdst, da + off, db + off, idesc_qk, (h | k4) ? 1u : 0u);
+                        constexpr int kStep = 32 >> 4;
+                        const uint64_t off = static_cast<uint64_t>((h * kHalfBytes) >> 4) + static_cast<uint64_t>(k4 * kStep);
+                        if (h == 0 && k4 == 0) mma_ss_first(sdst, da + off, db + off, idesc_qk);
+                        else mma_ss_acc(sdst, da + off, db + off, idesc_qk);
                     }
                 tc_commit(&kv_empty[slot]);
-                tc_commit(&s_full[buf]);
-                ++q;
+                tc_commit(&s_full[sbuf]);
+                next_slot();
+                if (++sbuf == NB3) sbuf = 0;
             };
             auto pv = [&](int it) {  // O += P(it) V(it)
                 if (!ok) return;
-                const int slot = q % NS, buf = it % NB3;
-                if (!mbar_wait(&p_full[buf], (it / NB3) & 1, p.wait_limit) || !mbar_wait(&kv_full[slot], (q / NS) & 1, p.wait_limit)) {
+                if (!mbar_wait(&p_full[pbuf], p_par, p.wait_limit) || !mbar_wait(&kv_full[slot], slot_par, p.wait_limit)) {
                     ok = false;
                     return;
                 }
                 tc_fence_after();
                 const uint64_t dv = d_v0 + static_cast<uint64_t>((slot * C::kTile) >> 4);
-                const uint32_t odst = tmem + C::kColO, psrc = tmem + C::kColS + 128 * buf;
+                const uint32_t odst = tmem + C::kColO, psrc = tmem + C::kColS + 128 * pbuf;
+                if (it == 0) mma_ts_first(odst, psrc, dv, idesc_pv);
+                else mma_ts_acc(odst, psrc, dv, idesc_pv);
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)  // keys 16 kk ..: packed bf16 over the first 64 columns of the score buffer
-                    mma_ts(odst, psrc + 8 * kk, dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
-                           (it | kk) ? 1u : 0u);
+                for (int kk = 1; kk < 8; ++kk)  // keys 16 kk ..: packed 16-bit P over the first 64 columns of the score buffer
+                    mma_ts_acc(odst, psrc + 8 * kk, dv + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv);
                 tc_commit(&kv_empty[slot]);
-                tc_commit(&pv_done[buf]);
-                ++q;
+                tc_commit(&pv_done[pbuf]);
+                next_slot();
+                if (++pbuf == NB3) {
+                    pbuf = 0;
+                    p_par ^= 1u;
+                }
             };
             for (int j = 0; j < NB3 && j < n; ++j) qk(j);
             for (int j = 0; j < n; ++j) {
