@@ -645,7 +645,7 @@ def main():
                       unit="TFLOP/s", frac=attn_tflops / peaks["tensor"], peak_source=f"{peaks['source']} (burst bf16 matmul)",
                       traffic=attention_bytes(w) * 1.012, traffic_unit="bytes per launch",
                       traffic_note="algorithmic bytes x 1.012, the DRAM read+write / algorithmic ratio ncu measured on the c2 "
-                                   "capture (profiles/); traffic grows in proportion to the units processed",
+                                   "capture; traffic grows in proportion to the (query tile, work item) pairs processed",
                       flops_per_launch=flops),
         stage_rooflines=stage_rooflines(w, stage_ms, peaks),
         cpu_baseline=cpu, e2e=e2e, gpu_launches=4 * args.steps, clocks=clocks, decode=decode, gather_ms=gather_ms,
