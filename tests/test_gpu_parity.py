@@ -325,6 +325,43 @@ def test_assign_tensor_path_ties_zero_keys_and_bias(api):
         np.testing.assert_array_equal(got.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("kind", ["heavy_tail", "low_rank", "near_duplicates", "tiny_codebook", "huge_norms", "all_equal_keys"])
+def test_assign_tensor_path_adversarial_distributions(api, kind):
+    """Data that stresses the error bound and the candidate records of the tensor-core assignment: heavy-tailed
+    keys, keys in a low-dimensional subspace, codebooks full of near-duplicates (many candidates per key), codewords
+    far smaller / far larger than the keys, identical keys.  Codes must equal the exact kernel's on every key (device
+    comparison) and the oracle's on a slice."""
+    g = torch.Generator().manual_seed(900 + len(kind) * 7 + ord(kind[0]))
+    B, Hkv, L, D, M, K = 2, 3, 3000, 128, 4, 256
+    k = torch.randn(B, Hkv, L, D, generator=g)
+    cb = torch.randn(Hkv, M, K, D, generator=g) * D ** -0.25
+    if kind == "heavy_tail":
+        k = k * torch.exp(2.0 * torch.randn(B, Hkv, L, 1, generator=g))
+    elif kind == "low_rank":
+        basis = torch.randn(4, D, generator=g)
+        k = torch.randn(B, Hkv, L, 4, generator=g) @ basis
+        cb = (torch.randn(Hkv, M, K, 4, generator=g) @ basis) * 0.3
+    elif kind == "near_duplicates":
+        base = torch.randn(Hkv, M, 16, D, generator=g) * D ** -0.25
+        cb = base.repeat_interleave(K // 16, dim=2) * (1 + 2 ** -20 * torch.randn(Hkv, M, K, 1, generator=g))
+        cb[:, :, 1::2] = cb[:, :, 0::2]                      # exact duplicates too: first index must win
+    elif kind == "tiny_codebook":
+        cb = cb * 1e-3
+    elif kind == "huge_norms":
+        cb = cb * 50.0
+        k = k * 20.0
+    elif kind == "all_equal_keys":
+        k = k[:, :, :1].expand(B, Hkv, L, D).contiguous()
+    k = k.bfloat16()
+    got = api.assign_codes(dev(k), dev(cb), out_dtype=torch.int32, impl="auto")
+    exact = api.assign_codes(dev(k), dev(cb), out_dtype=torch.int32, impl="simt")
+    torch.cuda.synchronize()
+    api.check_status()
+    assert torch.equal(got, exact), f"{int((got != exact).sum())} codes differ"
+    want = vo.assign_codes(k[:, :, :300].float().numpy(), cb.numpy())
+    np.testing.assert_array_equal(got[:, :, :300].cpu().numpy(), want)
+
+
 # ------------------------------------------------------------------ host-buffer entry (pipelined copies)
 @pytest.mark.gpu
 @pytest.mark.parametrize("B,Hq,Hkv,rerope,chunks", [(2, 8, 4, True, 8), (1, 6, 6, False, 4), (1, 4, 2, False, 1)])
