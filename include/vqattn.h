@@ -131,6 +131,19 @@ int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensorDesc *v, in
                             VqTensorDesc *vsum, void *stream);
 
 /*
+ * The same with a caller workspace of vqattn_aggregates_workspace_bytes(B, Hkv, NB, M, K) bytes (device memory,
+ * 16-byte aligned; contents need not be preserved between calls): the keys of every 128-key block are sorted by
+ * code once, so that the kernel that forms the sums reads each row's keys instead of scanning the block's codes.
+ * Same results, bit for bit.  Used for bf16 values and sums with D = 64 or 128 and K a multiple of 8 up to 4096;
+ * other inputs, a NULL workspace or one that is too small take the path of vqattn_build_aggregates.
+ * A code outside [0, K) is left out and reported through status_word (VQ_WORD_BAD_CODE; may be NULL).
+ */
+size_t vqattn_aggregates_workspace_bytes(int64_t B, int64_t Hkv, int64_t NB, int64_t M, int64_t K);
+int vqattn_build_aggregates_ws(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
+                               VqTensorDesc *vsum, void *workspace, size_t workspace_bytes, int32_t *status_word,
+                               void *stream);
+
+/*
  * Converts the reference's own aggregate format to the dense one above, for callers that already
  * hold it (the arguments of ops/triton_fused_vq_attn.py:190 vq_attn_forward):
  *   v_vq [B,H,L+1,D] f32|bf16 (sorted within-code prefix sums, ops/attn_vq.py:364-383)

@@ -108,6 +108,51 @@ def test_build_aggregates_skewed_codes(api, D):
     np.testing.assert_array_equal(vsum.float().cpu().numpy(), vo.round_bf16(vsum_w.reshape(B, Hkv, 4, M * K, D)))
 
 
+@pytest.mark.parametrize("D,M,K,cdt", [(128, 4, 256, torch.uint8), (64, 2, 512, torch.uint16), (128, 1, 1024, torch.int32),
+                                       (128, 3, 8, torch.uint8)])
+def test_build_aggregates_sorted_equals_scan(api, D, M, K, cdt):
+    """The entry point with a workspace (every block's keys sorted by code first) and the one without it give the
+    same counts and sums bit for bit - also on a strided view of the values and with skewed codes."""
+    B, Hkv, L, nb = 2, 3, 1024, 7
+    g = torch.Generator().manual_seed(5 + K)
+    codes = torch.randint(0, K, (B, Hkv, L, M), generator=g)
+    codes[0, 1, 128:512, 0] = K - 1                            # a row with far more keys than are staged at once
+    codes[1, 2, :, M - 1] = torch.arange(L) % 5               # five rows of one warp share every block
+    store = torch.randn(B, L, Hkv, D + 8, generator=g).to(torch.bfloat16)
+    v = dev(store)[..., :D].permute(0, 2, 1, 3)               # [B,Hkv,L,D] view of [B,L,Hkv,D+8] storage
+    c = dev(codes.to(cdt))
+    cnt_a, vsum_a = api.build_aggregates(c, v, K, nb=nb, impl="scan")
+    cnt_b, vsum_b = api.build_aggregates(c, v, K, nb=nb)
+    torch.cuda.synchronize()
+    api.check_status()
+    assert torch.equal(cnt_a, cnt_b)
+    assert torch.equal(vsum_a.view(torch.int16), vsum_b.view(torch.int16))
+    cnt_w, vsum_w = vo.build_aggregates(codes.numpy(), v.float().cpu().numpy(), K, NB=nb)
+    np.testing.assert_array_equal(cnt_b.cpu().numpy().reshape(cnt_w.shape), cnt_w.astype(np.float32))
+    np.testing.assert_array_equal(vsum_b.float().cpu().numpy(), vo.round_bf16(vsum_w.reshape(B, Hkv, nb, M * K, D)))
+
+
+def test_build_aggregates_sorted_reports_codes_out_of_range(api):
+    """A code outside [0, K) is left out of every row and raises the status word; the other keys are summed as usual."""
+    B, Hkv, L, M, K, D, nb = 1, 2, 512, 2, 64, 128, 4
+    g = torch.Generator().manual_seed(23)
+    codes = torch.randint(0, K, (B, Hkv, L, M), generator=g)
+    v = torch.randn(B, Hkv, L, D, generator=g).to(torch.bfloat16)
+    bad = codes.clone()
+    bad[0, 1, 200, 1] = 200                                    # >= K
+    keep = torch.ones(B, Hkv, L, M, dtype=torch.bool)
+    keep[0, 1, 200, 1] = False
+    cnt, vsum = api.build_aggregates(dev(bad.to(torch.uint8)), dev(v), K, nb=nb)
+    torch.cuda.synchronize()
+    with pytest.raises(Exception):
+        api.check_status()
+    # expected: the same sums with that (key, codebook) pair removed
+    onehot = torch.nn.functional.one_hot(codes, K).float() * keep[..., None]          # [B,Hkv,L,M,K]
+    want_cnt = onehot.reshape(B, Hkv, nb, 128, M * K).sum(3).cumsum(2)
+    np.testing.assert_array_equal(cnt.cpu().numpy(), want_cnt.numpy())
+    api.check_status()                                         # the word was reset by the failed check
+
+
 def test_gather_aggregates_from_reference_format(api, golden_dir):
     f = np.load(golden_dir / "fast_w128.npz")
     v_vq, vi = torch.from_numpy(f["v_vq"]), torch.from_numpy(f["vi"]).to(torch.int64)

@@ -109,10 +109,13 @@ def far_blocks(L: int, window: int) -> int:
 
 
 def build_aggregates(codes: torch.Tensor, v: torch.Tensor, K: int, nb: Optional[int] = None,
-                     out_dtype: Optional[torch.dtype] = None):
+                     out_dtype: Optional[torch.dtype] = None, workspace: Optional[torch.Tensor] = None,
+                     impl: str = "auto"):
     """Per-block counts and value sums (replaces ops/attn_vq.py:352-384,411-417).
 
     codes [B,Hkv,L,M], v [B,Hkv,L,D] -> cnt [B,Hkv,NB,M*K] f32, vsum [B,Hkv,NB,M*K,D] (v's dtype).
+    impl "auto": with a workspace (uint8, allocated here when none is passed) in which the library sorts every block's
+    keys by code first; "scan": the entry point without a workspace.  Same results bit for bit.
     """
     dev = _require_cuda(codes, v)
     B, Hkv, L, M = codes.shape
@@ -122,8 +125,16 @@ def build_aggregates(codes: torch.Tensor, v: torch.Tensor, K: int, nb: Optional[
     vsum = torch.empty((B, Hkv, nb, M * K, D), dtype=out_dtype or v.dtype, device=dev)
     if nb > 0:
         with torch.cuda.device(dev):
-            check(lib.vqattn_build_aggregates(desc(codes), desc(v), K, desc(cnt), desc(vsum), stream_ptr(dev)),
-                  "vqattn_build_aggregates")
+            if impl == "scan":
+                check(lib.vqattn_build_aggregates(desc(codes), desc(v), K, desc(cnt), desc(vsum), stream_ptr(dev)),
+                      "vqattn_build_aggregates")
+            else:
+                need = lib.vqattn_aggregates_workspace_bytes(B, Hkv, nb, M, K)
+                if workspace is None or workspace.numel() < need:
+                    workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+                check(lib.vqattn_build_aggregates_ws(desc(codes), desc(v), K, desc(cnt), desc(vsum), workspace.data_ptr(),
+                                                     workspace.numel(), device_status_word(dev).data_ptr(), stream_ptr(dev)),
+                      "vqattn_build_aggregates_ws")
     return cnt, vsum
 
 

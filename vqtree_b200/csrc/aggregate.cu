@@ -14,6 +14,10 @@ namespace vq {
 
 // aggregate_reg.cu: bf16 kernel with the running sums in registers
 bool aggregates_reg_eligible(const VqTensorDesc *v, const VqTensorDesc *vsum, int K);
+bool aggregates_sorted_eligible(const VqTensorDesc *v, const VqTensorDesc *vsum, int K);
+size_t aggregates_sorted_workspace_bytes(int64_t B, int64_t Hkv, int64_t NB, int64_t M, int64_t K);
+int launch_aggregates_sorted(const VqTensorDesc *codes, const VqTensorDesc *v, int K, VqTensorDesc *cnt, VqTensorDesc *vsum, void *workspace,
+                             int32_t *status, cudaStream_t stream);
 int launch_aggregates_reg(const VqTensorDesc *codes, const VqTensorDesc *v, int K, VqTensorDesc *cnt, VqTensorDesc *vsum,
                           cudaStream_t stream);
 
@@ -255,8 +259,32 @@ cache_advance_kernel(const void *__restrict__ codes, int code_dtype, int64_t c_s
 
 }  // namespace vq
 
+namespace vq {
+static int build_aggregates_impl(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt, VqTensorDesc *vsum,
+                                 void *workspace, size_t workspace_bytes, int32_t *status_word, void *stream);
+}
+
 extern "C" int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
                                        VqTensorDesc *vsum, void *stream)
+{
+    return vq::build_aggregates_impl(codes, v, K, cnt, vsum, nullptr, 0, nullptr, stream);
+}
+
+extern "C" size_t vqattn_aggregates_workspace_bytes(int64_t B, int64_t Hkv, int64_t NB, int64_t M, int64_t K)
+{
+    if (B <= 0 || Hkv <= 0 || NB <= 0 || M <= 0 || K <= 0) return 0;
+    return vq::aggregates_sorted_workspace_bytes(B, Hkv, NB, M, K);
+}
+
+extern "C" int vqattn_build_aggregates_ws(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
+                                          VqTensorDesc *vsum, void *workspace, size_t workspace_bytes, int32_t *status_word,
+                                          void *stream)
+{
+    return vq::build_aggregates_impl(codes, v, K, cnt, vsum, workspace, workspace_bytes, status_word, stream);
+}
+
+static int vq::build_aggregates_impl(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt, VqTensorDesc *vsum,
+                                     void *workspace, size_t workspace_bytes, int32_t *status_word, void *stream)
 {
     using namespace vq;
     int st;
@@ -281,6 +309,9 @@ extern "C" int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensor
     if (v->stride[0] % 4 || v->stride[1] % 4 || v->stride[2] % 4 || reinterpret_cast<uintptr_t>(v->ptr) % 16) return VQ_EINVAL_STRIDE;
     if (reinterpret_cast<uintptr_t>(vsum->ptr) % 16) return VQ_EINVAL_STRIDE;
     if (B * Hkv > 65535) return VQ_EUNSUPPORTED;
+    if (NB > 0 && workspace != nullptr && aggregates_sorted_eligible(v, vsum, K) &&
+        workspace_bytes >= aggregates_sorted_workspace_bytes(B, Hkv, NB, M, K))
+        return launch_aggregates_sorted(codes, v, K, cnt, vsum, workspace, status_word, static_cast<cudaStream_t>(stream));
     if (NB > 0 && aggregates_reg_eligible(v, vsum, K))
         return launch_aggregates_reg(codes, v, K, cnt, vsum, static_cast<cudaStream_t>(stream));
     int rows = static_cast<int>(K < kAggRows ? K : kAggRows);

@@ -14,6 +14,8 @@
 
 namespace vq {
 
+bool aggregates_reg_eligible(const VqTensorDesc *v, const VqTensorDesc *vsum, int K);
+
 constexpr int kArWarps = 4;   // warps per CTA (independent of each other)
 constexpr int kArRows = 8;    // code rows per warp
 constexpr int kArSlots = 8;   // value rows staged per warp and block
@@ -192,6 +194,261 @@ build_aggregates_reg_kernel(const void *__restrict__ codes, int code_dtype, int6
             c_nxt[t] = c_nn[t];
         }
     }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same sums with the keys of every block sorted by code first (caller workspace).
+//
+// In the kernel above every warp scans all 128 codes of a block to find the keys of its eight rows: 128 warps per
+// (batch, kv head) repeat the same scan.  With a workspace, sort_block_codes_kernel sorts the keys of every
+// (unit, block, codebook) by code once (stable: keys of one code stay in position order) and leaves a record
+//   entries[128] u8   key index inside the block, in sorted order
+//   start[K + 1] u8   start[c] = number of keys with a code below c
+// and a warp of build_aggregates_sorted_kernel reads nine bytes of `start` and the entries between them - no scan,
+// no ballots - and adds row by row (the rows of one code are contiguous, so there is no dispatch on the row either).
+// The sums are formed in the same order as above: bit-identical results.
+constexpr int kSortWarps = 4;
+
+__host__ __device__ inline int64_t sorted_record_bytes(int64_t K) { return (kBlock + K + 1 + 15) / 16 * 16; }
+
+__global__ void __launch_bounds__(kSortWarps * 32)
+sort_block_codes_kernel(const void *__restrict__ codes, int code_dtype, int64_t c_sb, int64_t c_sh, int64_t c_sl, uint8_t *__restrict__ ws,
+                        int Hkv, int M, int K, int NB, int32_t *__restrict__ status)
+{
+    constexpr unsigned kAll = 0xffffffffu;
+    extern __shared__ int s_sort[];   // per warp: cnt[K + 1], start[K + 1]
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int idx = blockIdx.x * kSortWarps + w;
+    if (idx >= NB * M) return;
+    const int n = idx / M, m = idx % M;
+    const int u = blockIdx.y, b = u / Hkv, h = u % Hkv;
+    uint8_t *rec = ws + ((static_cast<int64_t>(u) * NB + n) * M + m) * sorted_record_bytes(K);
+    int *cnt = s_sort + w * 2 * (K + 1), *st = cnt + (K + 1);
+    for (int i = lane; i <= K; i += 32) cnt[i] = 0;
+    __syncwarp();
+    int c[4];
+    const int64_t cbase = b * c_sb + h * c_sh + m;
+    bool bad = false;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        c[t] = load_code(codes, code_dtype, cbase + (static_cast<int64_t>(n) * kBlock + 32 * t + lane) * c_sl);
+        if (c[t] < 0 || c[t] >= K) {   // a code outside [0, K): the key is left out (it sorts behind every row) and reported
+            bad = true;
+            c[t] = K;
+        }
+        atomicAdd(&cnt[c[t]], 1);
+    }
+    if (bad && status != nullptr) atomicExch(status, VQ_WORD_BAD_CODE);
+    __syncwarp();
+    // exclusive scan over the K + 1 counters: a run of per consecutive counters per lane, then across the lanes
+    const int per = (K + 1 + 31) / 32;
+    int sum = 0;
+    for (int i = 0; i < per; ++i) {
+        const int j = lane * per + i;
+        if (j <= K) sum += cnt[j];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(kAll, incl, d);
+        if (lane >= d) incl += t;
+    }
+    int run = incl - sum;
+    for (int i = 0; i < per; ++i) {
+        const int j = lane * per + i;
+        if (j <= K) {
+            st[j] = run;
+            rec[kBlock + j] = static_cast<uint8_t>(run);
+            run += cnt[j];
+        }
+    }
+    __syncwarp();
+    for (int i = lane; i <= K; i += 32) cnt[i] = 0;
+    __syncwarp();
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const unsigned mask = __match_any_sync(kAll, c[t]);
+        const int rank = __popc(mask & ((1u << lane) - 1u));
+        const int pos = st[c[t]] + cnt[c[t]] + rank;
+        if (pos < kBlock) rec[pos] = static_cast<uint8_t>(32 * t + lane);
+        __syncwarp();
+        if (rank == 0) cnt[c[t]] += __popc(mask);
+        __syncwarp();
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kArWarps * 32, 7)
+build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat16 *__restrict__ v, int64_t v_sb, int64_t v_sh, int v_row_bytes,
+                               float *__restrict__ cnt,           // [B,Hkv,NB,MK] dense
+                               __nv_bfloat16 *__restrict__ vsum,  // [B,Hkv,NB,MK,D] dense
+                               int Hkv, int M, int K, int NB)
+{
+    constexpr int CPL = D / 32;  // columns per lane: 4 (D = 128) or 2 (D = 64)
+    constexpr unsigned kAll = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int MK = M * K;
+    const int base = (static_cast<int>(blockIdx.x) * kArWarps + (threadIdx.x >> 5)) * kArRows;  // first row, in [0, MK)
+    if (base >= MK) return;
+    const int m = base / K, row0 = base % K;
+    const int u = blockIdx.y, b = u / Hkv, h = u % Hkv;
+    const int rec_bytes = static_cast<int>(sorted_record_bytes(K));
+    // running pointers (no multiplications in the loop): this block's value rows, its record, its outputs
+    const uint8_t *vblk = reinterpret_cast<const uint8_t *>(v + b * v_sb + h * v_sh + CPL * lane);
+    const uint8_t *rec = ws + (static_cast<int64_t>(u) * NB * M + m) * rec_bytes;
+    const int rec_step = M * rec_bytes, v_step = kBlock * v_row_bytes;
+    __nv_bfloat16 *dst = vsum + (static_cast<int64_t>(u) * NB * MK + base) * D + CPL * lane;
+    float *cdst = cnt + static_cast<int64_t>(u) * NB * MK + base + lane;
+
+    float acc[kArRows][CPL];
+#pragma unroll
+    for (int r = 0; r < kArRows; ++r)
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) acc[r][c] = 0.f;
+    float my_cnt = 0.f;  // lane r < 8: number of keys of row r so far
+
+    __shared__ __align__(16) uint8_t s_stage[kArWarps][2][kArSlots][D * 2];
+    const uint32_t stage = static_cast<uint32_t>(__cvta_generic_to_shared(&s_stage[threadIdx.x >> 5][0][0][0])) + CPL * 2 * lane;
+    auto copy_row = [&](const uint8_t *src, int buf, int slot) {
+        const uint32_t d = stage + (buf * kArSlots + slot) * (D * 2);
+        if constexpr (CPL == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src) : "memory");
+        else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+    };
+    auto add_slot = [&](float (&a)[CPL], int buf, int slot) {
+        const uint32_t sp = stage + (buf * kArSlots + slot) * (D * 2);
+        uint32_t x0, x1 = 0;
+        if constexpr (CPL == 4) asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(x0), "=r"(x1) : "r"(sp));
+        else asm volatile("ld.shared.u32 %0, [%1];" : "=r"(x0) : "r"(sp));
+        a[0] = __fadd_rn(a[0], __uint_as_float(x0 << 16));
+        a[1] = __fadd_rn(a[1], __uint_as_float(x0 & 0xffff0000u));
+        if constexpr (CPL == 4) {
+            a[2] = __fadd_rn(a[2], __uint_as_float(x1 << 16));
+            a[3] = __fadd_rn(a[3], __uint_as_float(x1 & 0xffff0000u));
+        }
+    };
+    // lane r <= 8: start[row0 + r] of a block's record (the other lanes repeat the last one)
+    auto load_start = [&](const uint8_t *rc) { return static_cast<int>(__ldg(rc + kBlock + row0 + (lane < kArRows ? lane : kArRows))); };
+    // lane i: key index of entry first + i of the warp's rows
+    auto load_entry = [&](const uint8_t *rc, int first) { return static_cast<int>(__ldg(rc + ((first + lane) & (kBlock - 1)))); };
+    // copies the value rows of the first min(count, slots) entries into the staging buffer
+    auto stage_entries = [&](const uint8_t *vb, int e, int count, int buf) {
+        const int ns = count < kArSlots ? count : kArSlots;
+        for (int i = 0; i < ns; ++i) copy_row(vb + __shfl_sync(kAll, e, i) * v_row_bytes, buf, i);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    // Software pipeline over the blocks: starts two blocks ahead, entries and value rows one block ahead.
+    int st_cur = 0, st_nxt = 0, st_nn = 0, e_cur = 0, e_nxt = 0;
+    if (NB > 0) {
+        st_cur = load_start(rec);
+        if (NB > 1) st_nxt = load_start(rec + rec_step);
+        const int s0 = __shfl_sync(kAll, st_cur, 0);
+        e_cur = load_entry(rec, s0);
+        stage_entries(vblk, e_cur, __shfl_sync(kAll, st_cur, kArRows) - s0, 0);
+    }
+    for (int n = 0; n < NB; ++n) {
+        const int buf = n & 1;
+        if (n + 2 < NB) st_nn = load_start(rec + 2 * rec_step);
+        if (n + 1 < NB) {
+            const int s0n = __shfl_sync(kAll, st_nxt, 0);
+            e_nxt = load_entry(rec + rec_step, s0n);
+            stage_entries(vblk + v_step, e_nxt, __shfl_sync(kAll, st_nxt, kArRows) - s0n, buf ^ 1);
+        } else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // this block's rows have landed
+        __syncwarp();
+        // ---- this block's keys: row by row, position order within a row
+        const int s0 = __shfl_sync(kAll, st_cur, 0);
+        const int count = __shfl_sync(kAll, st_cur, kArRows) - s0;
+        my_cnt += static_cast<float>(__shfl_down_sync(kAll, st_cur, 1) - st_cur);   // lanes 0..7: keys of their row in this block
+        if (count <= kArSlots) {
+            int slot = 0;
+#pragma unroll
+            for (int r = 0; r < kArRows; ++r) {
+                const int end = __shfl_sync(kAll, st_cur, r + 1) - s0;
+                for (; slot < end; ++slot) add_slot(acc[r], buf, slot);
+            }
+        } else {
+            // more keys than staging slots (skewed codes): chunks of the sorted entries, staged and waited for at once
+            int first = 0, e = e_cur;
+#pragma unroll 1
+            while (true) {
+                const int ns = count - first < kArSlots ? count - first : kArSlots;
+                int slot = 0;
+#pragma unroll
+                for (int r = 0; r < kArRows; ++r) {
+                    int end = __shfl_sync(kAll, st_cur, r + 1) - s0 - first;
+                    end = end < ns ? end : ns;
+                    for (; slot < end; ++slot) add_slot(acc[r], buf, slot);
+                }
+                first += kArSlots;
+                if (first >= count) break;
+                __syncwarp();
+                e = load_entry(rec, s0 + first);
+                const int nn = count - first < kArSlots ? count - first : kArSlots;
+                for (int i = 0; i < nn; ++i) copy_row(vblk + __shfl_sync(kAll, e, i) * v_row_bytes, buf, i);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncwarp();
+            }
+        }
+        // ---- snapshot of the eight rows
+#pragma unroll
+        for (int r = 0; r < kArRows; ++r) {
+            if constexpr (CPL == 4)
+                __stcs(reinterpret_cast<uint2 *>(dst + r * D), make_uint2(ar_pack(acc[r][0], acc[r][1]), ar_pack(acc[r][2], acc[r][3])));
+            else
+                __stcs(reinterpret_cast<uint32_t *>(dst + r * D), ar_pack(acc[r][0], acc[r][1]));
+        }
+        if (lane < kArRows) __stcs(cdst, my_cnt);
+        // ---- next block
+        st_cur = st_nxt;
+        st_nxt = st_nn;
+        e_cur = e_nxt;
+        rec += rec_step;
+        vblk += v_step;
+        dst += static_cast<int64_t>(MK) * D;
+        cdst += MK;
+    }
+}
+
+size_t aggregates_sorted_workspace_bytes(int64_t B, int64_t Hkv, int64_t NB, int64_t M, int64_t K)
+{
+    return static_cast<size_t>(B * Hkv * NB * M * sorted_record_bytes(K));
+}
+
+// bf16 values and snapshots, D = 64 or 128, K a multiple of 8 and at most 2^15 (shared memory of the sort), rows of v
+// less than 16 MB apart (32-bit offsets inside a block)
+bool aggregates_sorted_eligible(const VqTensorDesc *v, const VqTensorDesc *vsum, int K)
+{
+    return aggregates_reg_eligible(v, vsum, K) && K <= 4096 && v->stride[2] * 2 * kBlock < (int64_t(1) << 31);
+}
+
+int launch_aggregates_sorted(const VqTensorDesc *codes, const VqTensorDesc *v, int K, VqTensorDesc *cnt, VqTensorDesc *vsum, void *workspace,
+                             int32_t *status, cudaStream_t stream)
+{
+    const int64_t B = codes->shape[0], Hkv = codes->shape[1], M = codes->shape[3];
+    const int64_t D = v->shape[3], NB = cnt->shape[2];
+    if (v->stride[0] % 4 || v->stride[1] % 4 || v->stride[2] % 4 || reinterpret_cast<uintptr_t>(v->ptr) % 8) return VQ_EINVAL_STRIDE;
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    const size_t smem = static_cast<size_t>(kSortWarps) * 2 * (K + 1) * sizeof(int);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(sort_block_codes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+        return VQ_ELAUNCH;
+    dim3 gs(static_cast<unsigned>((NB * M + kSortWarps - 1) / kSortWarps), static_cast<unsigned>(B * Hkv));
+    sort_block_codes_kernel<<<gs, kSortWarps * 32, smem, stream>>>(codes->ptr, codes->dtype, codes->stride[0], codes->stride[1], codes->stride[2],
+                                                                    ws, static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB), status);
+    const int64_t warps = M * K / kArRows;
+    dim3 grid(static_cast<unsigned>((warps + kArWarps - 1) / kArWarps), static_cast<unsigned>(B * Hkv));
+    const int row_bytes = static_cast<int>(v->stride[2] * 2);
+    if (D == 64)
+        build_aggregates_sorted_kernel<64><<<grid, kArWarps * 32, 0, stream>>>(
+            ws, static_cast<const __nv_bfloat16 *>(v->ptr), v->stride[0], v->stride[1], row_bytes, static_cast<float *>(cnt->ptr),
+            static_cast<__nv_bfloat16 *>(vsum->ptr), static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB));
+    else
+        build_aggregates_sorted_kernel<128><<<grid, kArWarps * 32, 0, stream>>>(
+            ws, static_cast<const __nv_bfloat16 *>(v->ptr), v->stride[0], v->stride[1], row_bytes, static_cast<float *>(cnt->ptr),
+            static_cast<__nv_bfloat16 *>(vsum->ptr), static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB));
+    return launch_status();
 }
 
 int launch_aggregates_reg(const VqTensorDesc *codes, const VqTensorDesc *v, int K, VqTensorDesc *cnt, VqTensorDesc *vsum,

@@ -31,6 +31,7 @@ _DTYPES = {
 
 EXPORTS = (
     "vqattn_version", "vqattn_status_string", "vqattn_assign_codes", "vqattn_build_aggregates",
+    "vqattn_aggregates_workspace_bytes", "vqattn_build_aggregates_ws",
     "vqattn_gather_aggregates", "vqattn_prefill", "vqattn_decode_workspace_bytes", "vqattn_decode",
     "vqattn_cache_advance", "vqattn_decode_static_capacity", "vqattn_decode_static",
     "vqattn_assign_workspace_bytes", "vqattn_assign_codes_ws", "vqattn_rope",
@@ -97,6 +98,10 @@ def _load() -> ctypes.CDLL:
                                            ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
     lib.vqattn_build_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc),
                                             P(VqTensorDesc), ctypes.c_void_p]
+    lib.vqattn_aggregates_workspace_bytes.restype = ctypes.c_size_t
+    lib.vqattn_aggregates_workspace_bytes.argtypes = [ctypes.c_int64] * 5
+    lib.vqattn_build_aggregates_ws.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc), P(VqTensorDesc),
+                                               ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
     lib.vqattn_gather_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
     lib.vqattn_prefill.argtypes = [P(VqPrefillArgs), ctypes.c_void_p]
     lib.vqattn_decode_workspace_bytes.restype = ctypes.c_size_t
@@ -122,7 +127,7 @@ def _load() -> ctypes.CDLL:
                                 P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p, ctypes.c_void_p]
     for name in EXPORTS:
         if name not in ("vqattn_status_string", "vqattn_decode_workspace_bytes", "vqattn_decode_static_capacity",
-                        "vqattn_assign_workspace_bytes", "vqattn_set_wait_limit_cycles"):
+                        "vqattn_assign_workspace_bytes", "vqattn_aggregates_workspace_bytes", "vqattn_set_wait_limit_cycles"):
             getattr(lib, name).restype = ctypes.c_int
     return lib
 
