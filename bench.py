@@ -74,8 +74,8 @@ def stage_rooflines(w, stage_ms, peaks):
         assign_codes=dict(kernel="assign_tc_kernel", bound="tensor", achieved=a_tf, peak=peaks["tensor"], unit="TFLOP/s",
                           frac=a_tf / peaks["tensor"], note="algorithmic score FLOPs (split_codebook + assign_tc + assign_repair "
                           "kernels); bound by the per-key scan / residual chain between its MMAs, not by the tensor pipe"),
-        build_aggregates=dict(kernel="build_aggregates_reg_kernel", bound="hbm", achieved=g_gbs, peak=peaks["hbm"], unit="GB/s",
-                              frac=g_gbs / peaks["hbm"]),
+        build_aggregates=dict(kernel="sort_block_codes_kernel + build_aggregates_sorted_kernel", bound="hbm", achieved=g_gbs,
+                              peak=peaks["hbm"], unit="GB/s", frac=g_gbs / peaks["hbm"]),
     )
 
 
@@ -648,7 +648,7 @@ def main():
                                    "capture; traffic grows in proportion to the (query tile, work item) pairs processed",
                       flops_per_launch=flops),
         stage_rooflines=stage_rooflines(w, stage_ms, peaks),
-        cpu_baseline=cpu, e2e=e2e, gpu_launches=4 * args.steps, clocks=clocks, decode=decode, gather_ms=gather_ms,
+        cpu_baseline=cpu, e2e=e2e, gpu_launches=6 * args.steps, clocks=clocks, decode=decode, gather_ms=gather_ms,
         parity=parity, strong=strong, reference_gpu=refgpu,
     )
     print(json.dumps(line))

@@ -35,6 +35,14 @@ def test_struct_layout_matches_header():
     assert native.VqDecodeArgs.n_valid.offset == 9 * 104
 
 
+def test_aggregates_workspace_size():
+    lib = _native().lib
+    # per (batch, kv head, block, codebook): 128 key indices + K + 1 starts, rounded up to 16 bytes
+    assert lib.vqattn_aggregates_workspace_bytes(1, 32, 247, 4, 256) == 32 * 247 * 4 * 400
+    assert lib.vqattn_aggregates_workspace_bytes(2, 8, 3, 1, 512) == 2 * 8 * 3 * 656
+    assert lib.vqattn_aggregates_workspace_bytes(0, 8, 3, 1, 512) == 0 and lib.vqattn_aggregates_workspace_bytes(1, 1, 1, 1, -4) == 0
+
+
 def test_status_strings():
     native = _native()
     assert native.lib.vqattn_status_string(0) == b"ok"
