@@ -108,7 +108,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(8) uint64_t full[NS], empty[NS], q_full[2], q_free[2], s_ready[2], p_ready[2], o_done[2];
     __shared__ uint32_t s_tmem;
-    __shared__ __align__(8) uint64_t xbar;   // the four softmax warps meet here (one arrival per warp, bounded wait)
     __shared__ int s_err, s_last;
     __shared__ uint32_t s_flag[2][4];
     __shared__ float s_wm[4][kDtN], s_wl[4][kDtN];
@@ -136,7 +135,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             mbar_init(&p_ready[i], 4);
             mbar_init(&o_done[i], 1);
         }
-        mbar_init(&xbar, 4);
         fence_mbar_init();
         s_err = 0;
     }
@@ -199,7 +197,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = s_tmem;  // columns: S^T buffers at 0 and 16, O^T at 32
+    const uint32_t tmem = s_tmem;  // columns: S^T buffers at 0 and 16, O^T buffers at 32 and 48 (the unit segments alternate)
 
     if (warp == 5) {
         // ================================================================== producer (the first loads were issued above)
@@ -218,6 +216,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             const uint64_t d_p = smem_desc_sw128(smem_u32(smem + kDtOffP), 16, 1024);
             bool ok = true;
             int seg = -1;                    // unit segment of the last issued score MMA
+            int seg_p = -1;                  // unit segment of the last issued product: its parity selects the O^T buffer
             int tt_s = tt0 - 1, tt_p = tt0 - 1;  // tile inside its unit of the last score / product item
             auto scores = [&](int t) {
                 if (!ok) return;
@@ -255,6 +254,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 const int st = t % NS, sb = t & 1;
                 if (++tt_p == TU) tt_p = 0;
                 const bool first_of_seg = (t == 0) || tt_p == 0;
+                if (first_of_seg) ++seg_p;
                 if (!mbar_wait(&p_ready[sb], (t >> 1) & 1, bp.wait_limit)) {
                     ok = false;
                     return;
@@ -264,7 +264,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 const uint64_t db = d_p + static_cast<uint64_t>((sb * kDtQBytes) >> 4);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)  // 16 rows per step: V rows advance 2048 B, P columns 32 B (second half of the rows: + 2048 B)
-                    mma_ss(tmem + 32, da + static_cast<uint64_t>((kk * 2048) >> 4),
+                    mma_ss(tmem + 32 + 16 * (seg_p & 1), da + static_cast<uint64_t>((kk * 2048) >> 4),
                            db + static_cast<uint64_t>(((kk >> 2) * (kDtN * 128) + (kk & 3) * 32) >> 4), idesc_o,
                            (!first_of_seg || kk) ? 1u : 0u);
                 tc_commit(&empty[st]);
@@ -288,43 +288,54 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             l_part[g] = 0.f;
         }
         bool ok = true;
-        int cur_ue = -1, last_t = -1;
+        int cur_ue = -1, last_t = -1, obuf = 1;
+        int pend_ue = -1, pend_t = -1, pend_buf = 0;   // a finished unit that has not been written out yet
+        float m_prev[kDtN], l_prev[kDtN];
+#pragma unroll
+        for (int g = 0; g < kDtN; ++g) {
+            m_prev[g] = -INFINITY;
+            l_prev[g] = 0.f;
+        }
         uint32_t xph = 0;
-        // barrier of the 128 softmax threads; false when the bounded wait expired
+        // Barrier of the 128 softmax threads (hardware barrier 1) that also ORs their failure flags: when a bounded wait
+        // has expired in any of them, all four warps learn it at the same barrier and leave together - nobody is left
+        // waiting at a barrier the others never reach.  (The waits that can fail are mbarrier waits on other roles; this
+        // barrier itself only joins warps that are all on their way to it.)
         auto sync4 = [&]() {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&xbar);
-            const bool r = __all_sync(kAll, mbar_wait(&xbar, xph & 1, bp.wait_limit));
+            uint32_t failed;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.or.pred p, 1, 128, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(failed)
+                : "r"(ok ? 0u : 1u)
+                : "memory");
             ++xph;
-            return r;
+            if (failed) ok = false;
+            return failed == 0;
         };
 
         // write this CTA's partial of unit `ue` (its last tile was t_last) and let the last contributor merge the unit
-        auto flush = [&](int ue, int t_last) {
-            if (!__all_sync(kAll, mbar_wait(&o_done[t_last & 1], (t_last >> 1) & 1, bp.wait_limit))) {
-                ok = false;
-                return;
-            }
+        // (ue: the unit; t_last: its last tile in this CTA; obuf: its O^T buffer; lp, mr: its denominators and references)
+        auto flush = [&](int ue, int t_last, int obuf, const float (&lp)[kDtN], const float (&mr)[kDtN]) {
+            if (!__all_sync(kAll, mbar_wait(&o_done[t_last & 1], (t_last >> 1) & 1, bp.wait_limit))) ok = false;   // known to all at the barrier below
             tc_fence_after();
             uint32_t o[16];
-            tmem_ld16(tmem + lane_off + 32, o);
+            tmem_ld16(tmem + lane_off + 32 + 16 * obuf, o);
             tc_wait_ld();
             // denominators: sum of the 128 threads' partial sums
 #pragma unroll
             for (int g = 0; g < kDtN; ++g)
                 if (g < G) {
-                    float v = l_part[g];
+                    float v = lp[g];
 #pragma unroll
                     for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(kAll, v, off);
                     if (lane == 0) s_wl[warp][g] = v;
                 }
-            if (!sync4()) {
-                ok = false;
-                return;
-            }
-            const int first_c = static_cast<int>(((static_cast<int64_t>(ue) * TU + 1) * NC - 1) / T);
-            const int last_c = static_cast<int>(((static_cast<int64_t>(ue + 1) * TU) * NC - 1) / T);
-            if (first_c == last_c) {
+            if (!sync4()) return;
+            // (s_wl is written again at the next flush; every tile in between passes a barrier)
+            if (static_cast<int64_t>(ue) * TU >= g0 && static_cast<int64_t>(ue + 1) * TU <= g1) {
                 // the whole unit was processed by this CTA: normalise and write the output row directly
                 const int b = ue / p.Hkv, hk = ue % p.Hkv;
 #pragma unroll
@@ -334,32 +345,27 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                         static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hk * G + g) * p.o_sh + tid] =
                             __float2bfloat16_rn(__uint_as_float(o[g]) / den);
                     }
-                if (!sync4()) ok = false;  // s_wl is reused by the next unit
                 return;
             }
+            const int first_c = static_cast<int>(((static_cast<int64_t>(ue) * TU + 1) * NC - 1) / T);
+            const int last_c = static_cast<int>(((static_cast<int64_t>(ue + 1) * TU) * NC - 1) / T);
             float *part = bp.partial + static_cast<int64_t>(c + ue) * G * (D + 2);
 #pragma unroll
             for (int g = 0; g < kDtN; ++g)
                 if (g < G) {
                     part[g * (D + 2) + tid] = __uint_as_float(o[g]);
                     if (tid == 0) {
-                        part[g * (D + 2) + D] = m_ref[g];
+                        part[g * (D + 2) + D] = mr[g];
                         part[g * (D + 2) + D + 1] = (s_wl[0][g] + s_wl[1][g]) + (s_wl[2][g] + s_wl[3][g]);
                     }
                 }
             __threadfence();
-            if (!sync4()) {
-                ok = false;
-                return;
-            }
+            if (!sync4()) return;
             if (tid == 0) {
                 const int tk = atomicAdd(bp.ticket + ue, 1);
                 s_last = (tk == last_c - first_c);
             }
-            if (!sync4()) {
-                ok = false;
-                return;
-            }
+            if (!sync4()) return;
             if (s_last) {
                 __threadfence();
                 const int b = ue / p.Hkv, hk = ue % p.Hkv;
@@ -379,11 +385,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 }
                 if (tid == 0) bp.ticket[ue] = 0;  // ready for the next call on this stream
             }
-            if (!sync4()) ok = false;  // s_wl and s_last are reused by the next unit
+            // (s_last is written again at the next flush, after the barriers of the tiles in between - or never)
         };
 
         int ue = ue0, tt = tt0 - 1;
-        for (int t = 0; t < n_items && ok; ++t) {
+        for (int t = 0; t < n_items; ++t) {
             const int st = t % NS, sb = t & 1;
             if (++tt == TU) {
                 tt = 0;
@@ -391,9 +397,20 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             }
             const bool first_of_seg = ue != cur_ue;
             if (first_of_seg) {
-                if (cur_ue >= 0) flush(cur_ue, last_t);
-                if (!ok) break;
+                // The unit that ends here is written out AFTER this tile (see below): its last product is still in
+                // flight, and the new unit accumulates in the other O^T buffer, so nothing has to wait for it.
+                if (cur_ue >= 0) {
+                    pend_ue = cur_ue;
+                    pend_t = last_t;
+                    pend_buf = obuf;
+#pragma unroll
+                    for (int gg = 0; gg < kDtN; ++gg) {
+                        m_prev[gg] = m_ref[gg];
+                        l_prev[gg] = l_part[gg];
+                    }
+                }
                 cur_ue = ue;
+                obuf ^= 1;
 #pragma unroll
                 for (int gg = 0; gg < kDtN; ++gg) {
                     m_ref[gg] = -INFINITY;
@@ -403,10 +420,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             last_t = t;
             const DtItem it = dt_item(bp, tt);
             // the counts of a far tile arrive with the tile; the scores once the MMAs have finished
-            if (!__all_sync(kAll, mbar_wait(&full[st], (t / NS) & 1, bp.wait_limit) && mbar_wait(&s_ready[sb], (t >> 1) & 1, bp.wait_limit))) {
+            // a wait that expires marks this warp as failed; the four warps find out together at the next barrier
+            if (!__all_sync(kAll, mbar_wait(&full[st], (t / NS) & 1, bp.wait_limit) && mbar_wait(&s_ready[sb], (t >> 1) & 1, bp.wait_limit)))
                 ok = false;
-                break;
-            }
             tc_fence_after();
             uint32_t sr[16];
             tmem_ld16(tmem + lane_off + 16 * sb, sr);
@@ -425,10 +441,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 if (lane == 0) s_flag[xph & 1][warp] = bal;
             }
             const uint32_t fslot = xph & 1;
-            if (!sync4()) {
-                ok = false;
-                break;
-            }
+            if (!sync4()) break;
             if ((s_flag[fslot][0] | s_flag[fslot][1] | s_flag[fslot][2] | s_flag[fslot][3]) != 0) {
                 // ---- raise the reference maxima (rare after the first tiles): tile maximum per head over the 128 rows
 #pragma unroll
@@ -438,10 +451,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                     for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(kAll, v, off));
                     if (lane == 0) s_wm[warp][gg] = v;
                 }
-                if (!sync4()) {
-                    ok = false;
-                    break;
-                }
+                if (!sync4()) break;
                 float alpha[kDtN];
                 bool any_scale = false;
 #pragma unroll
@@ -453,23 +463,17 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                     l_part[gg] *= alpha[gg];
                     m_ref[gg] = mn;
                 }
-                if (!sync4()) {  // s_wm may be rewritten
-                    ok = false;
-                    break;
-                }
+                if (!sync4()) break;  // s_wm may be rewritten
                 if (any_scale && !first_of_seg) {
                     // O^T holds the products up to the previous tile: wait for the last one, then scale column g by alpha[g]
-                    if (!__all_sync(kAll, mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1, bp.wait_limit))) {
-                        ok = false;
-                        break;
-                    }
+                    if (!__all_sync(kAll, mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1, bp.wait_limit))) ok = false;
                     tc_fence_after();
                     uint32_t o[16];
-                    tmem_ld16(tmem + lane_off + 32, o);
+                    tmem_ld16(tmem + lane_off + 32 + 16 * obuf, o);
                     tc_wait_ld();
 #pragma unroll
                     for (int gg = 0; gg < kDtN; ++gg) o[gg] = __float_as_uint(__uint_as_float(o[gg]) * alpha[gg]);
-                    tmem_st16(tmem + lane_off + 32, o);
+                    tmem_st16(tmem + lane_off + 32 + 16 * obuf, o);
                     tc_wait_st();
                 }
             }
@@ -487,8 +491,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[sb]);
+            if (pend_ue >= 0) {
+                flush(pend_ue, pend_t, pend_buf, l_prev, m_prev);
+                pend_ue = -1;
+                if (!ok) break;   // decided at a barrier: the same in all four warps
+            }
         }
-        if (ok && cur_ue >= 0) flush(cur_ue, last_t);
+        // ok was last decided at a barrier: the same in all four warps.  The barrier in between: the write-out of the
+        // previous unit may have run just before (a last unit of one tile) and still be reading the shared sums.
+        if (ok && cur_ue >= 0 && sync4()) flush(cur_ue, last_t, obuf, l_part, m_ref);
         if (!ok) s_err = 1;
     }
     tc_fence_before();
