@@ -445,23 +445,27 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             if ((s_flag[fslot][0] | s_flag[fslot][1] | s_flag[fslot][2] | s_flag[fslot][3]) != 0) {
                 // ---- raise the reference maxima (rare after the first tiles): tile maximum per head over the 128 rows
 #pragma unroll
-                for (int gg = 0; gg < kDtN; ++gg) {
-                    float v = sc[gg];
+                for (int gg = 0; gg < kDtN; ++gg)
+                    if (gg < G) {   // (G is the same in every thread: the shuffles stay warp-wide)
+                        float v = sc[gg];
 #pragma unroll
-                    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(kAll, v, off));
-                    if (lane == 0) s_wm[warp][gg] = v;
-                }
+                        for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(kAll, v, off));
+                        if (lane == 0) s_wm[warp][gg] = v;
+                    }
                 if (!sync4()) break;
                 float alpha[kDtN];
                 bool any_scale = false;
 #pragma unroll
                 for (int gg = 0; gg < kDtN; ++gg) {
-                    const float mt = fmaxf(fmaxf(s_wm[0][gg], s_wm[1][gg]), fmaxf(s_wm[2][gg], s_wm[3][gg]));
-                    const float mn = fmaxf(m_ref[gg], mt);
-                    alpha[gg] = (mn == m_ref[gg]) ? 1.f : ex2(m_ref[gg] - mn);   // reference -inf -> 0
-                    any_scale |= alpha[gg] != 1.f;
-                    l_part[gg] *= alpha[gg];
-                    m_ref[gg] = mn;
+                    alpha[gg] = 1.f;
+                    if (gg < G) {
+                        const float mt = fmaxf(fmaxf(s_wm[0][gg], s_wm[1][gg]), fmaxf(s_wm[2][gg], s_wm[3][gg]));
+                        const float mn = fmaxf(m_ref[gg], mt);
+                        alpha[gg] = (mn == m_ref[gg]) ? 1.f : ex2(m_ref[gg] - mn);   // reference -inf -> 0
+                        any_scale |= alpha[gg] != 1.f;
+                        l_part[gg] *= alpha[gg];
+                        m_ref[gg] = mn;
+                    }
                 }
                 if (!sync4()) break;  // s_wm may be rewritten
                 if (any_scale && !first_of_seg) {
