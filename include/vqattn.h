@@ -106,7 +106,7 @@ int vqattn_assign_codes(const VqTensorDesc *k, const VqTensorDesc *codebooks, co
 
 /*
  * The same assignment, bit for bit the same codes, with the score matrix on the tensor cores
- * (bf16 keys, K a multiple of 128 up to 512, M <= 8): approximate scores by tcgen05.mma over a bf16 hi/lo split of the
+ * (bf16 keys, K a multiple of 128 up to 512 or K = 1024, M <= 8): approximate scores by tcgen05.mma over a bf16 hi/lo split of the
  * codebook, then an exact fp32 re-score of every key whose two best approximate
  * scores are closer than the proven error bound.  Needs `workspace` (256-byte aligned) of
  * vqattn_assign_workspace_bytes(B, Hkv, L, M, K, D) bytes for the split codebook.  Inputs outside the

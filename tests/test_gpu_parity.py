@@ -337,6 +337,9 @@ def test_errors_are_reported_not_crashed(api):
     (1, 2, 900, 128, 3, 384),      # three 128-codeword chunks, one key tile per CTA
     (2, 1, 640, 64, 2, 512),       # D = 64 with 9-bit codes
     (1, 2, 385, 128, 2, 128),      # odd number of key tiles: the last CTA has one
+    (1, 2, 1500, 128, 1, 1024),    # one codebook of 1024 (the reference's format): four chunks through a score region of two
+    (2, 1, 600, 128, 3, 1024),     # ... with residual codebooks
+    (1, 2, 513, 64, 2, 1024),      # ... D = 64
 ])
 def test_assign_tensor_path_is_bit_exact(api, B, Hkv, L, D, M, K):
     g = torch.Generator().manual_seed(77 + L + K + M)
@@ -370,7 +373,8 @@ def test_assign_tensor_path_ties_zero_keys_and_bias(api):
         np.testing.assert_array_equal(got.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("kind", ["heavy_tail", "low_rank", "near_duplicates", "tiny_codebook", "huge_norms", "all_equal_keys"])
+@pytest.mark.parametrize("kind", ["heavy_tail", "low_rank", "near_duplicates", "tiny_codebook", "huge_norms", "all_equal_keys",
+                                  "near_duplicates_k1024", "heavy_tail_k1024"])
 def test_assign_tensor_path_adversarial_distributions(api, kind):
     """Data that stresses the error bound and the candidate records of the tensor-core assignment: heavy-tailed
     keys, keys in a low-dimensional subspace, codebooks full of near-duplicates (many candidates per key), codewords
@@ -378,6 +382,8 @@ def test_assign_tensor_path_adversarial_distributions(api, kind):
     comparison) and the oracle's on a slice."""
     g = torch.Generator().manual_seed(900 + len(kind) * 7 + ord(kind[0]))
     B, Hkv, L, D, M, K = 2, 3, 3000, 128, 4, 256
+    if kind.endswith("_k1024"):
+        kind, M, K = kind[:-6], 2, 1024
     k = torch.randn(B, Hkv, L, D, generator=g)
     cb = torch.randn(Hkv, M, K, D, generator=g) * D ** -0.25
     if kind == "heavy_tail":

@@ -43,7 +43,7 @@ using namespace ptx;
 
 constexpr int kAtMinChunk = 128;   // codewords per MMA chunk: 128, or 256 (one N = 256 instruction) when K allows
 constexpr int kAtMaxM = 8;
-constexpr int kAtMaxK = 512;
+constexpr int kAtMaxK = 1024;   // 32 groups of 32 codes: one bit each in a thread's group mask
 constexpr int kAtRepairWarps = 4;  // warps per CTA of the repair kernel (one doubtful key per warp at a time)
 
 // ------------------------------------------------------------------------------------------------
@@ -170,7 +170,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     constexpr int NH = C::NH, SL = C::kSlots;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ __align__(8) uint64_t bar_k[NS], bar_q[NS], bar_c[NS][C::kMaxChunks], b_full[SL], b_free[SL];
+    __shared__ __align__(8) uint64_t bar_k[NS], bar_q[NS], bar_c[NS][C::kMaxChunks], c_free[NS][C::kMaxChunks], b_full[SL], b_free[SL];
     __shared__ __align__(8) uint64_t x_half[NS][4], x_done[NS][4];   // hand-offs between the two warps of a lane quarter
     __shared__ __align__(16) float4 s_x[NS][kBlock];                  // per key: what its two threads tell each other
     __shared__ uint32_t s_tmem;
@@ -180,6 +180,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int u = blockIdx.y, b = u / p.Hkv, h = u % p.Hkv;
     const int M = p.M, K = p.K, MK = M * K;
     const int chunks = K / CH;
+    // A codebook with more chunks than the stream's score region holds (K = 1024: four chunks of 256 columns in a region of
+    // 512) goes through the region in rounds: chunk ch lands in slot ch mod kMaxChunks once the scan threads have
+    // released the chunk that was there; `rounds` uses of every slot per codebook.
+    const bool wrap = chunks > C::kMaxChunks;
+    const int rounds = wrap ? chunks / C::kMaxChunks : 1;
     const int tile0 = static_cast<int>(blockIdx.x) * NS;
     const int n_act = min(NS, p.ntiles - tile0);       // streams with a tile
 
@@ -191,7 +196,10 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 mbar_init(&x_half[i][qd], 1);
                 mbar_init(&x_done[i][qd], 1);
             }
-            for (int c = 0; c < C::kMaxChunks; ++c) mbar_init(&bar_c[i][c], 1);
+            for (int c = 0; c < C::kMaxChunks; ++c) {
+                mbar_init(&bar_c[i][c], 1);
+                mbar_init(&c_free[i][c], C::kScanWarps);
+            }
         }
         for (int i = 0; i < SL; ++i) {
             mbar_init(&b_full[i], 1);
@@ -258,7 +266,13 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                         break;
                     }
                     for (int ch = 0; ch < chunks && ok; ++ch) {
-                        const uint32_t dcol = tmem + s * C::kRegion + ch * CH;
+                        const int cs = wrap ? ch % C::kMaxChunks : ch, use = m * rounds + (wrap ? ch / C::kMaxChunks : 0);
+                        if (wrap && use >= 1 && !mbar_wait(&c_free[s][cs], (use - 1) & 1, p.wait_limit)) {   // the slot's previous chunk has been scanned
+                            ok = false;
+                            break;
+                        }
+                        if (wrap) tc_fence_after();
+                        const uint32_t dcol = tmem + s * C::kRegion + cs * CH;
 #pragma unroll
                         for (int rem = 0; rem < 2 * NH; ++rem, ++g) {
                             const int slot = g % SL, is_lo = rem / NH, hh = rem % NH;
@@ -280,7 +294,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                                     mma_ss(dcol, d_rl + static_cast<uint64_t>((k4 * 32) >> 4), d_b + static_cast<uint64_t>((k4 * 32) >> 4), idesc, 1u);
                             }
                             tc_commit(&b_free[slot]);
-                            if (rem == 2 * NH - 1) tc_commit(&bar_c[s][ch]);  // this chunk's score columns are complete
+                            if (rem == 2 * NH - 1) tc_commit(&bar_c[s][cs]);  // this chunk's score columns are complete
                         }
                     }
                 }
@@ -335,15 +349,9 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             int bgrp = g_lo;
             uint32_t gbits = 0;   // groups whose maximum came within the threshold of the running best: a superset of
                                   // the groups that can hold a candidate at the end
-#pragma unroll 1
-            for (int g = g_lo; g < g_hi && ok; ++g) {
-                if (g == g_lo || g % C::kGroupsPerChunk == 0) {
-                    ok = __all_sync(kAll, mbar_wait(&bar_c[s][g / C::kGroupsPerChunk], m & 1, p.wait_limit));
-                    tc_fence_after();
-                    if (!ok) break;
-                }
+            auto rank_group = [&](int g, uint32_t col) {   // group g of the codebook, its 32 score columns at `col` of the stream's region
                 float v[32];
-                load_scores(tbase + 32 * g, bm, 32 * g, v);
+                load_scores(tbase + col, bm, 32 * g, v);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = tag_score(v[i], i);
                 float hi, lo;
@@ -354,6 +362,33 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 // with a bias the fp32 additions s + bias round by up to 2^-24 |s + bias| each
                 const float thr_g = bm ? thr0 + fabsf(best) * 4.76837158203125e-7f : thr0;
                 gbits |= (hi >= best - thr_g ? 1u : 0u) << g;
+            };
+            if (!wrap) {
+#pragma unroll 1
+                for (int g = g_lo; g < g_hi && ok; ++g) {
+                    if (g == g_lo || g % C::kGroupsPerChunk == 0) {
+                        ok = __all_sync(kAll, mbar_wait(&bar_c[s][g / C::kGroupsPerChunk], m & 1, p.wait_limit));
+                        tc_fence_after();
+                        if (!ok) break;
+                    }
+                    rank_group(g, 32 * g);
+                }
+            } else {
+                // rounds through the region: of every chunk this thread ranks half hf of the groups, then releases the slot
+                constexpr int GPC = C::kGroupsPerChunk;
+                bgrp = hf * (GPC / 2);
+#pragma unroll 1
+                for (int ch = 0; ch < chunks && ok; ++ch) {
+                    const int cs = ch % C::kMaxChunks, use = m * rounds + ch / C::kMaxChunks;
+                    ok = __all_sync(kAll, mbar_wait(&bar_c[s][cs], use & 1, p.wait_limit));
+                    tc_fence_after();
+                    if (!ok) break;
+#pragma unroll 1
+                    for (int i = hf * (GPC / 2); i < (hf + 1) * (GPC / 2); ++i) rank_group(ch * GPC + i, cs * CH + 32 * i);
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&c_free[s][cs]);
+                }
             }
             if (!ok) break;
             // ---- the two halves meet: the upper half hands its result over, the lower half merges (a tie between
@@ -373,7 +408,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 if (!ok) break;
                 const float4 o = *xch;
                 second = fmax3(second, fminf(best, o.x), o.y);
-                if (o.x > best) {
+                if (o.x > best || (o.x == best && __float_as_int(o.z) < bgrp)) {   // equal tagged scores: the lower group holds the lower code
                     best = o.x;
                     bgrp = __float_as_int(o.z);
                 }
@@ -391,10 +426,10 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     const uint32_t gb = dflag ? (gbits | __float_as_uint(o.w)) : 0u;
                     const uint32_t un = __reduce_or_sync(kAll, gb);
                     const float cut = best - thr;
-                    int n = 0;
+                    int n = wrap ? 255 : 0;   // rounds through the region: the earlier chunks' scores are gone, every code is a candidate
                     uint32_t c01 = 0, c23 = 0;
 #pragma unroll 1
-                    for (int g = 0; g < groups; ++g) {
+                    for (int g = 0; g < groups && !wrap; ++g) {
                         if (!((un >> g) & 1u)) continue;
                         if (!__all_sync(kAll, mbar_wait(&bar_c[s][g / C::kGroupsPerChunk], m & 1, p.wait_limit))) {
                             ok = false;
@@ -715,7 +750,7 @@ extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc 
     const bool shapes_ok = k->ndim == 4 && codebooks->ndim == 4;
     const int64_t D = shapes_ok ? k->shape[3] : 0, M = shapes_ok ? codebooks->shape[1] : 0, K = shapes_ok ? codebooks->shape[2] : 0;
     const bool tensor_path = shapes_ok && k->dtype == VQ_BF16 && (D == 64 || D == 128) && M >= 1 && M <= kAtMaxM &&
-                             K % kAtMinChunk == 0 && K <= kAtMaxK && k->stride[0] % 8 == 0 && k->stride[1] % 8 == 0 &&
+                             K % kAtMinChunk == 0 && (K <= 512 || K == kAtMaxK) && k->stride[0] % 8 == 0 && k->stride[1] % 8 == 0 &&
                              k->stride[2] % 8 == 0 && k->shape[2] < (int64_t(1) << 31);
     if (!tensor_path) return vqattn_assign_codes(k, codebooks, bias, codes, stream);
     // same argument checks as the exact kernel's entry point
@@ -747,7 +782,7 @@ extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc 
     if (K == 256)
         return D == 64 ? launch_assign_tc<64, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s)
                        : launch_assign_tc<128, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s);
-    if (K == 512)
+    if (K == 512 || K == 1024)   // K = 1024: four chunks through a region of two
         return D == 64 ? launch_assign_tc<64, 1, 256>(k, codebooks, bias, codes, workspace, status_word, s)
                        : launch_assign_tc<128, 1, 256>(k, codebooks, bias, codes, workspace, status_word, s);
     return D == 64 ? launch_assign_tc<64, 1, 128>(k, codebooks, bias, codes, workspace, status_word, s)   // K = 384
