@@ -268,8 +268,8 @@ def reference_gpu_leg(dev, reps=5):
                                     "ops/attn_vq.py:352-417 host preparation (PyTorch)"),
                 ours=dict(attention_ms=kern_ms, attention_tflops=tf(kern_ms), prep_plus_attention_ms=native_ms,
                           total_tflops=tf(native_ms), drop_in_call_ms=compat_ms,
-                          what="attention_ms: vqattn_prefill alone; prep_plus_attention: assign (exact kernel: K = 1024 is outside "
-                               "the tensor-core assignment) + aggregates + attention; drop_in_call: fused_vq_attn.vq_attn_forward "
+                          what="attention_ms: vqattn_prefill alone; prep_plus_attention: assign (tensor-core kernel, K = 1024) + aggregates "
+                               "+ attention; drop_in_call: fused_vq_attn.vq_attn_forward "
                                "on the reference's kernel arguments (format conversion included)"),
                 speedup_kernels=ref["kernel_ms"] / kern_ms, speedup_total=ref["total_ms"] / native_ms,
                 max_abs_diff_drop_in=diff, max_abs_diff_native=diff2, tolerance=2e-2)
