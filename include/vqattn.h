@@ -144,6 +144,21 @@ int vqattn_build_aggregates_ws(const VqTensorDesc *codes, const VqTensorDesc *v,
                                void *stream);
 
 /*
+ * vqattn_build_aggregates_ws and, from the same pass over the values, the state a decode phase starts from
+ * (what ops/attn_vq.py:89-127 update_prefill is meant to leave in the cache): the counts and the fp32 value sums
+ * of the first state_blocks * 128 keys,
+ *   state_cnt [B,Hkv,M*K] f32,   state_vsum [B,Hkv,M*K,D] f32   (dense),   NB <= state_blocks <= L/128, NB >= 1.
+ * They equal, bit for bit, vqattn_cache_advance applied to those keys from zero.  The workspace is sized for
+ * state_blocks blocks: vqattn_aggregates_workspace_bytes(B, Hkv, state_blocks, M, K).  Inputs the sorted path does
+ * not cover (see above) get the snapshots from the path of vqattn_build_aggregates and the state from the
+ * cache-advance kernel: same results, one more pass over the values.
+ */
+int vqattn_build_aggregates_state(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
+                                  VqTensorDesc *vsum, VqTensorDesc *state_cnt, VqTensorDesc *state_vsum,
+                                  int64_t state_blocks, void *workspace, size_t workspace_bytes, int32_t *status_word,
+                                  void *stream);
+
+/*
  * Converts the reference's own aggregate format to the dense one above, for callers that already
  * hold it (the arguments of ops/triton_fused_vq_attn.py:190 vq_attn_forward):
  *   v_vq [B,H,L+1,D] f32|bf16 (sorted within-code prefix sums, ops/attn_vq.py:364-383)

@@ -80,7 +80,7 @@ def _round(x, dtype):
 
 
 def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window, scale=None, bias=None, impl="auto", return_state=False,
-                         out=None, codebook_act=None):
+                         out=None, codebook_act=None, state_blocks=None):
     cb = _np(codebooks)
     codes = vo.assign_codes(_np(k3), cb, None if bias is None else _np(bias))
     cb_act = cb if q1.dtype == torch.float32 else _round(cb, q1.dtype)
@@ -90,7 +90,8 @@ def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window, scale=None, bias=
         out.copy_(res)
         res = out
     if return_state:
-        return res, dict(codes=torch.from_numpy(codes).to(code_dtype_for(codebooks.shape[2])), cnt=None, vsum=None)
+        return res, dict(codes=torch.from_numpy(codes).to(code_dtype_for(codebooks.shape[2])), cnt=None, vsum=None,
+                         state_cnt=None, state_vsum=None)   # the state is then summed by cache_advance
     return res
 
 

@@ -35,6 +35,8 @@ def test_assign_and_aggregates_reject_arbitrary_descriptors(a, b, c, d):
     assert lib.vqattn_assign_codes_ws(P(a), P(b), None, P(d), None, 0, None, None) < 0
     assert lib.vqattn_build_aggregates(P(a), P(b), 256, P(c), P(d), None) < 0
     assert lib.vqattn_build_aggregates_ws(P(a), P(b), 256, P(c), P(d), None, 0, None, None) < 0
+    assert lib.vqattn_build_aggregates_state(P(a), P(b), 256, P(c), P(d), P(c), P(d), 1, None, 0, None, None) < 0
+    assert lib.vqattn_build_aggregates_state(P(a), P(b), 256, P(c), P(d), None, None, 1, None, 0, None, None) < 0
     assert lib.vqattn_gather_aggregates(P(a), P(b), P(c), P(d), None) < 0
     assert lib.vqattn_cache_advance(P(a), P(b), 128, P(c), P(d), None, None, None) < 0
 

@@ -132,6 +132,55 @@ def test_build_aggregates_sorted_equals_scan(api, D, M, K, cdt):
     np.testing.assert_array_equal(vsum_b.float().cpu().numpy(), vo.round_bf16(vsum_w.reshape(B, Hkv, nb, M * K, D)))
 
 
+@pytest.mark.parametrize("vdt,D,M,K,extra", [(torch.bfloat16, 128, 4, 256, 1), (torch.bfloat16, 64, 2, 512, 0),
+                                             (torch.bfloat16, 128, 1, 1024, 1), (torch.float32, 64, 2, 128, 1),
+                                             (torch.float16, 128, 2, 256, 1)])
+def test_build_aggregates_state_equals_cache_advance(api, vdt, D, M, K, extra):
+    """The decode-phase state taken from the aggregate pass (fp32 counts and sums of the first state_blocks * 128 keys)
+    equals the cache-advance kernel applied to those keys from zero, bit for bit, and the snapshots are unchanged -
+    on the sorted path (bf16) and on the inputs it does not cover (f32 / f16 values)."""
+    B, Hkv, L, nb = 2, 3, 1024 + 64, 7
+    sb = nb + extra
+    g = torch.Generator().manual_seed(11 + K)
+    codes = torch.randint(0, K, (B, Hkv, L, M), generator=g)
+    codes[0, 1, 128:512, 0] = K - 1
+    store = torch.randn(B, L, Hkv, D + 8, generator=g).to(vdt)
+    v = dev(store)[..., :D].permute(0, 2, 1, 3)
+    c = dev(codes.to(torch.int32))
+    cnt_a, vsum_a = api.build_aggregates(c, v, K, nb=nb)
+    cnt_b, vsum_b, s_cnt, s_vsum = api.build_aggregates(c, v, K, nb=nb, state_blocks=sb)
+    want_cnt = torch.zeros(B, Hkv, M * K, device="cuda")
+    want_vsum = torch.zeros(B, Hkv, M * K, D, device="cuda")
+    api.cache_advance(c[:, :, :sb * 128], v[:, :, :sb * 128], K, want_cnt, want_vsum, None)
+    torch.cuda.synchronize()
+    api.check_status()
+    assert torch.equal(cnt_a, cnt_b) and torch.equal(vsum_a.float(), vsum_b.float())
+    assert torch.equal(s_cnt, want_cnt)
+    assert torch.equal(s_vsum.view(torch.int32), want_vsum.view(torch.int32))
+    assert float(s_cnt.sum()) == B * Hkv * M * sb * 128
+
+
+def test_build_aggregates_state_rejects_bad_block_counts(api):
+    B, Hkv, L, M, K, D = 1, 2, 512, 2, 64, 128
+    codes = dev(torch.randint(0, K, (B, Hkv, L, M)).to(torch.uint8))
+    v = dev(torch.randn(B, Hkv, L, D).to(torch.bfloat16))
+    with pytest.raises(AssertionError):
+        api.build_aggregates(codes, v, K, nb=3, state_blocks=2)      # fewer blocks than snapshots
+    with pytest.raises(AssertionError):
+        api.build_aggregates(codes, v, K, nb=3, state_blocks=5)      # beyond the sequence
+    from vqtree_b200 import native
+    cnt = torch.empty(B, Hkv, 3, M * K, device="cuda")
+    vsum = torch.empty(B, Hkv, 3, M * K, D, device="cuda", dtype=torch.bfloat16)
+    s_cnt = torch.empty(B, Hkv, M * K, device="cuda")
+    s_vsum = torch.empty(B, Hkv, M * K, D, device="cuda")
+    d = native.desc
+    args = (d(codes), d(v), K, d(cnt), d(vsum), d(s_cnt), d(s_vsum))
+    assert native.lib.vqattn_build_aggregates_state(*args, 2, None, 0, None, None) == -1   # VQ_EINVAL_SHAPE
+    assert native.lib.vqattn_build_aggregates_state(*args, 5, None, 0, None, None) == -1   # VQ_EINVAL_SHAPE
+    assert native.lib.vqattn_build_aggregates_state(d(codes), d(v), K, d(cnt), d(vsum), None, d(s_vsum), 3, None, 0, None, None) \
+        == -7   # VQ_EINVAL_ARG
+
+
 def test_build_aggregates_sorted_reports_codes_out_of_range(api):
     """A code outside [0, K) is left out of every row and raises the status word; the other keys are summed as usual."""
     B, Hkv, L, M, K, D, nb = 1, 2, 512, 2, 64, 128, 4

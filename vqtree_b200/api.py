@@ -110,12 +110,14 @@ def far_blocks(L: int, window: int) -> int:
 
 def build_aggregates(codes: torch.Tensor, v: torch.Tensor, K: int, nb: Optional[int] = None,
                      out_dtype: Optional[torch.dtype] = None, workspace: Optional[torch.Tensor] = None,
-                     impl: str = "auto"):
+                     impl: str = "auto", state_blocks: Optional[int] = None):
     """Per-block counts and value sums (replaces ops/attn_vq.py:352-384,411-417).
 
     codes [B,Hkv,L,M], v [B,Hkv,L,D] -> cnt [B,Hkv,NB,M*K] f32, vsum [B,Hkv,NB,M*K,D] (v's dtype).
     impl "auto": with a workspace (uint8, allocated here when none is passed) in which the library sorts every block's
     keys by code first; "scan": the entry point without a workspace.  Same results bit for bit.
+    state_blocks (>= nb >= 1): also returns the fp32 counts [B,Hkv,M*K] and sums [B,Hkv,M*K,D] of the first
+    state_blocks * 128 keys, taken from the same pass (what cache_advance over those keys gives from zero).
     """
     dev = _require_cuda(codes, v)
     B, Hkv, L, M = codes.shape
@@ -123,6 +125,19 @@ def build_aggregates(codes: torch.Tensor, v: torch.Tensor, K: int, nb: Optional[
     nb = L // BLOCK if nb is None else nb
     cnt = torch.empty((B, Hkv, nb, M * K), dtype=torch.float32, device=dev)
     vsum = torch.empty((B, Hkv, nb, M * K, D), dtype=out_dtype or v.dtype, device=dev)
+    if state_blocks is not None:
+        assert nb >= 1 and nb <= state_blocks <= L // BLOCK, "state_blocks must lie in [nb, L // 128] and nb >= 1"
+        s_cnt = torch.empty((B, Hkv, M * K), dtype=torch.float32, device=dev)
+        s_vsum = torch.empty((B, Hkv, M * K, D), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            need = 0 if impl == "scan" else lib.vqattn_aggregates_workspace_bytes(B, Hkv, state_blocks, M, K)
+            if need and (workspace is None or workspace.numel() < need):
+                workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+            check(lib.vqattn_build_aggregates_state(desc(codes), desc(v), K, desc(cnt), desc(vsum), desc(s_cnt), desc(s_vsum),
+                                                    state_blocks, workspace.data_ptr() if need else None, need,
+                                                    device_status_word(dev).data_ptr(), stream_ptr(dev)),
+                  "vqattn_build_aggregates_state")
+        return cnt, vsum, s_cnt, s_vsum
     if nb > 0:
         with torch.cuda.device(dev):
             if impl == "scan":
@@ -265,7 +280,8 @@ def prefill_from_aggregates(q1, q2, k1, k3, v, codebook_act, cnt, vsum, window: 
 
 def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window: int, scale: Optional[float] = None,
                          bias: Optional[torch.Tensor] = None, impl: str = "auto", return_state: bool = False,
-                         out: Optional[torch.Tensor] = None, codebook_act: Optional[torch.Tensor] = None):
+                         out: Optional[torch.Tensor] = None, codebook_act: Optional[torch.Tensor] = None,
+                         state_blocks: Optional[int] = None):
     """The whole prefill path: assign codes to k3, build aggregates of v, fused attention.
 
     q1,q2 [B,Hq,L,D]; k1,k3,v [B,Hkv,L,D] (f32 or bf16); codebooks [Hkv,M,K,D] f32.
@@ -274,19 +290,24 @@ def vq_attention_prefill(q1, q2, k1, k3, v, codebooks, window: int, scale: Optio
     All five may be strided views with a contiguous last dim, and so may ``out`` ([B,Hq,L,D] view of
     [B,L,Hq,D] storage gives the layout the reference produces with a transposing copy, :442).
     codebook_act: [Hkv,M*K,D] copy of the codebooks in the activation dtype, if the caller keeps one.
+    state_blocks (with return_state): the state dict also gets "state_cnt" / "state_vsum", the fp32 aggregates of
+    the first state_blocks * 128 keys, when the aggregate pass can supply them (a far set exists).
     """
     B, Hq, L, D = q1.shape
     Hkv, M, K, _ = codebooks.shape
     nb = far_blocks(L, window)
-    codes = cnt = vsum = cb_act = None
+    codes = cnt = vsum = cb_act = s_cnt = s_vsum = None
     if nb > 0 or return_state:
         codes = assign_codes(k3, codebooks, bias)
     if nb > 0:
-        cnt, vsum = build_aggregates(codes, v, K, nb)
+        if return_state and state_blocks is not None and nb <= state_blocks <= L // BLOCK:
+            cnt, vsum, s_cnt, s_vsum = build_aggregates(codes, v, K, nb, state_blocks=state_blocks)
+        else:
+            cnt, vsum = build_aggregates(codes, v, K, nb)
         cb_act = codebook_act if codebook_act is not None else codebooks.reshape(Hkv, M * K, D).to(q1.dtype)
     out = prefill_from_aggregates(q1, q2, k1, k3, v, cb_act, cnt, vsum, window, scale, impl, out=out)
     if return_state:
-        return out, dict(codes=codes, cnt=cnt, vsum=vsum)
+        return out, dict(codes=codes, cnt=cnt, vsum=vsum, state_cnt=s_cnt, state_vsum=s_vsum)
     return out
 
 

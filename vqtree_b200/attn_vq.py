@@ -275,19 +275,25 @@ def _rope_base(past_key_value, rope_base):
     return rope_base or past_key_value.rope_base or 10000.0
 
 
-def _store_prefill_state(past_key_value, layer_idx, k1, k3, v, codes, q_len):
-    """Window from the boundary of the NEXT query on, and aggregates of everything older."""
+def _store_prefill_state(past_key_value, layer_idx, k1, k3, v, codes, q_len, state=None):
+    """Window from the boundary of the NEXT query on, and aggregates of everything older.
+
+    state: (counts, fp32 sums) of the keys before that boundary if the aggregate pass of the prefill already formed
+    them; otherwise they are summed here."""
     W = past_key_value.window_length
     H, M, K, D = past_key_value.codebooks.shape
     B, Hkv = k3.shape[0], k3.shape[1]
     dev = k3.device
     bd = max(0, (q_len - W) // BLOCK_SIZE * BLOCK_SIZE)
-    cnt = torch.zeros(B, Hkv, M * K, dtype=torch.float32, device=dev)
-    vs32 = torch.zeros(B, Hkv, M * K, D, dtype=torch.float32, device=dev)
-    if bd > 0:
-        if codes is None:
-            codes = api.assign_codes(k3, past_key_value.codebooks_f32(dev))
-        api.cache_advance(codes[:, :, :bd], v[:, :, :bd], K, cnt, vs32, None)
+    if state is not None and state[0] is not None:
+        cnt, vs32 = state
+    else:
+        cnt = torch.zeros(B, Hkv, M * K, dtype=torch.float32, device=dev)
+        vs32 = torch.zeros(B, Hkv, M * K, D, dtype=torch.float32, device=dev)
+        if bd > 0:
+            if codes is None:
+                codes = api.assign_codes(k3, past_key_value.codebooks_f32(dev))
+            api.cache_advance(codes[:, :, :bd], v[:, :, :bd], K, cnt, vs32, None)
     past_key_value.update_prefill(cnt, vs32, k1[:, :, bd:q_len], v[:, :, bd:q_len], layer_idx, q_len,
                                   {"key_unrotated": k3[:, :, bd:q_len]})
 
@@ -309,8 +315,10 @@ def long_prefilling_sort_based_linear(query_states, key_states, value_states, po
     out = torch.empty(bsz, q_len, hq, d, dtype=query_states.dtype, device=dev)
     _, st = api.vq_attention_prefill(q1, q2, k1, key_states, value_states, past_key_value.codebooks_f32(dev), W,
                                      scale=1.0 / math.sqrt(d), return_state=True, out=out.transpose(1, 2), impl=impl,
-                                     codebook_act=past_key_value.codebook_act(query_states.dtype, dev))
-    _store_prefill_state(past_key_value, layer_idx, k1, key_states, value_states, st["codes"], q_len)
+                                     codebook_act=past_key_value.codebook_act(query_states.dtype, dev),
+                                     state_blocks=max(0, (q_len - W) // BLOCK_SIZE))
+    _store_prefill_state(past_key_value, layer_idx, k1, key_states, value_states, st["codes"], q_len,
+                         (st.get("state_cnt"), st.get("state_vsum")))
     return out.flatten(2)
 
 

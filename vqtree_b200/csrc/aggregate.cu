@@ -17,7 +17,8 @@ bool aggregates_reg_eligible(const VqTensorDesc *v, const VqTensorDesc *vsum, in
 bool aggregates_sorted_eligible(const VqTensorDesc *v, const VqTensorDesc *vsum, int K);
 size_t aggregates_sorted_workspace_bytes(int64_t B, int64_t Hkv, int64_t NB, int64_t M, int64_t K);
 int launch_aggregates_sorted(const VqTensorDesc *codes, const VqTensorDesc *v, int K, VqTensorDesc *cnt, VqTensorDesc *vsum, void *workspace,
-                             int32_t *status, cudaStream_t stream);
+                             int32_t *status, cudaStream_t stream, float *state_cnt = nullptr, float *state_vsum = nullptr,
+                             int64_t state_blocks = 0);
 int launch_aggregates_reg(const VqTensorDesc *codes, const VqTensorDesc *v, int K, VqTensorDesc *cnt, VqTensorDesc *vsum,
                           cudaStream_t stream);
 
@@ -261,7 +262,8 @@ cache_advance_kernel(const void *__restrict__ codes, int code_dtype, int64_t c_s
 
 namespace vq {
 static int build_aggregates_impl(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt, VqTensorDesc *vsum,
-                                 void *workspace, size_t workspace_bytes, int32_t *status_word, void *stream);
+                                 void *workspace, size_t workspace_bytes, int32_t *status_word, void *stream,
+                                 VqTensorDesc *state_cnt = nullptr, VqTensorDesc *state_vsum = nullptr, int64_t state_blocks = 0);
 }
 
 extern "C" int vqattn_build_aggregates(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
@@ -283,8 +285,18 @@ extern "C" int vqattn_build_aggregates_ws(const VqTensorDesc *codes, const VqTen
     return vq::build_aggregates_impl(codes, v, K, cnt, vsum, workspace, workspace_bytes, status_word, stream);
 }
 
+extern "C" int vqattn_build_aggregates_state(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt,
+                                             VqTensorDesc *vsum, VqTensorDesc *state_cnt, VqTensorDesc *state_vsum, int64_t state_blocks,
+                                             void *workspace, size_t workspace_bytes, int32_t *status_word, void *stream)
+{
+    if (state_cnt == nullptr || state_vsum == nullptr) return VQ_EINVAL_ARG;
+    return vq::build_aggregates_impl(codes, v, K, cnt, vsum, workspace, workspace_bytes, status_word, stream, state_cnt, state_vsum,
+                                     state_blocks);
+}
+
 static int vq::build_aggregates_impl(const VqTensorDesc *codes, const VqTensorDesc *v, int32_t K, VqTensorDesc *cnt, VqTensorDesc *vsum,
-                                     void *workspace, size_t workspace_bytes, int32_t *status_word, void *stream)
+                                     void *workspace, size_t workspace_bytes, int32_t *status_word, void *stream,
+                                     VqTensorDesc *state_cnt, VqTensorDesc *state_vsum, int64_t state_blocks)
 {
     using namespace vq;
     int st;
@@ -309,6 +321,32 @@ static int vq::build_aggregates_impl(const VqTensorDesc *codes, const VqTensorDe
     if (v->stride[0] % 4 || v->stride[1] % 4 || v->stride[2] % 4 || reinterpret_cast<uintptr_t>(v->ptr) % 16) return VQ_EINVAL_STRIDE;
     if (reinterpret_cast<uintptr_t>(vsum->ptr) % 16) return VQ_EINVAL_STRIDE;
     if (B * Hkv > 65535) return VQ_EUNSUPPORTED;
+    if (state_cnt != nullptr) {
+        // the state after state_blocks blocks: fp32, dense, on the same device; at least as many blocks as snapshots
+        if ((st = check_basic(state_cnt, 3)) != VQ_OK) return st;
+        if ((st = check_basic(state_vsum, 4)) != VQ_OK) return st;
+        const VqTensorDesc *sd[] = {codes, state_cnt, state_vsum};
+        if ((st = check_device(sd, 3)) != VQ_OK) return st;
+        if (state_cnt->dtype != VQ_F32 || state_vsum->dtype != VQ_F32) return VQ_EINVAL_DTYPE;
+        if (state_blocks < NB || state_blocks < 1 || state_blocks * kBlock > L) return VQ_EINVAL_SHAPE;
+        if (state_cnt->shape[0] != B || state_cnt->shape[1] != Hkv || state_cnt->shape[2] != MK) return VQ_EINVAL_SHAPE;
+        if (state_vsum->shape[0] != B || state_vsum->shape[1] != Hkv || state_vsum->shape[2] != MK || state_vsum->shape[3] != D)
+            return VQ_EINVAL_SHAPE;
+        if (!is_dense(*state_cnt) || !is_dense(*state_vsum) || reinterpret_cast<uintptr_t>(state_vsum->ptr) % 16) return VQ_EINVAL_STRIDE;
+        if (NB > 0 && workspace != nullptr && aggregates_sorted_eligible(v, vsum, K) &&
+            workspace_bytes >= aggregates_sorted_workspace_bytes(B, Hkv, state_blocks, M, K))
+            return launch_aggregates_sorted(codes, v, K, cnt, vsum, workspace, status_word, static_cast<cudaStream_t>(stream),
+                                            static_cast<float *>(state_cnt->ptr), static_cast<float *>(state_vsum->ptr), state_blocks);
+        // other inputs: the snapshots as without a state, then the state by the cache-advance kernel from zero
+        if ((st = build_aggregates_impl(codes, v, K, cnt, vsum, workspace, workspace_bytes, status_word, stream)) != VQ_OK) return st;
+        cudaStream_t cs = static_cast<cudaStream_t>(stream);
+        if (cudaMemsetAsync(state_cnt->ptr, 0, sizeof(float) * static_cast<size_t>(B * Hkv * MK), cs) != cudaSuccess ||
+            cudaMemsetAsync(state_vsum->ptr, 0, sizeof(float) * static_cast<size_t>(B * Hkv * MK * D), cs) != cudaSuccess)
+            return VQ_ELAUNCH;
+        VqTensorDesc c2 = *codes, v2 = *v;
+        c2.shape[2] = v2.shape[2] = state_blocks * kBlock;
+        return vqattn_cache_advance(&c2, &v2, K, state_cnt, state_vsum, nullptr, status_word, stream);
+    }
     if (NB > 0 && workspace != nullptr && aggregates_sorted_eligible(v, vsum, K) &&
         workspace_bytes >= aggregates_sorted_workspace_bytes(B, Hkv, NB, M, K))
         return launch_aggregates_sorted(codes, v, K, cnt, vsum, workspace, status_word, static_cast<cudaStream_t>(stream));

@@ -282,8 +282,12 @@ __global__ void __launch_bounds__(kArWarps * 32, 7)
 build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat16 *__restrict__ v, int64_t v_sb, int64_t v_sh, int v_row_bytes,
                                float *__restrict__ cnt,           // [B,Hkv,NB,MK] dense
                                __nv_bfloat16 *__restrict__ vsum,  // [B,Hkv,NB,MK,D] dense
-                               int Hkv, int M, int K, int NB)
+                               float *__restrict__ state_cnt,     // nullptr or [B,Hkv,MK]: counts after NBT blocks
+                               float *__restrict__ state_vsum,    // nullptr or [B,Hkv,MK,D]: fp32 sums after NBT blocks
+                               int Hkv, int M, int K, int NB, int NBT)
 {
+    // The warp walks NBT >= NB blocks (the workspace holds NBT records per unit and codebook), writes a snapshot after
+    // each of the first NB and, if asked, its fp32 running sums at the end: the state a decode phase starts from.
     constexpr int CPL = D / 32;  // columns per lane: 4 (D = 128) or 2 (D = 64)
     constexpr unsigned kAll = 0xffffffffu;
     const int lane = threadIdx.x & 31;
@@ -295,7 +299,7 @@ build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat
     const int rec_bytes = static_cast<int>(sorted_record_bytes(K));
     // running pointers (no multiplications in the loop): this block's value rows, its record, its outputs
     const uint8_t *vblk = reinterpret_cast<const uint8_t *>(v + b * v_sb + h * v_sh + CPL * lane);
-    const uint8_t *rec = ws + (static_cast<int64_t>(u) * NB * M + m) * rec_bytes;
+    const uint8_t *rec = ws + (static_cast<int64_t>(u) * NBT * M + m) * rec_bytes;
     const int rec_step = M * rec_bytes, v_step = kBlock * v_row_bytes;
     __nv_bfloat16 *dst = vsum + (static_cast<int64_t>(u) * NB * MK + base) * D + CPL * lane;
     float *cdst = cnt + static_cast<int64_t>(u) * NB * MK + base + lane;
@@ -339,17 +343,17 @@ build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat
 
     // Software pipeline over the blocks: starts two blocks ahead, entries and value rows one block ahead.
     int st_cur = 0, st_nxt = 0, st_nn = 0, e_cur = 0, e_nxt = 0;
-    if (NB > 0) {
+    if (NBT > 0) {
         st_cur = load_start(rec);
-        if (NB > 1) st_nxt = load_start(rec + rec_step);
+        if (NBT > 1) st_nxt = load_start(rec + rec_step);
         const int s0 = __shfl_sync(kAll, st_cur, 0);
         e_cur = load_entry(rec, s0);
         stage_entries(vblk, e_cur, __shfl_sync(kAll, st_cur, kArRows) - s0, 0);
     }
-    for (int n = 0; n < NB; ++n) {
+    for (int n = 0; n < NBT; ++n) {
         const int buf = n & 1;
-        if (n + 2 < NB) st_nn = load_start(rec + 2 * rec_step);
-        if (n + 1 < NB) {
+        if (n + 2 < NBT) st_nn = load_start(rec + 2 * rec_step);
+        if (n + 1 < NBT) {
             const int s0n = __shfl_sync(kAll, st_nxt, 0);
             e_nxt = load_entry(rec + rec_step, s0n);
             stage_entries(vblk + v_step, e_nxt, __shfl_sync(kAll, st_nxt, kArRows) - s0n, buf ^ 1);
@@ -392,14 +396,16 @@ build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat
             }
         }
         // ---- snapshot of the eight rows
+        if (n < NB) {
 #pragma unroll
-        for (int r = 0; r < kArRows; ++r) {
-            if constexpr (CPL == 4)
-                __stcs(reinterpret_cast<uint2 *>(dst + r * D), make_uint2(ar_pack(acc[r][0], acc[r][1]), ar_pack(acc[r][2], acc[r][3])));
-            else
-                __stcs(reinterpret_cast<uint32_t *>(dst + r * D), ar_pack(acc[r][0], acc[r][1]));
+            for (int r = 0; r < kArRows; ++r) {
+                if constexpr (CPL == 4)
+                    __stcs(reinterpret_cast<uint2 *>(dst + r * D), make_uint2(ar_pack(acc[r][0], acc[r][1]), ar_pack(acc[r][2], acc[r][3])));
+                else
+                    __stcs(reinterpret_cast<uint32_t *>(dst + r * D), ar_pack(acc[r][0], acc[r][1]));
+            }
+            if (lane < kArRows) __stcs(cdst, my_cnt);
         }
-        if (lane < kArRows) __stcs(cdst, my_cnt);
         // ---- next block
         st_cur = st_nxt;
         st_nxt = st_nn;
@@ -408,6 +414,15 @@ build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat
         vblk += v_step;
         dst += static_cast<int64_t>(MK) * D;
         cdst += MK;
+    }
+    if (state_vsum != nullptr) {
+        float *sd = state_vsum + (static_cast<int64_t>(u) * MK + base) * D + CPL * lane;
+#pragma unroll
+        for (int r = 0; r < kArRows; ++r) {
+            if constexpr (CPL == 4) *reinterpret_cast<float4 *>(sd + r * D) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+            else *reinterpret_cast<float2 *>(sd + r * D) = make_float2(acc[r][0], acc[r][1]);
+        }
+        if (lane < kArRows) state_cnt[static_cast<int64_t>(u) * MK + base + lane] = my_cnt;
     }
 }
 
@@ -423,31 +438,35 @@ bool aggregates_sorted_eligible(const VqTensorDesc *v, const VqTensorDesc *vsum,
     return aggregates_reg_eligible(v, vsum, K) && K <= 4096 && v->stride[2] * 2 * kBlock < (int64_t(1) << 31);
 }
 
+// state_blocks > 0: the walk covers state_blocks >= NB blocks (records for as many in the workspace) and leaves the fp32 counts
+// and sums after the last one in state_cnt / state_vsum.
 int launch_aggregates_sorted(const VqTensorDesc *codes, const VqTensorDesc *v, int K, VqTensorDesc *cnt, VqTensorDesc *vsum, void *workspace,
-                             int32_t *status, cudaStream_t stream)
+                             int32_t *status, cudaStream_t stream, float *state_cnt, float *state_vsum, int64_t state_blocks)
 {
     const int64_t B = codes->shape[0], Hkv = codes->shape[1], M = codes->shape[3];
-    const int64_t D = v->shape[3], NB = cnt->shape[2];
+    const int64_t D = v->shape[3], NB = cnt->shape[2], NBT = state_blocks > NB ? state_blocks : NB;
     if (v->stride[0] % 4 || v->stride[1] % 4 || v->stride[2] % 4 || reinterpret_cast<uintptr_t>(v->ptr) % 8) return VQ_EINVAL_STRIDE;
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     const size_t smem = static_cast<size_t>(kSortWarps) * 2 * (K + 1) * sizeof(int);
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(sort_block_codes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
         return VQ_ELAUNCH;
-    dim3 gs(static_cast<unsigned>((NB * M + kSortWarps - 1) / kSortWarps), static_cast<unsigned>(B * Hkv));
+    dim3 gs(static_cast<unsigned>((NBT * M + kSortWarps - 1) / kSortWarps), static_cast<unsigned>(B * Hkv));
     sort_block_codes_kernel<<<gs, kSortWarps * 32, smem, stream>>>(codes->ptr, codes->dtype, codes->stride[0], codes->stride[1], codes->stride[2],
-                                                                    ws, static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB), status);
+                                                                    ws, static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NBT), status);
     const int64_t warps = M * K / kArRows;
     dim3 grid(static_cast<unsigned>((warps + kArWarps - 1) / kArWarps), static_cast<unsigned>(B * Hkv));
     const int row_bytes = static_cast<int>(v->stride[2] * 2);
     if (D == 64)
         build_aggregates_sorted_kernel<64><<<grid, kArWarps * 32, 0, stream>>>(
             ws, static_cast<const __nv_bfloat16 *>(v->ptr), v->stride[0], v->stride[1], row_bytes, static_cast<float *>(cnt->ptr),
-            static_cast<__nv_bfloat16 *>(vsum->ptr), static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB));
+            static_cast<__nv_bfloat16 *>(vsum->ptr), state_cnt, state_vsum, static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB),
+            static_cast<int>(NBT));
     else
         build_aggregates_sorted_kernel<128><<<grid, kArWarps * 32, 0, stream>>>(
             ws, static_cast<const __nv_bfloat16 *>(v->ptr), v->stride[0], v->stride[1], row_bytes, static_cast<float *>(cnt->ptr),
-            static_cast<__nv_bfloat16 *>(vsum->ptr), static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB));
+            static_cast<__nv_bfloat16 *>(vsum->ptr), state_cnt, state_vsum, static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB),
+            static_cast<int>(NBT));
     return launch_status();
 }
 

@@ -31,7 +31,7 @@ _DTYPES = {
 
 EXPORTS = (
     "vqattn_version", "vqattn_status_string", "vqattn_assign_codes", "vqattn_build_aggregates",
-    "vqattn_aggregates_workspace_bytes", "vqattn_build_aggregates_ws",
+    "vqattn_aggregates_workspace_bytes", "vqattn_build_aggregates_ws", "vqattn_build_aggregates_state",
     "vqattn_gather_aggregates", "vqattn_prefill", "vqattn_decode_workspace_bytes", "vqattn_decode",
     "vqattn_cache_advance", "vqattn_decode_static_capacity", "vqattn_decode_static",
     "vqattn_assign_workspace_bytes", "vqattn_assign_codes_ws", "vqattn_rope",
@@ -102,6 +102,9 @@ def _load() -> ctypes.CDLL:
     lib.vqattn_aggregates_workspace_bytes.argtypes = [ctypes.c_int64] * 5
     lib.vqattn_build_aggregates_ws.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc), P(VqTensorDesc),
                                                ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
+    lib.vqattn_build_aggregates_state.argtypes = [P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int32, P(VqTensorDesc), P(VqTensorDesc),
+                                                  P(VqTensorDesc), P(VqTensorDesc), ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t,
+                                                  ctypes.c_void_p, ctypes.c_void_p]
     lib.vqattn_gather_aggregates.argtypes = [P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), P(VqTensorDesc), ctypes.c_void_p]
     lib.vqattn_prefill.argtypes = [P(VqPrefillArgs), ctypes.c_void_p]
     lib.vqattn_decode_workspace_bytes.restype = ctypes.c_size_t
