@@ -362,6 +362,7 @@ class DecodeStepCall:
     def __init__(self, q1, q2, win_k1, win_k3, win_v, codebook, cnt, vsum, workspace, const_pos: int, base: float,
                  scale: float):
         self.dev = _require_cuda(q1, q2, win_k1, win_k3, win_v, codebook, cnt, vsum, workspace)
+        self.dev_index = _device_index(self.dev)
         self.base, self.far_tensors = base, (codebook, cnt, vsum)
         self.keep = (q1, q2, win_k1, win_k3, win_v, workspace)
         a = self.args = native.VqDecodeStepArgs()
@@ -381,6 +382,7 @@ class DecodeStepCall:
         d.status_word = device_status_word(self.dev).data_ptr()
         self._tables(max(const_pos + 1, 2))
         self._in = None
+        self._ref = ctypes.byref(a)
 
     def _tables(self, n_pos):
         D = self.keep[0].shape[-1]
@@ -415,8 +417,13 @@ class DecodeStepCall:
         a.pos, a.row = int(pos), int(row)
         d = a.decode
         d.n_valid, d.n_bd, d.use_far = int(n_valid), int(n_bd), 1 if use_far else 0
-        with torch.cuda.device(self.dev):
-            check(lib.vqattn_decode_step(ctypes.byref(a), stream_ptr(self.dev)), "vqattn_decode_step")
+        if torch.cuda.current_device() == self.dev_index:       # the usual case: no device switch around the call
+            st = lib.vqattn_decode_step(self._ref, stream_ptr(self.dev_index))
+        else:
+            with torch.cuda.device(self.dev):
+                st = lib.vqattn_decode_step(self._ref, stream_ptr(self.dev_index))
+        if st != 0:
+            check(st, "vqattn_decode_step")
         return out
 
 

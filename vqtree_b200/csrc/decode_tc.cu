@@ -523,11 +523,15 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
 
 // ------------------------------------------------------------------------------------------ host side
 
+// SM count of the current device; the answer is kept per device ordinal (this runs once per generated token)
 static int dt_sm_count()
 {
+    static int cached[64] = {0};
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (dev >= 0 && dev < 64) cached[dev] = n;
     return n;
 }
 
@@ -601,7 +605,16 @@ int launch_decode_tc(const VqDecodeArgs *a, const DecodeParams &p, cudaStream_t 
         mcb = mv;
         mvs = mv;
     }
-    if (cudaFuncSetAttribute(decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDtSmem) != cudaSuccess) return VQ_ELAUNCH;
+    {
+        // the shared-memory opt-in is a per-device attribute of the kernel: set once per device
+        static bool opted[64] = {false};
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess) return VQ_EDEVICE;
+        if (dev < 0 || dev >= 64 || !opted[dev]) {
+            if (cudaFuncSetAttribute(decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDtSmem) != cudaSuccess) return VQ_ELAUNCH;
+            if (dev >= 0 && dev < 64) opted[dev] = true;
+        }
+    }
     decode_tc_kernel<<<bp.num_ctas, kDtThreads, kDtSmem, s>>>(mk1, mk3, mv, mcb, mvs, mq1, mq2, bp);
     return launch_status();
 }

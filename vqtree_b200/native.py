@@ -170,5 +170,14 @@ def desc(t: torch.Tensor | None, d: VqTensorDesc | None = None) -> VqTensorDesc:
     return d
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device) -> int:
+    """Handle of torch's current stream on ``device`` (the per-token decode path calls this once per step: the raw
+    query avoids building a Stream object)."""
+    if _RAW_STREAM is not None:
+        idx = device if isinstance(device, int) else torch.device(device).index
+        if idx is not None:
+            return _RAW_STREAM(idx)
     return torch.cuda.current_stream(device).cuda_stream
