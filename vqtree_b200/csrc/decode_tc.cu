@@ -359,29 +359,55 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                         part[g * (D + 2) + D + 1] = (s_wl[0][g] + s_wl[1][g]) + (s_wl[2][g] + s_wl[3][g]);
                     }
                 }
-            __threadfence();
+            // Publication: the barrier orders the 128 threads' partial stores before thread 0's ticket increment, whose
+            // release makes them visible device-wide together with it; the last contributor's acquire (the same
+            // instruction) and the barrier after it order every thread's loads behind the other CTAs' partials.
             if (!sync4()) return;
             if (tid == 0) {
-                const int tk = atomicAdd(bp.ticket + ue, 1);
+                int tk;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(tk) : "l"(bp.ticket + ue) : "memory");
                 s_last = (tk == last_c - first_c);
             }
             if (!sync4()) return;
             if (s_last) {
-                __threadfence();
+                // merge of the contributors' partials, four heads at a time: one pass over the contributors with a
+                // running maximum (all loads of a contributor are independent and in flight together)
                 const int b = ue / p.Hkv, hk = ue % p.Hkv;
-                for (int g = 0; g < G; ++g) {
-                    float M = -INFINITY;
-                    for (int cc = first_c; cc <= last_c; ++cc)
-                        M = fmaxf(M, __ldcg(bp.partial + (static_cast<int64_t>(cc + ue) * G + g) * (D + 2) + D));
-                    float num = 0.f, den = 0.f;
-                    for (int cc = first_c; cc <= last_c; ++cc) {
-                        const float *pg = bp.partial + (static_cast<int64_t>(cc + ue) * G + g) * (D + 2);
-                        const float ms = __ldcg(pg + D);
-                        const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-                        num += w * __ldcg(pg + tid);
-                        den += w * __ldcg(pg + D + 1);
+#pragma unroll 1
+                for (int gq = 0; gq < G; gq += 4) {
+                    float M[4], num[4], den[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        M[i] = -INFINITY;
+                        num[i] = 0.f;
+                        den[i] = 0.f;
                     }
-                    static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hk * G + g) * p.o_sh + tid] = __float2bfloat16_rn(num / den);
+#pragma unroll 2
+                    for (int cc = first_c; cc <= last_c; ++cc) {
+                        const float *pc = bp.partial + (static_cast<int64_t>(cc + ue) * G + gq) * (D + 2);
+                        float ms[4], x[4], dd[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const bool on = gq + i < G;
+                            ms[i] = on ? __ldcg(pc + i * (D + 2) + D) : -INFINITY;
+                            x[i] = on ? __ldcg(pc + i * (D + 2) + tid) : 0.f;
+                            dd[i] = on ? __ldcg(pc + i * (D + 2) + D + 1) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float mn = fmaxf(M[i], ms[i]);
+                            const float a = (M[i] == -INFINITY) ? 0.f : exp2f(M[i] - mn);
+                            const float w = (ms[i] == -INFINITY) ? 0.f : exp2f(ms[i] - mn);
+                            num[i] = fmaf(num[i], a, w * x[i]);
+                            den[i] = fmaf(den[i], a, w * dd[i]);
+                            M[i] = mn;
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (gq + i < G)
+                            static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hk * G + gq + i) * p.o_sh + tid] =
+                                __float2bfloat16_rn(num[i] / den[i]);
                 }
                 if (tid == 0) bp.ticket[ue] = 0;  // ready for the next call on this stream
             }
