@@ -277,17 +277,19 @@ sort_block_codes_kernel(const void *__restrict__ codes, int code_dtype, int64_t 
     }
 }
 
-template <int D>
+template <int D, bool kState>
 __global__ void __launch_bounds__(kArWarps * 32, 7)
 build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat16 *__restrict__ v, int64_t v_sb, int64_t v_sh, int v_row_bytes,
                                float *__restrict__ cnt,           // [B,Hkv,NB,MK] dense
                                __nv_bfloat16 *__restrict__ vsum,  // [B,Hkv,NB,MK,D] dense
                                float *__restrict__ state_cnt,     // nullptr or [B,Hkv,MK]: counts after NBT blocks
                                float *__restrict__ state_vsum,    // nullptr or [B,Hkv,MK,D]: fp32 sums after NBT blocks
-                               int Hkv, int M, int K, int NB, int NBT)
+                               int Hkv, int M, int K, int NB, int NBT_arg)
 {
     // The warp walks NBT >= NB blocks (the workspace holds NBT records per unit and codebook), writes a snapshot after
     // each of the first NB and, if asked, its fp32 running sums at the end: the state a decode phase starts from.
+    // (kState = false: NBT = NB and no state - the loop below then has no test on the block index.)
+    const int NBT = kState ? NBT_arg : NB;
     constexpr int CPL = D / 32;  // columns per lane: 4 (D = 128) or 2 (D = 64)
     constexpr unsigned kAll = 0xffffffffu;
     const int lane = threadIdx.x & 31;
@@ -396,7 +398,7 @@ build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat
             }
         }
         // ---- snapshot of the eight rows
-        if (n < NB) {
+        if (!kState || n < NB) {
 #pragma unroll
             for (int r = 0; r < kArRows; ++r) {
                 if constexpr (CPL == 4)
@@ -415,7 +417,7 @@ build_aggregates_sorted_kernel(const uint8_t *__restrict__ ws, const __nv_bfloat
         dst += static_cast<int64_t>(MK) * D;
         cdst += MK;
     }
-    if (state_vsum != nullptr) {
+    if (kState && state_vsum != nullptr) {
         float *sd = state_vsum + (static_cast<int64_t>(u) * MK + base) * D + CPL * lane;
 #pragma unroll
         for (int r = 0; r < kArRows; ++r) {
@@ -457,16 +459,20 @@ int launch_aggregates_sorted(const VqTensorDesc *codes, const VqTensorDesc *v, i
     const int64_t warps = M * K / kArRows;
     dim3 grid(static_cast<unsigned>((warps + kArWarps - 1) / kArWarps), static_cast<unsigned>(B * Hkv));
     const int row_bytes = static_cast<int>(v->stride[2] * 2);
-    if (D == 64)
-        build_aggregates_sorted_kernel<64><<<grid, kArWarps * 32, 0, stream>>>(
-            ws, static_cast<const __nv_bfloat16 *>(v->ptr), v->stride[0], v->stride[1], row_bytes, static_cast<float *>(cnt->ptr),
-            static_cast<__nv_bfloat16 *>(vsum->ptr), state_cnt, state_vsum, static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB),
-            static_cast<int>(NBT));
-    else
-        build_aggregates_sorted_kernel<128><<<grid, kArWarps * 32, 0, stream>>>(
-            ws, static_cast<const __nv_bfloat16 *>(v->ptr), v->stride[0], v->stride[1], row_bytes, static_cast<float *>(cnt->ptr),
-            static_cast<__nv_bfloat16 *>(vsum->ptr), state_cnt, state_vsum, static_cast<int>(Hkv), static_cast<int>(M), K, static_cast<int>(NB),
-            static_cast<int>(NBT));
+#define VQ_SORTED(DD, ST)                                                                                                          \
+    build_aggregates_sorted_kernel<DD, ST><<<grid, kArWarps * 32, 0, stream>>>(                                                    \
+        ws, static_cast<const __nv_bfloat16 *>(v->ptr), v->stride[0], v->stride[1], row_bytes, static_cast<float *>(cnt->ptr),    \
+        static_cast<__nv_bfloat16 *>(vsum->ptr), state_cnt, state_vsum, static_cast<int>(Hkv), static_cast<int>(M), K,             \
+        static_cast<int>(NB), static_cast<int>(NBT))
+    const bool with_state = state_vsum != nullptr;
+    if (D == 64) {
+        if (with_state) VQ_SORTED(64, true);
+        else VQ_SORTED(64, false);
+    } else {
+        if (with_state) VQ_SORTED(128, true);
+        else VQ_SORTED(128, false);
+    }
+#undef VQ_SORTED
     return launch_status();
 }
 

@@ -29,7 +29,7 @@
 //      candidates of every doubtful codebook (first maximum wins), and - in the rare case that this changes
 //      a code - recomputes every later codebook of that key over all its codewords, since its residual
 //      changed.  The scan kernel never waits for any of this.
-// One CTA owns NS key tiles of 128 keys ("streams", NS = 2 when K <= 256): per stream eight warps,
+// One CTA owns NS key tiles of 128 keys ("streams", NS = 2 when K <= 256 or K = 1024): per stream eight warps,
 // two threads per key, each ranking half of the key's scores in tensor memory and updating half of
 // its residual row (the arithmetic between the MMAs is a chain of dependent instructions and loads
 // from L2: it needs the warps to hide its latency); one warp issues the MMAs of the streams in turn,
@@ -228,14 +228,15 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 for (int hh = 0; hh < NH; ++hh)
                     tma_load_4d(smem + s * 2 * C::kATile + hh * kHalfBytes, &tm_k, &bar_k[s], 64 * hh, (tile0 + s) * kBlock, h, b);
             }
-            // Units in the order the MMA warp consumes them: jobs (codebook m, stream s) with s fastest;
-            // inside a job, per chunk: hi term columns 0-63, 64-127 (D = 128), then the lo term likewise.
+            // Units in the order the MMA warp consumes them: per codebook m the chunks in turn, each chunk for the
+            // streams in turn (so that the scan of one stream's chunk runs under the other stream's MMAs); per
+            // (chunk, stream): hi term columns 0-63, 64-127 (D = 128), then the lo term likewise.
             // (nested counters instead of divisions of a flat index: this thread's instructions are serial)
             bool ok = true;
             int g = 0;
             for (int m = 0; m < M && ok; ++m)
-                for (int s = 0; s < n_act && ok; ++s)
-                    for (int ch = 0; ch < chunks && ok; ++ch)
+                for (int ch = 0; ch < chunks && ok; ++ch)
+                    for (int s = 0; s < n_act && ok; ++s)
 #pragma unroll
                         for (int rem = 0; rem < 2 * NH; ++rem, ++g) {
                             const int slot = g % SL, is_lo = rem / NH, hh = rem % NH;
@@ -259,19 +260,19 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             bool ok = true;
             int g = 0;
             for (int m = 0; m < M && ok; ++m)
-                for (int s = 0; s < n_act && ok; ++s) {
-                    // the residual terms of (s, m): the key tile itself for m = 0, else written by the scan threads
-                    if (!(m == 0 ? mbar_wait(&bar_k[s], 0, p.wait_limit) : mbar_wait(&bar_q[s], (m - 1) & 1, p.wait_limit))) {
-                        ok = false;
-                        break;
-                    }
-                    for (int ch = 0; ch < chunks && ok; ++ch) {
+                for (int ch = 0; ch < chunks && ok; ++ch)
+                    for (int s = 0; s < n_act && ok; ++s) {
+                        // the residual terms of (s, m): the key tile itself for m = 0, else written by the scan threads
+                        if (ch == 0 && !(m == 0 ? mbar_wait(&bar_k[s], 0, p.wait_limit) : mbar_wait(&bar_q[s], (m - 1) & 1, p.wait_limit))) {
+                            ok = false;
+                            break;
+                        }
                         const int cs = wrap ? ch % C::kMaxChunks : ch, use = m * rounds + (wrap ? ch / C::kMaxChunks : 0);
                         if (wrap && use >= 1 && !mbar_wait(&c_free[s][cs], (use - 1) & 1, p.wait_limit)) {   // the slot's previous chunk has been scanned
                             ok = false;
                             break;
                         }
-                        if (wrap) tc_fence_after();
+                        if (ch == 0 || wrap) tc_fence_after();
                         const uint32_t dcol = tmem + s * C::kRegion + cs * CH;
 #pragma unroll
                         for (int rem = 0; rem < 2 * NH; ++rem, ++g) {
@@ -297,7 +298,6 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                             if (rem == 2 * NH - 1) tc_commit(&bar_c[s][cs]);  // this chunk's score columns are complete
                         }
                     }
-                }
             if (!ok) s_err = 1;
         }
     } else if (warp / C::kScanWarps < n_act) {
@@ -782,9 +782,15 @@ extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc 
     if (K == 256)
         return D == 64 ? launch_assign_tc<64, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s)
                        : launch_assign_tc<128, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s);
-    if (K == 512 || K == 1024)   // K = 1024: four chunks through a region of two
+    // K = 512: one stream with both chunks resident (measured faster than two streams taking the chunks in rounds, whose
+    // doubtful keys the repair kernel has to score against the whole codebook); K = 1024: two streams, four chunks
+    // in rounds through each stream's 256-column region
+    if (K == 512)
         return D == 64 ? launch_assign_tc<64, 1, 256>(k, codebooks, bias, codes, workspace, status_word, s)
                        : launch_assign_tc<128, 1, 256>(k, codebooks, bias, codes, workspace, status_word, s);
+    if (K == 1024)
+        return D == 64 ? launch_assign_tc<64, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s)
+                       : launch_assign_tc<128, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s);
     return D == 64 ? launch_assign_tc<64, 1, 128>(k, codebooks, bias, codes, workspace, status_word, s)   // K = 384
                    : launch_assign_tc<128, 1, 128>(k, codebooks, bias, codes, workspace, status_word, s);
 }
