@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define VQATTN_VERSION 200
+#define VQATTN_VERSION 201
 #define VQATTN_BLOCK 128   /* key/query block size; ops/attn_vq.py:23 BLOCK_SIZE ("MUST MATCH KERNEL") */
 #define VQATTN_MAX_DIMS 5
 
