@@ -574,6 +574,38 @@ def test_prefill_fp16_matches_naive_oracle(api, impl, B, Hq, Hkv, L, D, M, K, W,
     assert np.abs(got - want).max() <= 2e-2
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,W,MK", [(3, 24, 8, 900, 512), (8, 32, 8, 2112, 2048)])
+def test_decode_partial_merge_is_deterministic(api, B, Hq, Hkv, W, MK):
+    """Units split over several CTAs are merged from per-CTA partials by whichever CTA arrives last, in a fixed
+    order: repeated calls on the same inputs give the same bits (a stale read of another CTA's partial would not),
+    and they agree with an fp32 evaluation of the step."""
+    D = 128
+    g = torch.Generator().manual_seed(7)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    cnt = dev(torch.randint(0, 60, (B, Hkv, MK), generator=g).float())
+    q, k, v = dev(rn(B, Hq, D).bfloat16()), dev(rn(B, Hkv, W, D).bfloat16()), dev(rn(B, Hkv, W, D).bfloat16())
+    vsum = (dev(rn(B, Hkv, MK, D)) * cnt[..., None].sqrt()).bfloat16()
+    cbd = dev((rn(Hkv, MK, D) * D ** -0.25).bfloat16())
+    ws = api.decode_workspace(B, Hq, Hkv, D, "cuda")
+    first = api.vq_attention_decode(q, q, k, k, v, cbd, cnt, vsum, workspace=ws).clone()
+    differing = 0
+    for _ in range(300):
+        o = api.vq_attention_decode(q, q, k, k, v, cbd, cnt, vsum, workspace=ws)
+        differing += int(not torch.equal(o.view(torch.int16), first.view(torch.int16)))
+    torch.cuda.synchronize()
+    api.check_status()
+    assert differing == 0
+    qf = q.float().view(B, Hkv, Hq // Hkv, D)
+    s_w = torch.einsum("bhgd,bhwd->bhgw", qf, k.float()) / D ** 0.5
+    s_f = (torch.einsum("bhgd,hcd->bhgc", qf, cbd.float()) / D ** 0.5).masked_fill((cnt <= 0)[:, :, None, :], float("-inf"))
+    m = torch.maximum(s_w.amax(-1), s_f.amax(-1))[..., None]
+    pw, pf = (s_w - m).exp(), (s_f - m).exp()
+    den = pw.sum(-1) + (pf * cnt[:, :, None, :]).sum(-1)
+    num = torch.einsum("bhgw,bhwd->bhgd", pw, v.float()) + torch.einsum("bhgc,bhcd->bhgd", pf, vsum.float())
+    want = (num / den[..., None]).view(B, Hq, D)
+    assert float((first.float() - want).abs().max()) < 2e-2     # bf16 output; observed 1e-4
+
+
 def test_decode_fp16_matches_oracle(api):
     B, Hq, Hkv, D, M, K, W, L = 2, 4, 2, 128, 2, 128, 128, 640
     case = make_case(B, Hq, Hkv, L, D, M, K, W, 23, True, torch.float16)
