@@ -4,6 +4,9 @@
 
 The shared object exports only the C ABI declared in ``include/vqattn.h``.  It is not a Python
 extension: the host layer binds it with ctypes, any other host language can bind it the same way.
+``build_torch_ext`` compiles the PyTorch C++ extension over that ABI (``lib/libvqattn_torch.so``:
+``csrc/torch_ext.cpp``, host code only, g++ against the installed torch headers), which registers the
+entry points as ``torch.ops.vqattn.*``.
 """
 from __future__ import annotations
 
@@ -72,9 +75,47 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+TORCH_EXT = LIBDIR / "libvqattn_torch.so"
+
+
+def build_torch_ext(force: bool = False, verbose: bool = False) -> Path:
+    """g++ build of csrc/torch_ext.cpp against the installed torch; links libvqattn.so from the same folder."""
+    import torch
+    from torch.utils import cpp_extension
+    lib = build(force=False, verbose=verbose)
+    src = CSRC / "torch_ext.cpp"
+    if not force and not _stale(TORCH_EXT, [src, lib, ROOT / "include" / "vqattn.h"]):
+        return TORCH_EXT
+    # The system compiler, whose libstdc++ is the shared one the process already runs on.  ($CXX may name a
+    # toolchain that links its own libstdc++ statically into the extension: that private copy's stream locale is
+    # never initialised, and formatting an error message through it crashes.)
+    cxx = next((c for c in ("/usr/bin/g++", shutil.which("g++"), os.environ.get("CXX")) if c and Path(c).exists()), "g++")
+    cuda_home = os.environ.get("CUDA_HOME") or str(Path(nvcc_path()).resolve().parent.parent)
+    torch_lib = Path(torch.__file__).resolve().parent / "lib"
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-Wno-unknown-pragmas",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for inc in cpp_extension.include_paths() + [str(Path(cuda_home) / "include"), str(ROOT / "include")]:
+        cmd += ["-isystem" if "torch" in inc or "cuda" in inc else "-I", inc]
+    cmd += [str(src), "-o", str(TORCH_EXT), f"-L{torch_lib}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
+            f"-L{LIBDIR}", "-lvqattn", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed on torch_ext.cpp")
+    nm = shutil.which("nm")
+    if nm:   # a statically linked libstdc++ shows as thousands of std:: definitions in the dynamic symbol table
+        syms = subprocess.run([nm, "-D", "--defined-only", str(TORCH_EXT)], capture_output=True, text=True).stdout
+        if "_ZNSo9_M_insertIlEERSoT_" in syms:
+            TORCH_EXT.unlink()
+            raise RuntimeError(f"{cxx} linked libstdc++ statically into the extension; build it with the system g++")
+    return TORCH_EXT
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args()
     print(build(a.force, a.verbose))
+    print(build_torch_ext(a.force, a.verbose))
