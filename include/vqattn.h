@@ -259,7 +259,7 @@ int vqattn_decode_static(const VqDecodeArgs *args, void *stream);
  * cos_tab, sin_tab: device fp32 tables [n_pos, D/2] (angle = pos * base^(-2i/D)).  Products and sum
  * are rounded separately in fp32, then once to the output dtype.  A position outside [0, n_pos)
  * sets *status_word to VQ_WORD_BAD_POSITION (status_word may be NULL) and uses the nearest table row.
- * Constraints: D % 16 == 0 (bf16) or D % 8 == 0 (f32); 16-byte aligned rows.
+ * Constraints: D % 16 == 0 (bf16) or D % 8 == 0 (f32); 16-byte aligned rows and tables.
  */
 int vqattn_rope(const VqTensorDesc *x, const int64_t *positions, const float *cos_tab, const float *sin_tab, int64_t n_pos,
                 int64_t const_pos, VqTensorDesc *out_pos, VqTensorDesc *out_const, int32_t *status_word, void *stream);

@@ -69,11 +69,18 @@ template <> struct RopeVec<__half> {
 template <int N>
 __device__ __forceinline__ void rope_rotate(const float (&x1)[N], const float (&x2)[N], const float *c, const float *s, float (&o1)[N], float (&o2)[N])
 {
+    // the table rows start on 16-byte boundaries (D/2 and d are multiples of four floats): 128-bit loads
+    static_assert(N % 4 == 0, "vector width");
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
-        const float ci = __ldg(c + i), si = __ldg(s + i);
-        o1[i] = __fadd_rn(__fmul_rn(x1[i], ci), __fmul_rn(-x2[i], si));
-        o2[i] = __fadd_rn(__fmul_rn(x2[i], ci), __fmul_rn(x1[i], si));
+    for (int i4 = 0; i4 < N / 4; ++i4) {
+        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(c) + i4), s4 = __ldg(reinterpret_cast<const float4 *>(s) + i4);
+        const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = 4 * i4 + e;
+            o1[i] = __fadd_rn(__fmul_rn(x1[i], cv[e]), __fmul_rn(-x2[i], sv[e]));
+            o2[i] = __fadd_rn(__fmul_rn(x2[i], cv[e]), __fmul_rn(x1[i], sv[e]));
+        }
     }
 }
 
@@ -92,9 +99,19 @@ __global__ void __launch_bounds__(256) rope_kernel(const T *__restrict__ x, int6
          i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int64_t r = i / tpr;
         const int d = static_cast<int>(i % tpr) * N;
-        const int64_t l = r % L, bh = r / L;
-        const int h = static_cast<int>(bh % H);
-        const int64_t b = bh / H;
+        // rows in the order they lie in memory: heads vary fastest when the tensor is a [B,H,L,D] view of [B,L,H,D]
+        // storage (consecutive work items then touch consecutive addresses instead of 256 bytes in every H*D)
+        int64_t l, b;
+        int h;
+        if (x_sh < x_sl) {
+            h = static_cast<int>(r % H);
+            l = (r / H) % L;
+            b = r / (static_cast<int64_t>(H) * L);
+        } else {
+            l = r % L;
+            h = static_cast<int>((r / L) % H);
+            b = r / (static_cast<int64_t>(H) * L);
+        }
         float x1[N], x2[N], o1[N], o2[N];
         const T *xp = x + b * x_sb + h * x_sh + l * x_sl + d;
         RopeVec<T>::load(xp, x1);
@@ -160,9 +177,18 @@ __global__ void __launch_bounds__(256) rope_multi_kernel(const RopeMultiParams p
         const int64_t w = i - jb.first;
         const int64_t r = w / tpr;
         const int d = static_cast<int>(w % tpr) * N;
-        const int64_t l = r % p.L, bh = r / p.L;
-        const int h = static_cast<int>(bh % jb.H);
-        const int64_t b = bh / jb.H;
+        // rows in the order they lie in memory (see rope_kernel)
+        int64_t l, b;
+        int h;
+        if (jb.x_sh < jb.x_sl) {
+            h = static_cast<int>(r % jb.H);
+            l = (r / jb.H) % p.L;
+            b = r / (static_cast<int64_t>(jb.H) * p.L);
+        } else {
+            l = r % p.L;
+            h = static_cast<int>((r / p.L) % jb.H);
+            b = r / (static_cast<int64_t>(jb.H) * p.L);
+        }
         float x1[N], x2[N], o1[N], o2[N];
         const T *xp = static_cast<const T *>(jb.x) + b * jb.x_sb + h * jb.x_sh + l * jb.x_sl + d;
         RopeVec<T>::load(xp, x1);
@@ -252,6 +278,7 @@ extern "C" int vqattn_rope(const VqTensorDesc *x, const int64_t *positions, cons
     if (out_const != nullptr && out_const->ptr == nullptr) out_const = nullptr;
     if ((st = check_basic(x, 4)) != VQ_OK) return st;
     if (cos_tab == nullptr || sin_tab == nullptr || n_pos <= 0 || (out_pos == nullptr && out_const == nullptr)) return VQ_EINVAL_ARG;
+    if (reinterpret_cast<uintptr_t>(cos_tab) % 16 || reinterpret_cast<uintptr_t>(sin_tab) % 16) return VQ_EINVAL_STRIDE;   // 128-bit table loads
     if (out_const != nullptr && (const_pos < 0 || const_pos >= n_pos)) return VQ_EINVAL_ARG;
     if (!is_act_dtype(x->dtype)) return VQ_EINVAL_DTYPE;
     const int64_t B = x->shape[0], H = x->shape[1], L = x->shape[2], D = x->shape[3];
@@ -298,6 +325,7 @@ extern "C" int vqattn_rope_qk(const VqTensorDesc *q, const VqTensorDesc *k, cons
     using namespace vq;
     if (q == nullptr || k == nullptr || q1 == nullptr || k1 == nullptr || cos_tab == nullptr || sin_tab == nullptr || n_pos <= 0)
         return VQ_EINVAL_ARG;
+    if (reinterpret_cast<uintptr_t>(cos_tab) % 16 || reinterpret_cast<uintptr_t>(sin_tab) % 16) return VQ_EINVAL_STRIDE;   // 128-bit table loads
     const bool want_q2 = q2 != nullptr && q2->ptr != nullptr;
     if (want_q2 && (const_pos < 0 || const_pos >= n_pos)) return VQ_EINVAL_ARG;
     if (q->ndim != 4 || k->ndim != 4) return VQ_EINVAL_SHAPE;
@@ -327,6 +355,7 @@ extern "C" int vqattn_decode_append(const VqTensorDesc *q, const VqTensorDesc *k
     if (q == nullptr || k == nullptr || v == nullptr || q1 == nullptr || q2 == nullptr || k1_win == nullptr || k3_win == nullptr ||
         v_win == nullptr || cos_tab == nullptr || sin_tab == nullptr || n_pos <= 0)
         return VQ_EINVAL_ARG;
+    if (reinterpret_cast<uintptr_t>(cos_tab) % 16 || reinterpret_cast<uintptr_t>(sin_tab) % 16) return VQ_EINVAL_STRIDE;   // 128-bit table loads
     if (const_pos < 0 || const_pos >= n_pos) return VQ_EINVAL_ARG;
     if (q->ndim != 4 || k->ndim != 4 || v->ndim != 4 || q->shape[2] != 1) return VQ_EINVAL_SHAPE;
     if (!is_act_dtype(q->dtype) || k->dtype != q->dtype || v->dtype != q->dtype) return VQ_EINVAL_DTYPE;
