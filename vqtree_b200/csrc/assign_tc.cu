@@ -392,7 +392,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             }
             if (!ok) break;
             // ---- the two halves meet: the upper half hands its result over, the lower half merges (a tie between
-            // the halves goes to the lower one, which holds the lower codes) and hands the verdict back
+            // the halves goes to the lower one, which holds the lower codes) and hands the result back
             int code;
             if (hf == 1) {
                 *xch = make_float4(best, second, __int_as_float(bgrp), __uint_as_float(gbits));
