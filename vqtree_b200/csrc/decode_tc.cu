@@ -12,7 +12,12 @@
 //   warp 4  (one lane) issues the MMAs: scores of tile t+1 before the product of tile t;
 //   warps 0-3 softmax: thread i reads the scores of row i, masks, exponentiates against a reference
 //           maximum kept per head (raised, with O rescaled, only when a score exceeds it by 2^8 -
-//           an OR over the four warps tells), adds to its partial denominators and writes P for the product.
+//           an OR over the four warps tells), adds to its partial denominators and writes P for the product;
+//           at the end of a unit it hands the denominators to the write-out warps and goes on with the next
+//           unit, which accumulates in the other of two O^T buffers;
+//   warps 6-9 write-out: thread d reads column d of a finished unit's O^T buffer once the unit's last product
+//           has completed, releases the buffer, and normalises and stores the output row - or, for a unit
+//           shared with other CTAs, publishes this CTA's partial and merges the unit if it is the last contributor.
 // The global list of tiles is split evenly over the CTAs (a range may start or end inside a unit);
 // a CTA writes one partial (numerator, maximum, denominator) per unit it touched and the last CTA
 // of a unit (atomic ticket) merges them - the same workspace protocol as the SIMT bulk kernel.
@@ -27,7 +32,7 @@ using namespace ptx;
 constexpr int kDtRows = 128;       // rows per tile
 constexpr int kDtStages = 3;
 constexpr int kDtN = 16;           // query heads per MMA (columns of S^T and O^T)
-constexpr int kDtThreads = 192;    // 4 softmax warps + MMA warp + TMA warp
+constexpr int kDtThreads = 320;    // 4 softmax warps + MMA warp + TMA warp + 4 write-out warps
 constexpr int kDtD = 128;
 constexpr int kDtTile = kDtRows * kDtD * 2;             // 32 KB
 constexpr int kDtStageBytes = 2 * kDtTile;              // key-like tile, value tile
@@ -107,10 +112,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ __align__(8) uint64_t full[NS], empty[NS], q_full[2], q_free[2], s_ready[2], p_ready[2], o_done[2];
+    __shared__ __align__(8) uint64_t o_final[2], f_req[2], f_done[2];   // hand-offs with the write-out warps, one set per O^T buffer
+    __shared__ float s_wlr[2][4][kDtN], s_mr[2][kDtN];                  // a finished unit's denominators (per softmax warp) and references
     __shared__ uint32_t s_tmem;
     __shared__ int s_err, s_last;
     __shared__ uint32_t s_flag[2][4];
-    __shared__ float s_wm[4][kDtN], s_wl[4][kDtN];
+    __shared__ float s_wm[4][kDtN];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = p.G, TU = bp.TU;
@@ -134,6 +141,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             mbar_init(&s_ready[i], 1);
             mbar_init(&p_ready[i], 4);
             mbar_init(&o_done[i], 1);
+            mbar_init(&o_final[i], 1);
+            mbar_init(&f_req[i], 4);
+            mbar_init(&f_done[i], 1);
         }
         fence_mbar_init();
         s_err = 0;
@@ -254,7 +264,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                 const int st = t % NS, sb = t & 1;
                 if (++tt_p == TU) tt_p = 0;
                 const bool first_of_seg = (t == 0) || tt_p == 0;
-                if (first_of_seg) ++seg_p;
+                if (first_of_seg) {
+                    ++seg_p;
+                    // this segment's O^T buffer was used two segments ago: the write-out warps must have read it
+                    if (seg_p >= 2 && !mbar_wait(&f_done[seg_p & 1], ((seg_p >> 1) - 1) & 1, bp.wait_limit)) {
+                        ok = false;
+                        return;
+                    }
+                }
                 if (!mbar_wait(&p_ready[sb], (t >> 1) & 1, bp.wait_limit)) {
                     ok = false;
                     return;
@@ -269,6 +286,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
                            (!first_of_seg || kk) ? 1u : 0u);
                 tc_commit(&empty[st]);
                 tc_commit(&o_done[sb]);
+                if (t + 1 == n_items || tt_p + 1 == TU) tc_commit(&o_final[seg_p & 1]);   // the segment's accumulator is complete
             };
             if (n_items > 0) scores(0);
             for (int t = 0; t < n_items; ++t) {
@@ -277,8 +295,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             }
             if (!ok) s_err = 1;
         }
-    } else {
-        // ================================================================== softmax (thread = row of a tile, and column d of O^T)
+    } else if (warp < 4) {
+        // ================================================================== softmax (thread = row of a tile)
         constexpr unsigned kAll = 0xffffffffu;
         const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
         float m_ref[kDtN], l_part[kDtN];
@@ -288,14 +306,8 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             l_part[g] = 0.f;
         }
         bool ok = true;
-        int cur_ue = -1, last_t = -1, obuf = 1;
-        int pend_ue = -1, pend_t = -1, pend_buf = 0;   // a finished unit that has not been written out yet
-        float m_prev[kDtN], l_prev[kDtN];
-#pragma unroll
-        for (int g = 0; g < kDtN; ++g) {
-            m_prev[g] = -INFINITY;
-            l_prev[g] = 0.f;
-        }
+        int cur_ue = -1, obuf = 1;
+        int req = 0;            // unit segments handed to the write-out warps so far
         uint32_t xph = 0;
         // Barrier of the 128 softmax threads (hardware barrier 1) that also ORs their failure flags: when a bounded wait
         // has expired in any of them, all four warps learn it at the same barrier and leave together - nobody is left
@@ -316,104 +328,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             return failed == 0;
         };
 
-        // write this CTA's partial of unit `ue` (its last tile was t_last) and let the last contributor merge the unit
-        // (ue: the unit; t_last: its last tile in this CTA; obuf: its O^T buffer; lp, mr: its denominators and references)
-        auto flush = [&](int ue, int t_last, int obuf, const float (&lp)[kDtN], const float (&mr)[kDtN]) {
-            if (!__all_sync(kAll, mbar_wait(&o_done[t_last & 1], (t_last >> 1) & 1, bp.wait_limit))) ok = false;   // known to all at the barrier below
-            tc_fence_after();
-            uint32_t o[16];
-            tmem_ld16(tmem + lane_off + 32 + 16 * obuf, o);
-            tc_wait_ld();
-            // denominators: sum of the 128 threads' partial sums
-#pragma unroll
-            for (int g = 0; g < kDtN; ++g)
-                if (g < G) {
-                    float v = lp[g];
-#pragma unroll
-                    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(kAll, v, off);
-                    if (lane == 0) s_wl[warp][g] = v;
-                }
-            if (!sync4()) return;
-            // (s_wl is written again at the next flush; every tile in between passes a barrier)
-            if (static_cast<int64_t>(ue) * TU >= g0 && static_cast<int64_t>(ue + 1) * TU <= g1) {
-                // the whole unit was processed by this CTA: normalise and write the output row directly
-                const int b = ue / p.Hkv, hk = ue % p.Hkv;
-#pragma unroll
-                for (int g = 0; g < kDtN; ++g)
-                    if (g < G) {
-                        const float den = (s_wl[0][g] + s_wl[1][g]) + (s_wl[2][g] + s_wl[3][g]);
-                        static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hk * G + g) * p.o_sh + tid] =
-                            __float2bfloat16_rn(__uint_as_float(o[g]) / den);
-                    }
-                return;
-            }
-            const int first_c = static_cast<int>(((static_cast<int64_t>(ue) * TU + 1) * NC - 1) / T);
-            const int last_c = static_cast<int>(((static_cast<int64_t>(ue + 1) * TU) * NC - 1) / T);
-            float *part = bp.partial + static_cast<int64_t>(c + ue) * G * (D + 2);
-#pragma unroll
-            for (int g = 0; g < kDtN; ++g)
-                if (g < G) {
-                    part[g * (D + 2) + tid] = __uint_as_float(o[g]);
-                    if (tid == 0) {
-                        part[g * (D + 2) + D] = mr[g];
-                        part[g * (D + 2) + D + 1] = (s_wl[0][g] + s_wl[1][g]) + (s_wl[2][g] + s_wl[3][g]);
-                    }
-                }
-            // Publication: the barrier orders the 128 threads' partial stores before thread 0's ticket increment, whose
-            // release makes them visible device-wide together with it; the last contributor's acquire (the same
-            // instruction) and the barrier after it order every thread's loads behind the other CTAs' partials.
-            if (!sync4()) return;
-            if (tid == 0) {
-                int tk;
-                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(tk) : "l"(bp.ticket + ue) : "memory");
-                s_last = (tk == last_c - first_c);
-            }
-            if (!sync4()) return;
-            if (s_last) {
-                // merge of the contributors' partials, four heads at a time: one pass over the contributors with a
-                // running maximum (all loads of a contributor are independent and in flight together)
-                const int b = ue / p.Hkv, hk = ue % p.Hkv;
-#pragma unroll 1
-                for (int gq = 0; gq < G; gq += 4) {
-                    float M[4], num[4], den[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        M[i] = -INFINITY;
-                        num[i] = 0.f;
-                        den[i] = 0.f;
-                    }
-#pragma unroll 2
-                    for (int cc = first_c; cc <= last_c; ++cc) {
-                        const float *pc = bp.partial + (static_cast<int64_t>(cc + ue) * G + gq) * (D + 2);
-                        float ms[4], x[4], dd[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const bool on = gq + i < G;
-                            ms[i] = on ? __ldcg(pc + i * (D + 2) + D) : -INFINITY;
-                            x[i] = on ? __ldcg(pc + i * (D + 2) + tid) : 0.f;
-                            dd[i] = on ? __ldcg(pc + i * (D + 2) + D + 1) : 0.f;
-                        }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float mn = fmaxf(M[i], ms[i]);
-                            const float a = (M[i] == -INFINITY) ? 0.f : exp2f(M[i] - mn);
-                            const float w = (ms[i] == -INFINITY) ? 0.f : exp2f(ms[i] - mn);
-                            num[i] = fmaf(num[i], a, w * x[i]);
-                            den[i] = fmaf(den[i], a, w * dd[i]);
-                            M[i] = mn;
-                        }
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (gq + i < G)
-                            static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hk * G + gq + i) * p.o_sh + tid] =
-                                __float2bfloat16_rn(num[i] / den[i]);
-                }
-                if (tid == 0) bp.ticket[ue] = 0;  // ready for the next call on this stream
-            }
-            // (s_last is written again at the next flush, after the barriers of the tiles in between - or never)
-        };
-
         int ue = ue0, tt = tt0 - 1;
         for (int t = 0; t < n_items; ++t) {
             const int st = t % NS, sb = t & 1;
@@ -423,27 +337,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             }
             const bool first_of_seg = ue != cur_ue;
             if (first_of_seg) {
-                // The unit that ends here is written out AFTER this tile (see below): its last product is still in
-                // flight, and the new unit accumulates in the other O^T buffer, so nothing has to wait for it.
-                if (cur_ue >= 0) {
-                    pend_ue = cur_ue;
-                    pend_t = last_t;
-                    pend_buf = obuf;
-#pragma unroll
-                    for (int gg = 0; gg < kDtN; ++gg) {
-                        m_prev[gg] = m_ref[gg];
-                        l_prev[gg] = l_part[gg];
-                    }
-                }
                 cur_ue = ue;
-                obuf ^= 1;
+                obuf ^= 1;      // the unit segments alternate between the two O^T buffers
 #pragma unroll
                 for (int gg = 0; gg < kDtN; ++gg) {
                     m_ref[gg] = -INFINITY;
                     l_part[gg] = 0.f;
                 }
             }
-            last_t = t;
             const DtItem it = dt_item(bp, tt);
             // the counts of a far tile arrive with the tile; the scores once the MMAs have finished
             // a wait that expires marks this warp as failed; the four warps find out together at the next barrier
@@ -521,15 +422,149 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k1, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[sb]);
-            if (pend_ue >= 0) {
-                flush(pend_ue, pend_t, pend_buf, l_prev, m_prev);
-                pend_ue = -1;
-                if (!ok) break;   // decided at a barrier: the same in all four warps
+            if (t + 1 == n_items || tt + 1 == TU) {
+                // ---- the unit segment ends here: its denominators (summed over this warp's 32 rows) and references go to
+                // the write-out warps, which wait for the segment's last product themselves; nothing here waits for them
+                // except for the slot of the segment before last to be free again
+                const int slot = req & 1;
+                if (req >= 2 && !__all_sync(kAll, mbar_wait(&f_done[slot], ((req >> 1) - 1) & 1, bp.wait_limit))) ok = false;
+#pragma unroll
+                for (int gg = 0; gg < kDtN; ++gg)
+                    if (gg < G) {
+                        float v = l_part[gg];
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(kAll, v, off);
+                        if (lane == 0) {
+                            s_wlr[slot][warp][gg] = v;
+                            if (warp == 0) s_mr[slot][gg] = m_ref[gg];
+                        }
+                    }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&f_req[slot]);
+                ++req;
             }
         }
-        // ok was last decided at a barrier: the same in all four warps.  The barrier in between: the write-out of the
-        // previous unit may have run just before (a last unit of one tile) and still be reading the shared sums.
-        if (ok && cur_ue >= 0 && sync4()) flush(cur_ue, last_t, obuf, l_part, m_ref);
+        if (!ok) s_err = 1;
+    } else if (warp >= 6) {
+        // ================================================================== write-out (thread = column d of O^T)
+        // Warps 6-9 take a finished unit segment off the softmax warps: they read its O^T buffer once the segment's
+        // last product has finished, release the buffer, and then normalise and write the output row (a unit this CTA
+        // processed alone) or publish this CTA's partial and, as the last contributor, merge the unit.
+        constexpr unsigned kAll = 0xffffffffu;
+        const int q = warp & 3;                              // the TMEM lane quarter this warp may read
+        const int dcol = q * 32 + lane;                      // column of O^T = element d of the output rows
+        const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+        const bool lead = warp == 6 && lane == 0;
+        bool ok = true;
+        auto syncf = [&]() {                                 // hardware barrier 2: the 128 write-out threads, failure flags ORed
+            uint32_t failed;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.u32 q, %1, 0;\n\t"
+                "bar.red.or.pred p, 2, 128, q;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(failed)
+                : "r"(ok ? 0u : 1u)
+                : "memory");
+            if (failed) ok = false;
+            return failed == 0;
+        };
+        const int nseg = n_items > 0 ? static_cast<int>((g1 - 1) / TU) - ue0 + 1 : 0;
+#pragma unroll 1
+        for (int r = 0; r < nseg; ++r) {
+            const int slot = r & 1, ue = ue0 + r;
+            const uint32_t par = static_cast<uint32_t>(r >> 1) & 1u;
+            if (!__all_sync(kAll, mbar_wait(&f_req[slot], par, bp.wait_limit) && mbar_wait(&o_final[slot], par, bp.wait_limit))) ok = false;
+            tc_fence_after();
+            uint32_t o[16];
+            tmem_ld16(tmem + lane_off + 32 + 16 * slot, o);
+            tc_wait_ld();
+            float den[kDtN], mr[kDtN];
+#pragma unroll
+            for (int g = 0; g < kDtN; ++g) {
+                den[g] = g < G ? (s_wlr[slot][0][g] + s_wlr[slot][1][g]) + (s_wlr[slot][2][g] + s_wlr[slot][3][g]) : 1.f;
+                mr[g] = g < G ? s_mr[slot][g] : 0.f;
+            }
+            tc_fence_before();
+            if (!syncf()) break;
+            if (lead) mbar_arrive(&f_done[slot]);            // buffer and sums have been read by all 128 threads
+            if (static_cast<int64_t>(ue) * TU >= g0 && static_cast<int64_t>(ue + 1) * TU <= g1) {
+                // the whole unit was processed by this CTA: normalise and write the output row directly
+                const int b = ue / p.Hkv, hk = ue % p.Hkv;
+#pragma unroll
+                for (int g = 0; g < kDtN; ++g)
+                    if (g < G)
+                        static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hk * G + g) * p.o_sh + dcol] =
+                            __float2bfloat16_rn(__uint_as_float(o[g]) / den[g]);
+                continue;
+            }
+            const int first_c = static_cast<int>(((static_cast<int64_t>(ue) * TU + 1) * NC - 1) / T);
+            const int last_c = static_cast<int>(((static_cast<int64_t>(ue + 1) * TU) * NC - 1) / T);
+            float *part = bp.partial + static_cast<int64_t>(c + ue) * G * (D + 2);
+#pragma unroll
+            for (int g = 0; g < kDtN; ++g)
+                if (g < G) {
+                    part[g * (D + 2) + dcol] = __uint_as_float(o[g]);
+                    if (dcol == 0) {
+                        part[g * (D + 2) + D] = mr[g];
+                        part[g * (D + 2) + D + 1] = den[g];
+                    }
+                }
+            // Publication: the barrier orders the 128 threads' partial stores before the lead thread's ticket increment,
+            // whose release makes them visible device-wide together with it; the last contributor's acquire (the same
+            // instruction) and the barrier after it order every thread's loads behind the other CTAs' partials.
+            if (!syncf()) break;
+            if (lead) {
+                int tk;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(tk) : "l"(bp.ticket + ue) : "memory");
+                s_last = (tk == last_c - first_c);
+            }
+            if (!syncf()) break;
+            const bool last = s_last != 0;
+            if (!syncf()) break;                             // s_last may be rewritten for the next segment
+            if (last) {
+                // merge of the contributors' partials, four heads at a time: one pass over the contributors with a
+                // running maximum (all loads of a contributor are independent and in flight together)
+                const int b = ue / p.Hkv, hk = ue % p.Hkv;
+#pragma unroll 1
+                for (int gq = 0; gq < G; gq += 4) {
+                    float M[4], num[4], dd4[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        M[i] = -INFINITY;
+                        num[i] = 0.f;
+                        dd4[i] = 0.f;
+                    }
+#pragma unroll 2
+                    for (int cc = first_c; cc <= last_c; ++cc) {
+                        const float *pc = bp.partial + (static_cast<int64_t>(cc + ue) * G + gq) * (D + 2);
+                        float ms[4], x[4], dd[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const bool on = gq + i < G;
+                            ms[i] = on ? __ldcg(pc + i * (D + 2) + D) : -INFINITY;
+                            x[i] = on ? __ldcg(pc + i * (D + 2) + dcol) : 0.f;
+                            dd[i] = on ? __ldcg(pc + i * (D + 2) + D + 1) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float mn = fmaxf(M[i], ms[i]);
+                            const float a = (M[i] == -INFINITY) ? 0.f : exp2f(M[i] - mn);
+                            const float w = (ms[i] == -INFINITY) ? 0.f : exp2f(ms[i] - mn);
+                            num[i] = fmaf(num[i], a, w * x[i]);
+                            dd4[i] = fmaf(dd4[i], a, w * dd[i]);
+                            M[i] = mn;
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (gq + i < G)
+                            static_cast<__nv_bfloat16 *>(p.out)[b * p.o_sb + (hk * G + gq + i) * p.o_sh + dcol] =
+                                __float2bfloat16_rn(num[i] / dd4[i]);
+                }
+                if (lead) bp.ticket[ue] = 0;  // ready for the next call on this stream
+            }
+        }
         if (!ok) s_err = 1;
     }
     tc_fence_before();
