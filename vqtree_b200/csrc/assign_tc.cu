@@ -29,7 +29,14 @@
 //      candidates of every doubtful codebook (first maximum wins), and - in the rare case that this changes
 //      a code - recomputes every later codebook of that key over all its codewords, since its residual
 //      changed.  The scan kernel never waits for any of this.
-// One CTA owns NS key tiles of 128 keys ("streams", NS = 2 when K <= 256 or K = 1024): per stream eight warps,
+//      When a codebook is larger than the 256 score columns a stream owns in tensor memory (K = 512, 1024), its
+//      chunks pass through that region in rounds and the scores of a chunk are gone once the next one lands.  The
+//      candidates are then tracked during the scan: best, runner-up (each with its group of 32 codes) and the third
+//      largest of all group maxima and group runners-up.  If the third lies below the cut and no group's runner-up
+//      ever came within thr of the running best (the 30 unranked scores of a group are at most its runner-up, and
+//      the cut only rises with the running best), the best and the runner-up are the only candidates; otherwise,
+//      and always with a bias (thr then moves with the best score), the record says "all of them".
+// One CTA owns NS key tiles of 128 keys ("streams", NS = 2 except for K = 384): per stream eight warps,
 // two threads per key, each ranking half of the key's scores in tensor memory and updating half of
 // its residual row (the arithmetic between the MMAs is a chain of dependent instructions and loads
 // from L2: it needs the warps to hide its latency); one warp issues the MMAs of the streams in turn,
@@ -48,17 +55,20 @@ constexpr int kAtRepairWarps = 4;  // warps per CTA of the repair kernel (one do
 
 // ------------------------------------------------------------------------------------------------
 // fp32 codebook -> bf16 hi / lo terms [Hkv, M*K, D], the squared norm of every row and the largest row
-// norm of every codebook.
+// norm of every codebook (grid.x: codebook, grid.y: slices of kSplitRows rows; cmax zeroed by the launcher, the
+// slices meet in it through an atomic maximum on the bits of their non-negative norms).
+constexpr int kSplitRows = 64;
 __global__ void __launch_bounds__(256)
 split_codebook_kernel(const float *__restrict__ cb, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo,
                       float *__restrict__ cmax, float *__restrict__ cn2, unsigned int *__restrict__ work_count, int K, int D)
 {
     __shared__ float s_max[8];
-    if (blockIdx.x == 0 && threadIdx.x < 2) work_count[threadIdx.x] = 0u;   // the scan kernel that follows fills the lists
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 2) work_count[threadIdx.x] = 0u;   // the scan kernel that follows fills the lists
     const int hm = blockIdx.x;  // h * M + m
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float wmax = 0.f;
-    for (int c = warp; c < K; c += 8) {
+    const int c_end = min(K, (static_cast<int>(blockIdx.y) + 1) * kSplitRows);
+    for (int c = static_cast<int>(blockIdx.y) * kSplitRows + warp; c < c_end; c += 8) {
         const int64_t row = static_cast<int64_t>(hm) * K + c;
         float ss = 0.f;
         for (int d = lane; d < D; d += 32) {
@@ -79,7 +89,7 @@ split_codebook_kernel(const float *__restrict__ cb, __nv_bfloat16 *__restrict__ 
     if (threadIdx.x == 0) {
         float m = 0.f;
         for (int w = 0; w < 8; ++w) m = fmaxf(m, s_max[w]);
-        cmax[hm] = m * 1.0001f;  // sqrt / summation rounding
+        atomicMax(reinterpret_cast<unsigned int *>(cmax + hm), __float_as_uint(m * 1.0001f));  // sqrt / summation rounding
     }
 }
 
@@ -161,7 +171,8 @@ __device__ __forceinline__ void load_scores(uint32_t taddr, const float *bm, int
     }
 }
 
-template <int D, int NS, int CH>
+// WRAP: a codebook has more chunks than the stream's score region holds and goes through it in rounds.
+template <int D, int NS, int CH, bool WRAP>
 __global__ void __launch_bounds__(AtCfg<D, NS, CH>::kThreads, 1)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_hi,
                  const __grid_constant__ CUtensorMap tm_lo, AtParams p)
@@ -173,6 +184,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     __shared__ __align__(8) uint64_t bar_k[NS], bar_q[NS], bar_c[NS][C::kMaxChunks], c_free[NS][C::kMaxChunks], b_full[SL], b_free[SL];
     __shared__ __align__(8) uint64_t x_half[NS][4], x_done[NS][4];   // hand-offs between the two warps of a lane quarter
     __shared__ __align__(16) float4 s_x[NS][kBlock];                  // per key: what its two threads tell each other
+    __shared__ __align__(16) float4 s_y[WRAP ? NS : 1][WRAP ? kBlock : 1];   // WRAP: the rest of it (runner-up's group, third best, flag)
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
 
@@ -183,7 +195,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     // A codebook with more chunks than the stream's score region holds (K = 1024: four chunks of 256 columns in a region of
     // 512) goes through the region in rounds: chunk ch lands in slot ch mod kMaxChunks once the scan threads have
     // released the chunk that was there; `rounds` uses of every slot per codebook.
-    const bool wrap = chunks > C::kMaxChunks;
+    constexpr bool wrap = WRAP;                        // (the launcher picks WRAP = chunks > kMaxChunks)
     const int rounds = wrap ? chunks / C::kMaxChunks : 1;
     const int tile0 = static_cast<int>(blockIdx.x) * NS;
     const int n_act = min(NS, p.ntiles - tile0);       // streams with a tile
@@ -349,6 +361,13 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             int bgrp = g_lo;
             uint32_t gbits = 0;   // groups whose maximum came within the threshold of the running best: a superset of
                                   // the groups that can hold a candidate at the end
+            // WRAP: the scores of earlier chunks are gone by the time a key turns out to be doubtful, so the candidates are
+            // tracked on the way: the group of the runner-up, the third largest of all group maxima and group
+            // runners-up, and whether the runner-up of any group came within the threshold of the running best (the
+            // other 30 scores of such a group are unknown here and may hold further candidates).
+            float third = -INFINITY;
+            int sgrp = g_lo;
+            bool amb = bm != nullptr;   // with a bias the threshold moves with the best score: no short list then
             auto rank_group = [&](int g, uint32_t col) {   // group g of the codebook, its 32 score columns at `col` of the stream's region
                 float v[32];
                 load_scores(tbase + col, bm, 32 * g, v);
@@ -356,14 +375,32 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 for (int i = 0; i < 32; ++i) v[i] = tag_score(v[i], i);
                 float hi, lo;
                 top2_32(v, hi, lo);
-                second = fmax3(second, fminf(best, hi), lo);
-                bgrp = hi > best ? g : bgrp;
-                best = fmaxf(best, hi);
-                // with a bias the fp32 additions s + bias round by up to 2^-24 |s + bias| each
-                const float thr_g = bm ? thr0 + fabsf(best) * 4.76837158203125e-7f : thr0;
-                gbits |= (hi >= best - thr_g ? 1u : 0u) << g;
+                if constexpr (wrap) {
+                    // hi, then lo (<= hi) into the sorted triple (best, second, third); a tie with the best goes to the
+                    // earlier group, which holds the lower codes
+                    if (hi > best) {
+                        third = second; second = best; sgrp = bgrp; best = hi; bgrp = g;
+                    } else if (hi > second) {
+                        third = second; second = hi; sgrp = g;
+                    } else {
+                        third = fmaxf(third, hi);
+                    }
+                    if (lo > second) {
+                        third = second; second = lo; sgrp = g;
+                    } else {
+                        third = fmaxf(third, lo);
+                    }
+                    amb |= lo >= best - thr0;
+                } else {
+                    second = fmax3(second, fminf(best, hi), lo);
+                    bgrp = hi > best ? g : bgrp;
+                    best = fmaxf(best, hi);
+                    // with a bias the fp32 additions s + bias round by up to 2^-24 |s + bias| each
+                    const float thr_g = bm ? thr0 + fabsf(best) * 4.76837158203125e-7f : thr0;
+                    gbits |= (hi >= best - thr_g ? 1u : 0u) << g;
+                }
             };
-            if (!wrap) {
+            if constexpr (!wrap) {
 #pragma unroll 1
                 for (int g = g_lo; g < g_hi && ok; ++g) {
                     if (g == g_lo || g % C::kGroupsPerChunk == 0) {
@@ -376,7 +413,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             } else {
                 // rounds through the region: of every chunk this thread ranks half hf of the groups, then releases the slot
                 constexpr int GPC = C::kGroupsPerChunk;
-                bgrp = hf * (GPC / 2);
+                bgrp = sgrp = hf * (GPC / 2);
 #pragma unroll 1
                 for (int ch = 0; ch < chunks && ok; ++ch) {
                     const int cs = ch % C::kMaxChunks, use = m * rounds + ch / C::kMaxChunks;
@@ -396,6 +433,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             int code;
             if (hf == 1) {
                 *xch = make_float4(best, second, __int_as_float(bgrp), __uint_as_float(gbits));
+                if constexpr (wrap) s_y[s][row] = make_float4(third, __int_as_float(sgrp), amb ? 1.f : 0.f, 0.f);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&x_half[s][wq]);
                 ok = __all_sync(kAll, mbar_wait(&x_done[s][wq], m & 1, p.wait_limit));
@@ -407,10 +445,30 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 ok = __all_sync(kAll, mbar_wait(&x_half[s][wq], m & 1, p.wait_limit));
                 if (!ok) break;
                 const float4 o = *xch;
-                second = fmax3(second, fminf(best, o.x), o.y);
-                if (o.x > best || (o.x == best && __float_as_int(o.z) < bgrp)) {   // equal tagged scores: the lower group holds the lower code
-                    best = o.x;
-                    bgrp = __float_as_int(o.z);
+                if constexpr (wrap) {
+                    // the other half's sorted triple into this one (its best with its group, its runner-up with its group, its third)
+                    const float4 oy = s_y[s][row];
+                    const int obg = __float_as_int(o.z), osg = __float_as_int(oy.y);
+                    amb |= oy.z != 0.f;
+                    if (o.x > best || (o.x == best && obg < bgrp)) {   // equal tagged scores: the lower group holds the lower code
+                        third = second; second = best; sgrp = bgrp; best = o.x; bgrp = obg;
+                    } else if (o.x > second) {
+                        third = second; second = o.x; sgrp = obg;
+                    } else {
+                        third = fmaxf(third, o.x);
+                    }
+                    if (o.y > second) {
+                        third = second; second = o.y; sgrp = osg;
+                    } else {
+                        third = fmaxf(third, o.y);
+                    }
+                    third = fmaxf(third, oy.x);
+                } else {
+                    second = fmax3(second, fminf(best, o.x), o.y);
+                    if (o.x > best || (o.x == best && __float_as_int(o.z) < bgrp)) {   // equal tagged scores: the lower group holds the lower code
+                        best = o.x;
+                        bgrp = __float_as_int(o.z);
+                    }
                 }
                 code = bgrp * 32 + 31 - static_cast<int>(__float_as_uint(best) & 31u);  // first group holding the maximum
                 *xch = make_float4(best, __int_as_float(code), 0.f, 0.f);
@@ -426,8 +484,20 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                     const uint32_t gb = dflag ? (gbits | __float_as_uint(o.w)) : 0u;
                     const uint32_t un = __reduce_or_sync(kAll, gb);
                     const float cut = best - thr;
-                    int n = wrap ? 255 : 0;   // rounds through the region: the earlier chunks' scores are gone, every code is a candidate
+                    int n = 0;
                     uint32_t c01 = 0, c23 = 0;
+                    if constexpr (wrap) {
+                        // the best and the runner-up are the only candidates when the third largest tracked score is below the
+                        // cut and no group's runner-up came near the best; otherwise every code is one (the repair kernel
+                        // then scores the whole codebook)
+                        if (!amb && third < cut) {
+                            n = 2;
+                            c01 = static_cast<uint32_t>(code) |
+                                  (static_cast<uint32_t>(sgrp * 32 + 31 - static_cast<int>(__float_as_uint(second) & 31u)) << 16);
+                        } else {
+                            n = 255;
+                        }
+                    }
 #pragma unroll 1
                     for (int g = 0; g < groups && !wrap; ++g) {
                         if (!((un >> g) & 1u)) continue;
@@ -678,7 +748,7 @@ assign_repair_kernel(AtParams p)
     }
 }
 
-template <int D, int NS, int CH>
+template <int D, int NS, int CH, bool WRAP = false>
 static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const VqTensorDesc *bias, VqTensorDesc *codes,
                             void *workspace, int32_t *status, cudaStream_t stream)
 {
@@ -692,8 +762,9 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     unsigned int *counters = reinterpret_cast<unsigned int *>(cn2 + (Hkv * MK + 63) / 64 * 64);
     uint4 *work = reinterpret_cast<uint4 *>(counters + 64);
     uint4 *pool = work + B * Hkv * L;
-    split_codebook_kernel<<<static_cast<unsigned>(Hkv * M), 256, 0, stream>>>(static_cast<const float *>(cb->ptr), hi, lo, cmax, cn2,
-                                                                              counters, static_cast<int>(K), D);
+    if (cudaMemsetAsync(cmax, 0, sizeof(float) * static_cast<size_t>(Hkv * M), stream) != cudaSuccess) return VQ_ELAUNCH;
+    split_codebook_kernel<<<dim3(static_cast<unsigned>(Hkv * M), static_cast<unsigned>((K + kSplitRows - 1) / kSplitRows)), 256, 0, stream>>>(
+        static_cast<const float *>(cb->ptr), hi, lo, cmax, cn2, counters, static_cast<int>(K), D);
     if (launch_status() != VQ_OK) return VQ_ELAUNCH;
     CUtensorMap mk, mhi, mlo;
     const uint64_t cd[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(Hkv * MK), 1};
@@ -717,7 +788,9 @@ static int launch_assign_tc(const VqTensorDesc *k, const VqTensorDesc *cb, const
     p.ntiles = static_cast<int>((L + kBlock - 1) / kBlock);
     p.status = status;
     p.wait_limit = wait_limit_cycles();
-    auto kern = assign_tc_kernel<D, NS, CH>;
+    static_assert(!WRAP || CH == AtCfg<D, NS, CH>::kRegion, "rounds of one chunk per use of the region");
+    if (WRAP != (K / CH > C::kMaxChunks)) return VQ_EUNSUPPORTED;
+    auto kern = assign_tc_kernel<D, NS, CH, WRAP>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal) != cudaSuccess) return VQ_ELAUNCH;
     dim3 grid(static_cast<unsigned>((p.ntiles + NS - 1) / NS), static_cast<unsigned>(B * Hkv));
     kern<<<grid, C::kThreads, C::kTotal, stream>>>(mk, mhi, mlo, p);
@@ -782,15 +855,14 @@ extern "C" int vqattn_assign_codes_ws(const VqTensorDesc *k, const VqTensorDesc 
     if (K == 256)
         return D == 64 ? launch_assign_tc<64, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s)
                        : launch_assign_tc<128, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s);
-    // K = 512: one stream with both chunks resident (measured faster than two streams taking the chunks in rounds, whose
-    // doubtful keys the repair kernel has to score against the whole codebook); K = 1024: two streams, four chunks
-    // in rounds through each stream's 256-column region
+    // K = 512 and K = 1024: two streams, the codebook's 256-column chunks in rounds through each stream's region (the
+    // candidates of a doubtful key are tracked during the scan, the earlier chunks being gone by the end)
     if (K == 512)
-        return D == 64 ? launch_assign_tc<64, 1, 256>(k, codebooks, bias, codes, workspace, status_word, s)
-                       : launch_assign_tc<128, 1, 256>(k, codebooks, bias, codes, workspace, status_word, s);
+        return D == 64 ? launch_assign_tc<64, 2, 256, true>(k, codebooks, bias, codes, workspace, status_word, s)
+                       : launch_assign_tc<128, 2, 256, true>(k, codebooks, bias, codes, workspace, status_word, s);
     if (K == 1024)
-        return D == 64 ? launch_assign_tc<64, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s)
-                       : launch_assign_tc<128, 2, 256>(k, codebooks, bias, codes, workspace, status_word, s);
+        return D == 64 ? launch_assign_tc<64, 2, 256, true>(k, codebooks, bias, codes, workspace, status_word, s)
+                       : launch_assign_tc<128, 2, 256, true>(k, codebooks, bias, codes, workspace, status_word, s);
     return D == 64 ? launch_assign_tc<64, 1, 128>(k, codebooks, bias, codes, workspace, status_word, s)   // K = 384
                    : launch_assign_tc<128, 1, 128>(k, codebooks, bias, codes, workspace, status_word, s);
 }
