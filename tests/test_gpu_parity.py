@@ -423,7 +423,8 @@ def test_assign_tensor_path_ties_zero_keys_and_bias(api):
 
 
 @pytest.mark.parametrize("kind", ["heavy_tail", "low_rank", "near_duplicates", "tiny_codebook", "huge_norms", "all_equal_keys",
-                                  "near_duplicates_k1024", "heavy_tail_k1024"])
+                                  "near_duplicates_k1024", "heavy_tail_k1024", "near_duplicates_k512", "low_rank_k512",
+                                  "all_equal_keys_k512", "close_pairs_k512", "close_pairs_k1024"])
 def test_assign_tensor_path_adversarial_distributions(api, kind):
     """Data that stresses the error bound and the candidate records of the tensor-core assignment: heavy-tailed
     keys, keys in a low-dimensional subspace, codebooks full of near-duplicates (many candidates per key), codewords
@@ -433,6 +434,8 @@ def test_assign_tensor_path_adversarial_distributions(api, kind):
     B, Hkv, L, D, M, K = 2, 3, 3000, 128, 4, 256
     if kind.endswith("_k1024"):
         kind, M, K = kind[:-6], 2, 1024
+    elif kind.endswith("_k512"):       # four codebooks of 512: two chunks in rounds, with the residual chain
+        kind, M, K = kind[:-5], 4, 512
     k = torch.randn(B, Hkv, L, D, generator=g)
     cb = torch.randn(Hkv, M, K, D, generator=g) * D ** -0.25
     if kind == "heavy_tail":
@@ -445,6 +448,11 @@ def test_assign_tensor_path_adversarial_distributions(api, kind):
         base = torch.randn(Hkv, M, 16, D, generator=g) * D ** -0.25
         cb = base.repeat_interleave(K // 16, dim=2) * (1 + 2 ** -20 * torch.randn(Hkv, M, K, 1, generator=g))
         cb[:, :, 1::2] = cb[:, :, 0::2]                      # exact duplicates too: first index must win
+    elif kind == "close_pairs":
+        # every codeword has one near-twin 2^-16 away, in another chunk of 256 codes: the two candidates of a doubtful
+        # key then come from different rounds through the score region
+        half = cb[:, :, :K // 2]
+        cb = torch.cat([half, half * (1 + 2 ** -16 * torch.randn(Hkv, M, K // 2, 1, generator=g))], dim=2)
     elif kind == "tiny_codebook":
         cb = cb * 1e-3
     elif kind == "huge_norms":
