@@ -184,7 +184,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     __shared__ __align__(8) uint64_t bar_k[NS], bar_q[NS], bar_c[NS][C::kMaxChunks], c_free[NS][C::kMaxChunks], b_full[SL], b_free[SL];
     __shared__ __align__(8) uint64_t x_half[NS][4], x_done[NS][4];   // hand-offs between the two warps of a lane quarter
     __shared__ __align__(16) float4 s_x[NS][kBlock];                  // per key: what its two threads tell each other
-    __shared__ __align__(16) float4 s_y[WRAP ? NS : 1][WRAP ? kBlock : 1];   // WRAP: the rest of it (runner-up's group, third best, flag)
+    __shared__ __align__(16) float4 s_y[NS][kBlock];                  // ... the rest of it (third best, runner-up's group, flag)
     __shared__ uint32_t s_tmem;
     __shared__ int s_err;
 
@@ -361,10 +361,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             int bgrp = g_lo;
             uint32_t gbits = 0;   // groups whose maximum came within the threshold of the running best: a superset of
                                   // the groups that can hold a candidate at the end
-            // WRAP: the scores of earlier chunks are gone by the time a key turns out to be doubtful, so the candidates are
-            // tracked on the way: the group of the runner-up, the third largest of all group maxima and group
-            // runners-up, and whether the runner-up of any group came within the threshold of the running best (the
-            // other 30 scores of such a group are unknown here and may hold further candidates).
+            // The candidates of a key that turns out doubtful are tracked on the way: the group of the runner-up, the third
+            // largest of all group maxima and group runners-up, and whether the runner-up of any group came within the
+            // threshold of the running best (the other 30 scores of such a group are unknown here and may hold further
+            // candidates).  A doubtful key whose third lies below the cut needs no second look at its scores - which WRAP
+            // could not take anyway: the scores of earlier chunks are gone by then.
             float third = -INFINITY;
             int sgrp = g_lo;
             bool amb = bm != nullptr;   // with a bias the threshold moves with the best score: no short list then
@@ -375,27 +376,24 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 for (int i = 0; i < 32; ++i) v[i] = tag_score(v[i], i);
                 float hi, lo;
                 top2_32(v, hi, lo);
-                if constexpr (wrap) {
-                    // hi, then lo (<= hi) into the sorted triple (best, second, third); a tie with the best goes to the
-                    // earlier group, which holds the lower codes
-                    if (hi > best) {
-                        third = second; second = best; sgrp = bgrp; best = hi; bgrp = g;
-                    } else if (hi > second) {
-                        third = second; second = hi; sgrp = g;
-                    } else {
-                        third = fmaxf(third, hi);
-                    }
-                    if (lo > second) {
-                        third = second; second = lo; sgrp = g;
-                    } else {
-                        third = fmaxf(third, lo);
-                    }
-                    amb |= lo >= best - thr0;
+                // hi, then lo (<= hi) into the sorted triple (best, second, third); a tie with the best goes to the
+                // earlier group, which holds the lower codes
+                if (hi > best) {
+                    third = second; second = best; sgrp = bgrp; best = hi; bgrp = g;
+                } else if (hi > second) {
+                    third = second; second = hi; sgrp = g;
                 } else {
-                    second = fmax3(second, fminf(best, hi), lo);
-                    bgrp = hi > best ? g : bgrp;
-                    best = fmaxf(best, hi);
-                    // with a bias the fp32 additions s + bias round by up to 2^-24 |s + bias| each
+                    third = fmaxf(third, hi);
+                }
+                if (lo > second) {
+                    third = second; second = lo; sgrp = g;
+                } else {
+                    third = fmaxf(third, lo);
+                }
+                amb |= lo >= best - thr0;
+                if constexpr (!wrap) {
+                    // for the keys that do need a second look: the groups whose maximum came within the threshold
+                    // (with a bias the fp32 additions s + bias round by up to 2^-24 |s + bias| each)
                     const float thr_g = bm ? thr0 + fabsf(best) * 4.76837158203125e-7f : thr0;
                     gbits |= (hi >= best - thr_g ? 1u : 0u) << g;
                 }
@@ -433,7 +431,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             int code;
             if (hf == 1) {
                 *xch = make_float4(best, second, __int_as_float(bgrp), __uint_as_float(gbits));
-                if constexpr (wrap) s_y[s][row] = make_float4(third, __int_as_float(sgrp), amb ? 1.f : 0.f, 0.f);
+                s_y[s][row] = make_float4(third, __int_as_float(sgrp), amb ? 1.f : 0.f, 0.f);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&x_half[s][wq]);
                 ok = __all_sync(kAll, mbar_wait(&x_done[s][wq], m & 1, p.wait_limit));
@@ -445,7 +443,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 ok = __all_sync(kAll, mbar_wait(&x_half[s][wq], m & 1, p.wait_limit));
                 if (!ok) break;
                 const float4 o = *xch;
-                if constexpr (wrap) {
+                {
                     // the other half's sorted triple into this one (its best with its group, its runner-up with its group, its third)
                     const float4 oy = s_y[s][row];
                     const int obg = __float_as_int(o.z), osg = __float_as_int(oy.y);
@@ -463,12 +461,6 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                         third = fmaxf(third, o.y);
                     }
                     third = fmaxf(third, oy.x);
-                } else {
-                    second = fmax3(second, fminf(best, o.x), o.y);
-                    if (o.x > best || (o.x == best && __float_as_int(o.z) < bgrp)) {   // equal tagged scores: the lower group holds the lower code
-                        best = o.x;
-                        bgrp = __float_as_int(o.z);
-                    }
                 }
                 code = bgrp * 32 + 31 - static_cast<int>(__float_as_uint(best) & 31u);  // first group holding the maximum
                 *xch = make_float4(best, __int_as_float(code), 0.f, 0.f);
@@ -479,25 +471,24 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 const bool dflag = valid && !(best - second > thr);
                 if (__ballot_sync(kAll, dflag)) {
                     // ---- some key of this warp is doubtful: its candidates (scores within thr of the best) go into a
-                    // record for the repair kernel; carry on with the approximate winner.  Tensor-memory loads are
-                    // warp-wide, so the warp re-reads the union of its doubtful keys' marked groups.
-                    const uint32_t gb = dflag ? (gbits | __float_as_uint(o.w)) : 0u;
-                    const uint32_t un = __reduce_or_sync(kAll, gb);
+                    // record for the repair kernel; carry on with the approximate winner.  The best and the runner-up are
+                    // the only candidates when the third largest tracked score is below the cut and no group's runner-up
+                    // came near the best.  The other doubtful keys take a second look at their scores (tensor-memory
+                    // loads are warp-wide, so the warp re-reads the union of those keys' marked groups) - or, with WRAP,
+                    // name every code a candidate (the repair kernel then scores the whole codebook).
                     const float cut = best - thr;
+                    const bool quick = dflag && !amb && third < cut;
+                    const bool slow = dflag && !quick;
                     int n = 0;
                     uint32_t c01 = 0, c23 = 0;
-                    if constexpr (wrap) {
-                        // the best and the runner-up are the only candidates when the third largest tracked score is below the
-                        // cut and no group's runner-up came near the best; otherwise every code is one (the repair kernel
-                        // then scores the whole codebook)
-                        if (!amb && third < cut) {
-                            n = 2;
-                            c01 = static_cast<uint32_t>(code) |
-                                  (static_cast<uint32_t>(sgrp * 32 + 31 - static_cast<int>(__float_as_uint(second) & 31u)) << 16);
-                        } else {
-                            n = 255;
-                        }
+                    if (quick) {
+                        n = 2;
+                        c01 = static_cast<uint32_t>(code) |
+                              (static_cast<uint32_t>(sgrp * 32 + 31 - static_cast<int>(__float_as_uint(second) & 31u)) << 16);
                     }
+                    if (wrap && slow) n = 255;
+                    const uint32_t gb = (!wrap && slow) ? (gbits | __float_as_uint(o.w)) : 0u;
+                    const uint32_t un = __reduce_or_sync(kAll, gb);
 #pragma unroll 1
                     for (int g = 0; g < groups && !wrap; ++g) {
                         if (!((un >> g) & 1u)) continue;
