@@ -530,48 +530,92 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 // This thread updates half hf of its key's row, 8 columns (one 16-byte chunk of each term) at a time;
                 // its part of the codebook row is loaded first (independent 16-byte loads, all in flight: the rows
                 // of a tile's keys are scattered over the codebook, every load is a trip to L2).
-                constexpr int CPT = D / 16;                    // 16-byte chunks per thread
-                const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D + hf * (D / 2);
-                const uint32_t rbase = row * 128;
-                float4 crow4[2 * CPT];
+                if constexpr (D == 128) {
+                    // The warp walks 16 of its quarter's 32 keys (the partner warp the other 16); lane l owns the columns
+                    // 4l .. 4l+3 of every one of them.  One load instruction then covers one codebook row - four full
+                    // 128-byte lines - where a thread fetching its own key's half row touched 32 different lines per
+                    // instruction; eight loads are in flight at a time.
+                    const uint32_t lane_off = (lane >> 4) * kHalfBytes + 8 * (lane & 1);   // the 64-column half and the 8 bytes inside a 16-byte chunk
+                    const int chunk = (lane & 15) >> 1;
+#pragma unroll 1
+                    for (int i0 = 0; i0 < 16; i0 += 8) {   // two batches of eight rows (registers)
+                        float4 crow4[8];
 #pragma unroll
-                for (int i = 0; i < 2 * CPT; ++i) crow4[i] = __ldg(reinterpret_cast<const float4 *>(crow + 4 * i));
+                        for (int i = 0; i < 8; ++i) {
+                            const int ck = __shfl_sync(kAll, code, 16 * hf + i0 + i);
+                            crow4[i] = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(m) * K + ck) * D) + lane);
+                        }
 #pragma unroll
-                for (int cc = 0; cc < CPT; ++cc) {
-                    const int ck = hf * CPT + cc;
-                    const float4 ca = crow4[2 * cc], cb4 = crow4[2 * cc + 1];
-                    const uint32_t off = (ck >> 3) * kHalfBytes + rbase + (((ck & 7) ^ (row & 7)) << 4);
-                    uint4 *ph = reinterpret_cast<uint4 *>(a_rh + off);
-                    uint4 *pl = reinterpret_cast<uint4 *>(a_rl + off);
-                    const uint4 vh = *ph;
-                    const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&vh);
-                    float x[8];
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = wq * 32 + 16 * hf + i0 + i;
+                            const uint32_t off = lane_off + r * 128 + ((chunk ^ (r & 7)) << 4);
+                            uint2 *ph = reinterpret_cast<uint2 *>(a_rh + off);
+                            uint2 *pl = reinterpret_cast<uint2 *>(a_rl + off);
+                            const uint2 vh = *ph;
+                            float x[4] = {__uint_as_float(vh.x << 16), __uint_as_float(vh.x & 0xffff0000u), __uint_as_float(vh.y << 16),
+                                          __uint_as_float(vh.y & 0xffff0000u)};
+                            if (m > 0) {
+                                const uint2 vl = *pl;
+                                x[0] += __uint_as_float(vl.x << 16); x[1] += __uint_as_float(vl.x & 0xffff0000u);
+                                x[2] += __uint_as_float(vl.y << 16); x[3] += __uint_as_float(vl.y & 0xffff0000u);
+                            }
+                            x[0] -= crow4[i].x; x[1] -= crow4[i].y; x[2] -= crow4[i].z; x[3] -= crow4[i].w;
+                            uint32_t wh[2], wl[2];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        x[2 * e] = __low2float(h2[e]);
-                        x[2 * e + 1] = __high2float(h2[e]);
-                    }
-                    if (m > 0) {
-                        const uint4 vl = *pl;
-                        const __nv_bfloat162 *l2 = reinterpret_cast<const __nv_bfloat162 *>(&vl);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            x[2 * e] += __low2float(l2[e]);
-                            x[2 * e + 1] += __high2float(l2[e]);
+                            for (int e = 0; e < 2; ++e) {
+                                const __nv_bfloat16 h0 = __float2bfloat16_rn(x[2 * e]), h1 = __float2bfloat16_rn(x[2 * e + 1]);
+                                __nv_bfloat162 hv = __halves2bfloat162(h0, h1);
+                                wh[e] = *reinterpret_cast<uint32_t *>(&hv);
+                                wl[e] = pack_bf16(x[2 * e] - __bfloat162float(h0), x[2 * e + 1] - __bfloat162float(h1));
+                            }
+                            *ph = make_uint2(wh[0], wh[1]);
+                            *pl = make_uint2(wl[0], wl[1]);
                         }
                     }
-                    x[0] -= ca.x; x[1] -= ca.y; x[2] -= ca.z; x[3] -= ca.w;
-                    x[4] -= cb4.x; x[5] -= cb4.y; x[6] -= cb4.z; x[7] -= cb4.w;
-                    uint32_t wh[4], wl[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat16 h0 = __float2bfloat16_rn(x[2 * e]), h1 = __float2bfloat16_rn(x[2 * e + 1]);
-                        __nv_bfloat162 hv = __halves2bfloat162(h0, h1);
-                        wh[e] = *reinterpret_cast<uint32_t *>(&hv);
-                        wl[e] = pack_bf16(x[2 * e] - __bfloat162float(h0), x[2 * e + 1] - __bfloat162float(h1));
+                } else {
+                    constexpr int CPT = D / 16;                    // 16-byte chunks per thread
+                    const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D + hf * (D / 2);
+                    const uint32_t rbase = row * 128;
+                    float4 crow4[2 * CPT];
+    #pragma unroll
+                    for (int i = 0; i < 2 * CPT; ++i) crow4[i] = __ldg(reinterpret_cast<const float4 *>(crow + 4 * i));
+    #pragma unroll
+                    for (int cc = 0; cc < CPT; ++cc) {
+                        const int ck = hf * CPT + cc;
+                        const float4 ca = crow4[2 * cc], cb4 = crow4[2 * cc + 1];
+                        const uint32_t off = (ck >> 3) * kHalfBytes + rbase + (((ck & 7) ^ (row & 7)) << 4);
+                        uint4 *ph = reinterpret_cast<uint4 *>(a_rh + off);
+                        uint4 *pl = reinterpret_cast<uint4 *>(a_rl + off);
+                        const uint4 vh = *ph;
+                        const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&vh);
+                        float x[8];
+    #pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            x[2 * e] = __low2float(h2[e]);
+                            x[2 * e + 1] = __high2float(h2[e]);
+                        }
+                        if (m > 0) {
+                            const uint4 vl = *pl;
+                            const __nv_bfloat162 *l2 = reinterpret_cast<const __nv_bfloat162 *>(&vl);
+    #pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                x[2 * e] += __low2float(l2[e]);
+                                x[2 * e + 1] += __high2float(l2[e]);
+                            }
+                        }
+                        x[0] -= ca.x; x[1] -= ca.y; x[2] -= ca.z; x[3] -= ca.w;
+                        x[4] -= cb4.x; x[5] -= cb4.y; x[6] -= cb4.z; x[7] -= cb4.w;
+                        uint32_t wh[4], wl[4];
+    #pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat16 h0 = __float2bfloat16_rn(x[2 * e]), h1 = __float2bfloat16_rn(x[2 * e + 1]);
+                            __nv_bfloat162 hv = __halves2bfloat162(h0, h1);
+                            wh[e] = *reinterpret_cast<uint32_t *>(&hv);
+                            wl[e] = pack_bf16(x[2 * e] - __bfloat162float(h0), x[2 * e + 1] - __bfloat162float(h1));
+                        }
+                        *ph = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                        *pl = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                     }
-                    *ph = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-                    *pl = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
                 // Norm of the new residual rho' = rho - C[code] without another pass over it:
                 //   |rho'|^2 = |rho|^2 - 2 rho.C + |C|^2,   rho.C >= s - eps |rho| max|C|
