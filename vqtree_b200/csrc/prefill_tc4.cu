@@ -422,21 +422,37 @@ prefill_tc4_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_const
             }
             const float inv = den > 0.f ? 1.f / den : 0.f;
             const int64_t grow = static_cast<int64_t>(m) * kBlock + row;
-            uint16_t *o = p.out + b * p.o_sb + hq * p.o_sh + grow * p.o_sl + g * C::kOq;
             uint32_t r[C::kOq];
 #pragma unroll
             for (int c = 0; c < C::kOq / 32; ++c) tmem_ld32(o_addr + g * C::kOq + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
             tc_wait_ld();
-            if (grow < p.L) {
+            // The thread holds kOq columns of its own row; stored from here, every instruction of the warp would touch 32
+            // different rows.  So the warp's 32 x (2 kOq)-byte block goes through the tile ring (free: the last product has
+            // completed, and with it every read of the ring) and is written out with eight lanes per row - whole 128-byte
+            // lines.  Rows padded by 16 bytes: the 16-byte accesses of eight lanes fall into different banks.
+            constexpr int kRowB = C::kOq * 2, kPitch = kRowB + 16;          // bytes per row of the warp's block
+            uint8_t *stg = smem + C::kRing + warp * (32 * kPitch);
 #pragma unroll
-                for (int j = 0; j < C::kOq / 8; ++j) {
-                    uint4 w;
-                    w.x = pack16<F16>(__uint_as_float(r[8 * j]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
-                    w.y = pack16<F16>(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
-                    w.z = pack16<F16>(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
-                    w.w = pack16<F16>(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
-                    *reinterpret_cast<uint4 *>(o + 8 * j) = w;
-                }
+            for (int j = 0; j < C::kOq / 8; ++j) {
+                uint4 w;
+                w.x = pack16<F16>(__uint_as_float(r[8 * j]) * inv, __uint_as_float(r[8 * j + 1]) * inv);
+                w.y = pack16<F16>(__uint_as_float(r[8 * j + 2]) * inv, __uint_as_float(r[8 * j + 3]) * inv);
+                w.z = pack16<F16>(__uint_as_float(r[8 * j + 4]) * inv, __uint_as_float(r[8 * j + 5]) * inv);
+                w.w = pack16<F16>(__uint_as_float(r[8 * j + 6]) * inv, __uint_as_float(r[8 * j + 7]) * inv);
+                *reinterpret_cast<uint4 *>(stg + lane * kPitch + 16 * j) = w;
+            }
+            __syncwarp();
+            constexpr int kLanesPerRow = kRowB / 16, kRowsPerIt = 32 / kLanesPerRow;
+            const int sub = lane / kLanesPerRow, ch = lane % kLanesPerRow;
+            uint16_t *obase = p.out + b * p.o_sb + hq * p.o_sh + g * C::kOq + 8 * ch;
+#pragma unroll
+            for (int it = 0; it < 32 / kRowsPerIt; ++it) {
+                const int rr = it * kRowsPerIt + sub;                           // row inside the warp's block
+                const int64_t gr = static_cast<int64_t>(m) * kBlock + lq * 32 + rr;
+                const uint4 w = *reinterpret_cast<const uint4 *>(stg + rr * kPitch + 16 * ch);
+                if (gr < p.L) *reinterpret_cast<uint4 *>(obase + gr * p.o_sl) = w;
+            }
+            if (grow < p.L) {
                 if (g == 0 && p.lse2) p.lse2[static_cast<int64_t>(bh) * p.L + grow] = ref + log2f(den);
             }
         }
