@@ -526,28 +526,28 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             }
             rbound += cm;
             if (m + 1 < M) {
-                // ---- residual -= C_m[code], re-split into bf16 hi / lo in the 128B-swizzled operand layout.
-                // This thread updates half hf of its key's row, 8 columns (one 16-byte chunk of each term) at a time;
-                // its part of the codebook row is loaded first (independent 16-byte loads, all in flight: the rows
-                // of a tile's keys are scattered over the codebook, every load is a trip to L2).
-                if constexpr (D == 128) {
-                    // The warp walks 16 of its quarter's 32 keys (the partner warp the other 16); lane l owns the columns
-                    // 4l .. 4l+3 of every one of them.  One load instruction then covers one codebook row - four full
+                // ---- residual -= C_m[code] (fp32), re-split into bf16 hi / lo in the 128B-swizzled operand layout
+                {
+                    // The warp walks 16 of its quarter's 32 keys (the partner warp the other 16); D/4 lanes share a key, lane l
+                    // of them owns its columns 4l .. 4l+3.  One load instruction then covers whole codebook rows - full
                     // 128-byte lines - where a thread fetching its own key's half row touched 32 different lines per
                     // instruction; eight loads are in flight at a time.
-                    const uint32_t lane_off = (lane >> 4) * kHalfBytes + 8 * (lane & 1);   // the 64-column half and the 8 bytes inside a 16-byte chunk
-                    const int chunk = (lane & 15) >> 1;
+                    constexpr int LPR = D / 4, KPI = 32 / LPR, NIT = 16 / KPI;   // lanes per row, keys per instruction, instructions
+                    constexpr int NB = NIT < 8 ? NIT : 8;                       // loads in flight (registers)
+                    const int sub = lane / LPR, l = lane % LPR;
+                    const uint32_t lane_off = (l >> 4) * kHalfBytes + 8 * (l & 1);   // the 64-column half and the 8 bytes inside a 16-byte chunk
+                    const int chunk = (l & 15) >> 1;
 #pragma unroll 1
-                    for (int i0 = 0; i0 < 16; i0 += 8) {   // two batches of eight rows (registers)
-                        float4 crow4[8];
+                    for (int i0 = 0; i0 < NIT; i0 += NB) {
+                        float4 crow4[NB];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int ck = __shfl_sync(kAll, code, 16 * hf + i0 + i);
-                            crow4[i] = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(m) * K + ck) * D) + lane);
+                        for (int i = 0; i < NB; ++i) {
+                            const int ck = __shfl_sync(kAll, code, 16 * hf + (i0 + i) * KPI + sub);
+                            crow4[i] = __ldg(reinterpret_cast<const float4 *>(cbh + (static_cast<int64_t>(m) * K + ck) * D) + l);
                         }
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int r = wq * 32 + 16 * hf + i0 + i;
+                        for (int i = 0; i < NB; ++i) {
+                            const int r = wq * 32 + 16 * hf + (i0 + i) * KPI + sub;
                             const uint32_t off = lane_off + r * 128 + ((chunk ^ (r & 7)) << 4);
                             uint2 *ph = reinterpret_cast<uint2 *>(a_rh + off);
                             uint2 *pl = reinterpret_cast<uint2 *>(a_rl + off);
@@ -571,50 +571,6 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                             *ph = make_uint2(wh[0], wh[1]);
                             *pl = make_uint2(wl[0], wl[1]);
                         }
-                    }
-                } else {
-                    constexpr int CPT = D / 16;                    // 16-byte chunks per thread
-                    const float *crow = cbh + (static_cast<int64_t>(m) * K + code) * D + hf * (D / 2);
-                    const uint32_t rbase = row * 128;
-                    float4 crow4[2 * CPT];
-    #pragma unroll
-                    for (int i = 0; i < 2 * CPT; ++i) crow4[i] = __ldg(reinterpret_cast<const float4 *>(crow + 4 * i));
-    #pragma unroll
-                    for (int cc = 0; cc < CPT; ++cc) {
-                        const int ck = hf * CPT + cc;
-                        const float4 ca = crow4[2 * cc], cb4 = crow4[2 * cc + 1];
-                        const uint32_t off = (ck >> 3) * kHalfBytes + rbase + (((ck & 7) ^ (row & 7)) << 4);
-                        uint4 *ph = reinterpret_cast<uint4 *>(a_rh + off);
-                        uint4 *pl = reinterpret_cast<uint4 *>(a_rl + off);
-                        const uint4 vh = *ph;
-                        const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&vh);
-                        float x[8];
-    #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            x[2 * e] = __low2float(h2[e]);
-                            x[2 * e + 1] = __high2float(h2[e]);
-                        }
-                        if (m > 0) {
-                            const uint4 vl = *pl;
-                            const __nv_bfloat162 *l2 = reinterpret_cast<const __nv_bfloat162 *>(&vl);
-    #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                x[2 * e] += __low2float(l2[e]);
-                                x[2 * e + 1] += __high2float(l2[e]);
-                            }
-                        }
-                        x[0] -= ca.x; x[1] -= ca.y; x[2] -= ca.z; x[3] -= ca.w;
-                        x[4] -= cb4.x; x[5] -= cb4.y; x[6] -= cb4.z; x[7] -= cb4.w;
-                        uint32_t wh[4], wl[4];
-    #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat16 h0 = __float2bfloat16_rn(x[2 * e]), h1 = __float2bfloat16_rn(x[2 * e + 1]);
-                            __nv_bfloat162 hv = __halves2bfloat162(h0, h1);
-                            wh[e] = *reinterpret_cast<uint32_t *>(&hv);
-                            wl[e] = pack_bf16(x[2 * e] - __bfloat162float(h0), x[2 * e + 1] - __bfloat162float(h1));
-                        }
-                        *ph = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-                        *pl = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                     }
                 }
                 // Norm of the new residual rho' = rho - C[code] without another pass over it:
